@@ -1,0 +1,166 @@
+/*
+ * tritonix_b200 — C ABI of the dense-contraction path (GEMM, split-K GEMM, fused GLU/SwiGLU)
+ * for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point takes plain pointers and sizes.  The library never allocates or frees
+ * device memory (with the single documented exception of nothing: outputs, the split-K
+ * workspace and the status word all belong to the caller) and never synchronises the host
+ * with the device unless the function's comment says so.  Kernels are enqueued on the
+ * stream handle that is passed in (a cudaStream_t cast to void*; NULL = default stream).
+ *
+ * Status codes (returned by every function that returns int):
+ *   TNX_OK                0  success (kernel enqueued)
+ *   TNX_ERR_INVALID       1  bad shape / stride / alignment / dtype / null pointer
+ *   TNX_ERR_RESOURCES     2  configuration exceeds the shared-memory or TMEM budget of one SM
+ *                            (the "out of resources" condition the tuner prunes on; decided on
+ *                            the host before any launch)
+ *   TNX_ERR_NOT_BUILT     3  configuration is valid in principle but has no compiled kernel
+ *   TNX_ERR_CUDA          4  CUDA runtime / driver error; text in tnx_last_error()
+ *   TNX_ERR_DEVICE        5  the device status word is non-zero (a bounded wait in a kernel
+ *                            gave up); only returned by tnx_read_status()
+ */
+#ifndef TRITONIX_B200_H_
+#define TRITONIX_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TNX_OK 0
+#define TNX_ERR_INVALID 1
+#define TNX_ERR_RESOURCES 2
+#define TNX_ERR_NOT_BUILT 3
+#define TNX_ERR_CUDA 4
+#define TNX_ERR_DEVICE 5
+
+/* element types of A, B and C (C always has the type of A and B) */
+#define TNX_F16 0
+#define TNX_BF16 1
+#define TNX_F32 2
+
+/* epilogue applied to the fp32 accumulator before the cast to the output type */
+#define TNX_EPI_NONE 0        /* C = A.B                                                    */
+#define TNX_EPI_GLU_LINEAR 1  /* Z[:, j] = acc[:, 2j] * acc[:, 2j+1]        (activation="none") */
+#define TNX_EPI_GLU_SILU 2    /* Z[:, j] = silu(acc[:, 2j]) * acc[:, 2j+1]  (activation="silu") */
+#define TNX_EPI_GLU_SIGMOID 3 /* Z[:, j] = sigmoid(acc[:, 2j]) * acc[:, 2j+1]                   */
+
+/* order in which the persistent CTAs walk the output tiles */
+#define TNX_ORDER_GROUPED 0    /* bands of group_m tile rows, column-major inside a band       */
+#define TNX_ORDER_SERPENTINE 1 /* same bands, boustrophedon: consecutive tiles share an operand */
+#define TNX_ORDER_TABLE 2      /* caller-supplied table (e.g. a Hilbert curve), see tile_table  */
+
+/* which kernel family executes the call */
+#define TNX_KERNEL_AUTO 0    /* tcgen05 path when the operands qualify, else the strided path */
+#define TNX_KERNEL_TCGEN05 1 /* TMA + tcgen05.mma + TMEM; fails with TNX_ERR_INVALID otherwise */
+#define TNX_KERNEL_STRIDED 2 /* CUDA-core kernel for arbitrary strides, odd sizes and fp32     */
+
+/*
+ * One contraction problem.  Replaces the positional arguments of the reference's Triton
+ * kernels: (a_ptr, b_ptr, c_ptr, m, n, k, stride_am, stride_ak, stride_bk, stride_bn,
+ * stride_cm, stride_cn) of matmul_kernel (tritonix/ops/matmul.py:42-56), gemm_splitk_kernel
+ * (tritonix/ops/matmul.py:147-161) and glu_kernel (tritonix/ops/swiglu.py:24-37).
+ * Strides are in elements.  For the GLU epilogues n is the number of columns of the
+ * interleaved weight matrix W12 (n = 2F) and the output has n/2 columns, exactly as the
+ * reference passes it (tritonix/ops/swiglu.py:104-110).
+ */
+typedef struct tnx_problem {
+  int32_t m, n, k;
+  int32_t dtype;    /* TNX_F16 | TNX_BF16 | TNX_F32 */
+  int32_t epilogue; /* TNX_EPI_* */
+  int32_t reserved0;
+  int64_t stride_am, stride_ak;
+  int64_t stride_bk, stride_bn;
+  int64_t stride_cm, stride_cn;
+} tnx_problem;
+
+/*
+ * Kernel configuration = the tuner's search space (replaces the constexpr / launch keyword
+ * arguments block_m, block_n, block_k, group_m, split_k, num_stages of the reference's kernels,
+ * tritonix/ops/matmul.py:33-39,136-143).  Zero in any field selects the library default.
+ */
+typedef struct tnx_config {
+  int32_t tile_m;     /* rows of C per CTA (128) or per CTA pair (256 when cta_group == 2)        */
+  int32_t tile_n;     /* columns of B per tile: 64, 128 or 256                                    */
+  int32_t tile_k;     /* K elements per pipeline stage: 64 or 128                                 */
+  int32_t stages;     /* depth of the TMA -> shared-memory ring, >= 2                             */
+  int32_t acc_stages; /* TMEM accumulator buffers: 1 or 2 (2 overlaps epilogue and main loop)     */
+  int32_t cta_group;  /* 1 = one SM per tile, 2 = tcgen05 cta_group::2 (CTA pair shares one tile) */
+  int32_t split_k;    /* K slices per tile, >= 1; > 1 needs the workspace                         */
+  int32_t group_m;    /* band height of the grouped / serpentine order                            */
+  int32_t tile_order; /* TNX_ORDER_*                                                              */
+  int32_t kernel;     /* TNX_KERNEL_*                                                             */
+  int32_t max_ctas;   /* cap on the persistent grid (0 = one CTA per SM)                          */
+  int32_t reserved0;
+} tnx_config;
+
+/* What a (problem, config) pair needs.  Filled by tnx_gemm_query(). */
+typedef struct tnx_resources {
+  int32_t kernel;          /* TNX_KERNEL_TCGEN05 or TNX_KERNEL_STRIDED: the family that will run */
+  int32_t smem_bytes;      /* dynamic shared memory per CTA                                      */
+  int32_t tmem_columns;    /* TMEM columns allocated per CTA (power of two, <= 512)              */
+  int32_t grid;            /* CTAs launched                                                      */
+  int32_t tiles_m, tiles_n;
+  int32_t split_k;         /* effective split (clamped so that no slice is empty)                */
+  int32_t reserved0;
+  int64_t workspace_bytes; /* bytes of caller-owned scratch needed at this split_k (0 if none)   */
+} tnx_resources;
+
+/* Library version, "major.minor.patch". */
+const char* tnx_version(void);
+
+/* Text of the most recent error on the calling thread ("" if none). */
+const char* tnx_last_error(void);
+
+/* Number of SMs of the current device (0 and TNX_ERR_CUDA text if there is none). */
+int tnx_sm_count(void);
+
+/*
+ * Resource query: validates (problem, config), fills *out and returns TNX_OK,
+ * TNX_ERR_INVALID, TNX_ERR_RESOURCES or TNX_ERR_NOT_BUILT without touching the device.
+ * This is the host-side replacement for Triton raising OutOfResources at launch
+ * (tritonix/autotune.py:134-138): the tuner calls it (through tnx_gemm) before timing.
+ */
+int tnx_gemm_query(const tnx_problem* problem, const tnx_config* config, tnx_resources* out);
+
+/*
+ * C = epilogue(A . B).  Replaces a launch of matmul_kernel / gemm_splitk_kernel / glu_kernel
+ * (tritonix/ops/matmul.py:222-236, :249-263; tritonix/ops/swiglu.py:24-110).
+ *
+ *   a, b, c      device pointers (c: m x n, or m x n/2 for a GLU epilogue)
+ *   workspace    device scratch of at least tnx_resources.workspace_bytes, 256-byte aligned;
+ *                may be NULL when workspace_bytes == 0.  The first 64 KiB hold the split-K
+ *                tile counters and MUST be zero before the first call that uses the buffer;
+ *                the kernel leaves them zero again, so no clearing is needed between calls.
+ *                Calls that share a workspace must be ordered on one stream.
+ *   tile_table   device int32[tiles_m*tiles_n], entry t = (tile_row << 16) | tile_col of the
+ *                t-th tile to process; only read when config->tile_order == TNX_ORDER_TABLE
+ *   status_word  device int32 that a kernel sets to a non-zero code if one of its bounded
+ *                waits expires (may be NULL).  Read it with tnx_read_status().
+ *   stream       cudaStream_t
+ */
+int tnx_gemm(const tnx_problem* problem, const tnx_config* config, const void* a, const void* b,
+             void* c, void* workspace, size_t workspace_bytes, const int32_t* tile_table,
+             int32_t* status_word, void* stream);
+
+/*
+ * Convenience wrapper over tnx_gemm for the fused gate*up product: problem->epilogue is
+ * overridden by `activation` (TNX_EPI_GLU_LINEAR / _SILU / _SIGMOID).  Replaces
+ * glu_kernel[grid](x, w12, z, m, n, k, ..., activation=...) (tritonix/ops/swiglu.py:24-43).
+ */
+int tnx_glu(const tnx_problem* problem, const tnx_config* config, int activation, const void* x,
+            const void* w12, void* z, const int32_t* tile_table, int32_t* status_word,
+            void* stream);
+
+/*
+ * Synchronises `stream`, copies *status_word to the host and returns TNX_OK if it is zero,
+ * else TNX_ERR_DEVICE (code available in *code_out if not NULL) after resetting it to zero.
+ */
+int tnx_read_status(int32_t* status_word, int32_t* code_out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TRITONIX_B200_H_ */

@@ -1,0 +1,238 @@
+"""ctypes binding of libtritonix_b200.so (declared in include/tritonix_b200.h).
+
+This module is the only place where Python touches the C ABI.  There is no fallback: if the
+library is missing or fails to load, importing this module raises, and every op of the package
+raises with it.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from pathlib import Path
+
+import torch
+
+_LIB_PATH = Path(__file__).resolve().parent / "lib" / "libtritonix_b200.so"
+
+# ---- constants mirrored from include/tritonix_b200.h
+OK, ERR_INVALID, ERR_RESOURCES, ERR_NOT_BUILT, ERR_CUDA, ERR_DEVICE = range(6)
+F16, BF16, F32 = 0, 1, 2
+EPI_NONE, EPI_GLU_LINEAR, EPI_GLU_SILU, EPI_GLU_SIGMOID = 0, 1, 2, 3
+ORDER_GROUPED, ORDER_SERPENTINE, ORDER_TABLE = 0, 1, 2
+KERNEL_AUTO, KERNEL_TCGEN05, KERNEL_STRIDED = 0, 1, 2
+COUNTER_BYTES = 65536
+
+DTYPES = {torch.float16: F16, torch.bfloat16: BF16, torch.float32: F32}
+ACTIVATIONS = {"none": EPI_GLU_LINEAR, "silu": EPI_GLU_SILU, "sigmoid": EPI_GLU_SIGMOID}
+TILE_ORDERS = {"grouped": ORDER_GROUPED, "serpentine": ORDER_SERPENTINE, "hilbert": ORDER_TABLE,
+               "table": ORDER_TABLE}
+KERNELS = {"auto": KERNEL_AUTO, "tcgen05": KERNEL_TCGEN05, "strided": KERNEL_STRIDED}
+
+
+class OutOfResources(Exception):
+    """A kernel configuration exceeds the shared-memory or TMEM budget of one SM.
+
+    Plays the role of ``triton.OutOfResources`` in the reference's tuner
+    (tritonix/autotune.py:134-138): the tuner catches it and prunes every configuration that
+    needs at least as much memory.
+    """
+
+
+class DeviceStatusError(RuntimeError):
+    """A kernel gave up one of its bounded waits and reported it through the status word."""
+
+
+class Problem(ctypes.Structure):
+    _fields_ = [("m", ctypes.c_int32), ("n", ctypes.c_int32), ("k", ctypes.c_int32),
+                ("dtype", ctypes.c_int32), ("epilogue", ctypes.c_int32),
+                ("reserved0", ctypes.c_int32),
+                ("stride_am", ctypes.c_int64), ("stride_ak", ctypes.c_int64),
+                ("stride_bk", ctypes.c_int64), ("stride_bn", ctypes.c_int64),
+                ("stride_cm", ctypes.c_int64), ("stride_cn", ctypes.c_int64)]
+
+
+class Config(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int32) for n in (
+        "tile_m", "tile_n", "tile_k", "stages", "acc_stages", "cta_group", "split_k", "group_m",
+        "tile_order", "kernel", "max_ctas", "reserved0")]
+
+
+class Resources(ctypes.Structure):
+    _fields_ = [("kernel", ctypes.c_int32), ("smem_bytes", ctypes.c_int32),
+                ("tmem_columns", ctypes.c_int32), ("grid", ctypes.c_int32),
+                ("tiles_m", ctypes.c_int32), ("tiles_n", ctypes.c_int32),
+                ("split_k", ctypes.c_int32), ("reserved0", ctypes.c_int32),
+                ("workspace_bytes", ctypes.c_int64)]
+
+
+EXPORTS = ("tnx_version", "tnx_last_error", "tnx_sm_count", "tnx_gemm_query", "tnx_gemm",
+           "tnx_glu", "tnx_read_status")
+
+
+def _load() -> ctypes.CDLL:
+    if not _LIB_PATH.exists():
+        raise ImportError(
+            f"{_LIB_PATH} is missing: build it with `python -m tritonix_b200.csrc.build` "
+            "(needs nvcc). tritonix_b200 has no CPU or PyTorch fallback.")
+    lib = ctypes.CDLL(str(_LIB_PATH))
+    lib.tnx_version.restype = ctypes.c_char_p
+    lib.tnx_last_error.restype = ctypes.c_char_p
+    lib.tnx_sm_count.restype = ctypes.c_int
+    lib.tnx_gemm_query.restype = ctypes.c_int
+    lib.tnx_gemm_query.argtypes = [ctypes.POINTER(Problem), ctypes.POINTER(Config),
+                                   ctypes.POINTER(Resources)]
+    lib.tnx_gemm.restype = ctypes.c_int
+    lib.tnx_gemm.argtypes = [ctypes.POINTER(Problem), ctypes.POINTER(Config), ctypes.c_void_p,
+                             ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t,
+                             ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+    lib.tnx_glu.restype = ctypes.c_int
+    lib.tnx_glu.argtypes = [ctypes.POINTER(Problem), ctypes.POINTER(Config), ctypes.c_int,
+                            ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                            ctypes.c_void_p, ctypes.c_void_p]
+    lib.tnx_read_status.restype = ctypes.c_int
+    lib.tnx_read_status.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32),
+                                    ctypes.c_void_p]
+    return lib
+
+
+lib = _load()
+
+
+def last_error() -> str:
+    return lib.tnx_last_error().decode()
+
+
+def raise_for(rc: int) -> None:
+    """Maps a TNX_* status to the exception the reference's callers expect."""
+    if rc == OK:
+        return
+    msg = last_error()
+    if rc == ERR_RESOURCES:
+        raise OutOfResources(msg)
+    if rc in (ERR_INVALID, ERR_NOT_BUILT):
+        raise ValueError(msg)  # the tuner skips ValueError (tritonix/autotune.py:130-133)
+    if rc == ERR_DEVICE:
+        raise DeviceStatusError(msg)
+    raise RuntimeError(msg)
+
+
+# Config keys: new names, with the reference's Triton names accepted as aliases
+# (block_m/block_n/block_k/num_stages, tritonix/ops/matmul.py:33-38).  num_warps is a Triton
+# launch option with no meaning here; it is accepted and ignored.
+_ALIASES = {"block_m": "tile_m", "block_n": "tile_n", "block_k": "tile_k", "num_stages": "stages"}
+_IGNORED = {"num_warps", "use_tf32", "activation", "num_ctas", "maxnreg"}
+_CONFIG_FIELDS = {n for n, _ in Config._fields_} - {"reserved0"}
+
+
+def make_config(cfg: dict | None) -> Config:
+    c = Config()
+    for key, value in (cfg or {}).items():
+        name = _ALIASES.get(key, key)
+        if name in _IGNORED or value is None:
+            continue
+        if name == "tile_order":
+            value = TILE_ORDERS[value] if isinstance(value, str) else int(value)
+        elif name == "kernel":
+            value = KERNELS[value] if isinstance(value, str) else int(value)
+        if name not in _CONFIG_FIELDS:
+            raise ValueError(f"unknown kernel configuration key {key!r}")
+        setattr(c, name, int(value))
+    return c
+
+
+def make_problem(m, n, k, dtype, strides, epilogue=EPI_NONE) -> Problem:
+    if dtype not in DTYPES:
+        raise ValueError(f"unsupported dtype {dtype}; expected float16, bfloat16 or float32")
+    sam, sak, sbk, sbn, scm, scn = (int(s) for s in strides)
+    return Problem(int(m), int(n), int(k), DTYPES[dtype], int(epilogue), 0,
+                   sam, sak, sbk, sbn, scm, scn)
+
+
+def query(problem: Problem, config: Config) -> Resources:
+    res = Resources()
+    raise_for(lib.tnx_gemm_query(ctypes.byref(problem), ctypes.byref(config), ctypes.byref(res)))
+    return res
+
+
+# ---- per-device scratch owned by the Python layer (the C ABI never allocates)
+_scratch_lock = threading.Lock()
+_status_words: dict[int, torch.Tensor] = {}
+_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def status_word(device: torch.device) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    with _scratch_lock:
+        w = _status_words.get(idx)
+        if w is None:
+            w = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+            _status_words[idx] = w
+        return w
+
+
+def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Zero-initialised split-K scratch, one per (device, stream), grown on demand.
+
+    The kernel leaves the counter region zero after every launch, so the buffer is cleared
+    only when it is (re)allocated.
+    """
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    key = (idx, torch.cuda.current_stream(idx).cuda_stream)
+    with _scratch_lock:
+        w = _workspaces.get(key)
+        if w is None or w.numel() < nbytes:
+            size = max(nbytes, 2 * w.numel() if w is not None else 0)
+            w = torch.zeros(size, dtype=torch.uint8, device=torch.device("cuda", idx))
+            _workspaces[key] = w
+        return w
+
+
+def check_status(device: torch.device | None = None) -> None:
+    """Synchronises the current stream and raises DeviceStatusError if a kernel gave up a wait."""
+    device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+    w = status_word(device)
+    code = ctypes.c_int32(0)
+    stream = torch.cuda.current_stream(w.device).cuda_stream
+    raise_for(lib.tnx_read_status(w.data_ptr(), ctypes.byref(code), stream))
+
+
+def launch(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, cfg: dict | None = None,
+           epilogue: int = EPI_NONE, tile_table: torch.Tensor | None = None) -> Resources:
+    """Enqueues C = epilogue(A.B) on torch's current stream.  a: M x K, b: K x N, c: M x N (or
+    M x N/2 for a GLU epilogue); any strides.  Returns the resources the launch used."""
+    if not (a.is_cuda and b.is_cuda and c.is_cuda):
+        raise RuntimeError("tritonix_b200 runs on CUDA tensors only (there is no CPU path)")
+    if a.dim() != 2 or b.dim() != 2 or c.dim() != 2:
+        raise ValueError("a, b and c must be 2-D")
+    if not (a.dtype == b.dtype == c.dtype):
+        raise ValueError(f"dtype mismatch: {a.dtype}, {b.dtype}, {c.dtype}")
+    if not (a.device == b.device == c.device):
+        raise ValueError("a, b and c must live on the same device")
+    m, k = a.shape
+    kb, n = b.shape
+    if kb != k:
+        raise ValueError(f"inner dimensions differ: a is {tuple(a.shape)}, b is {tuple(b.shape)}")
+    n_out = n // 2 if epilogue != EPI_NONE else n
+    if tuple(c.shape) != (m, n_out):
+        raise ValueError(f"output must be {(m, n_out)}, got {tuple(c.shape)}")
+    problem = make_problem(m, n, k, a.dtype, (*a.stride(), *b.stride(), *c.stride()), epilogue)
+    config = make_config(cfg)
+    with torch.cuda.device(a.device):
+        res = query(problem, config)
+        ws_ptr, ws_bytes = None, 0
+        if res.workspace_bytes > 0:
+            ws = workspace(a.device, int(res.workspace_bytes))
+            ws_ptr, ws_bytes = ws.data_ptr(), ws.numel()
+        table_ptr = None
+        if config.tile_order == ORDER_TABLE:
+            if tile_table is None or tile_table.dtype != torch.int32 or not tile_table.is_cuda:
+                raise ValueError("tile_order='hilbert'/'table' needs an int32 CUDA tile table")
+            if tile_table.numel() != res.tiles_m * res.tiles_n:
+                raise ValueError("tile table length does not match the tile grid")
+            table_ptr = tile_table.data_ptr()
+        stream = torch.cuda.current_stream(a.device).cuda_stream
+        rc = lib.tnx_gemm(ctypes.byref(problem), ctypes.byref(config), a.data_ptr(), b.data_ptr(),
+                          c.data_ptr(), ws_ptr, ws_bytes, table_ptr,
+                          status_word(a.device).data_ptr(), stream)
+    raise_for(rc)
+    return res

@@ -1,0 +1,34 @@
+// Declarations shared by the translation units of libtritonix_b200.so (not part of the ABI).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/tritonix_b200.h"
+
+namespace tnx {
+
+// Budgets of one B200 SM.
+constexpr int kMaxDynamicSmem = 232448;  // 227 KiB opt-in dynamic shared memory per CTA
+constexpr int kTmemColumns = 512;        // TMEM columns per SM (x 128 lanes x 32 bit)
+
+// Split-K scratch layout: [counters: kCounterBytes][fp32 partial tiles].
+constexpr int64_t kCounterBytes = 65536;
+constexpr int kMaxCounterTiles = static_cast<int>(kCounterBytes / 4);
+
+void set_error(const char* fmt, ...);
+
+// Fills defaults into *cfg, validates, computes resources.  Returns a TNX_* status.
+int umma_query(const tnx_problem& p, tnx_config* cfg, tnx_resources* out);
+int umma_launch(const tnx_problem& p, const tnx_config& cfg, const tnx_resources& res,
+                const void* a, const void* b, void* c, void* workspace, const int32_t* tile_table,
+                int32_t* status_word, cudaStream_t stream);
+
+// True when the operands can use the TMA/tcgen05 path (16-bit type, unit inner strides,
+// 16-byte aligned row pitches).  Pointer alignment is checked at launch.
+bool umma_eligible(const tnx_problem& p, const char** why);
+
+int strided_query(const tnx_problem& p, tnx_config* cfg, tnx_resources* out);
+int strided_launch(const tnx_problem& p, const void* a, const void* b, void* c,
+                   cudaStream_t stream);
+
+}  // namespace tnx

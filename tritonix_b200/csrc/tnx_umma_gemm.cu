@@ -1,0 +1,816 @@
+// Persistent, warp-specialised GEMM for sm_100a:
+//   TMA (cp.async.bulk.tensor) -> 128B-swizzled shared-memory ring -> tcgen05.mma with the fp32
+//   accumulator in TMEM -> tcgen05.ld epilogue (plain cast, fused GLU gate*up, or deterministic
+//   split-K fix-up) -> TMA store.
+//
+// It computes what the reference's Triton kernels compute, one 128 x TILE_N tile of C per work
+// unit: matmul_kernel (tritonix/ops/matmul.py:42-108), gemm_splitk_kernel (:147-202, with the
+// atomic_add of :202 replaced by an ordered fp32 reduction) and glu_kernel
+// (tritonix/ops/swiglu.py:24-110).  A is row-major M x K (K-major operand), B is row-major K x N
+// (an "MN-major" tcgen05 operand: no transpose pass is needed).
+//
+// Warp roles in a CTA of 192 threads:
+//   warp 0      TMA producer (one elected lane)
+//   warp 1      TMEM allocation + tcgen05.mma issue (one elected lane; leader CTA only in pair mode)
+//   warps 2..5  epilogue: warp w reads TMEM lanes [32*(w%4), 32*(w%4)+32)
+//
+// CTA_GROUP == 2 runs tcgen05 cta_group::2: a cluster of two CTAs owns a 256 x TILE_N tile, each
+// CTA loads its own 128 rows of A and its own half of the B columns (plain per-CTA TMA loads),
+// and the leader CTA issues M=256 MMAs that read both CTAs' shared memory.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <mutex>
+
+#include "tnx_internal.h"
+#include "tnx_ptx.cuh"
+
+namespace tnx {
+
+namespace {
+
+constexpr int kRowsPerCta = 128;  // TMEM lanes = rows of C owned by one CTA
+constexpr int kThreads = 192;
+constexpr int kEpiThreads = 128;
+constexpr int kEpiBarrier = 1;               // named barrier id of the epilogue warps
+constexpr int kAtomBytes = 128;              // swizzle span: 64 16-bit elements
+constexpr int kAtomElems = 64;
+constexpr int kStagingBytes = kRowsPerCta * kAtomBytes;  // 128 rows x 128 B of output
+constexpr int kMaxStages = 14;
+constexpr int kCtrlBytes = 512;
+constexpr int kAlignSlack = 1024;
+
+// Status-word codes written when a bounded wait expires.
+constexpr int kAbortProducer = 0x101;
+constexpr int kAbortMma = 0x102;
+constexpr int kAbortEpilogue = 0x103;
+
+struct UmmaParams {
+  int m, n, k;          // n counts columns of B (2F for GLU)
+  int n_out;            // columns of C
+  int tiles_m, tiles_n; // tiles_m counts (128*CTA_GROUP)-row tiles
+  int num_kb;           // K blocks of tile_k in total
+  int kb_per_slice;     // K blocks per split-K slice
+  int split_k;
+  int tile_k;
+  int stages;
+  int acc_stages;
+  int group_m;
+  int tile_order;
+  int epilogue;
+  const int32_t* tile_table;
+  float* partials;      // split-K: fp32 partial tiles
+  int* counters;        // split-K: one arrival counter per 128-row output tile
+  int* status;
+  unsigned long long timeout_ns;
+};
+
+// Control block at the end of dynamic shared memory.
+struct Ctrl {
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort;
+  int is_last;
+};
+static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block too large");
+
+__device__ __forceinline__ void tile_coords(const UmmaParams& p, int t, int& tm, int& tn) {
+  if (p.tile_order == TNX_ORDER_TABLE) {
+    const int v = __ldg(p.tile_table + t);
+    tm = v >> 16;
+    tn = v & 0xffff;
+    return;
+  }
+  // Bands of group_m tile rows, walked column by column (tl.swizzle2d's mapping, used at
+  // tritonix/ops/matmul.py:70).
+  const int band_tiles = p.group_m * p.tiles_n;
+  const int band = t / band_tiles;
+  const int first_row = band * p.group_m;
+  const int rows = min(p.tiles_m - first_row, p.group_m);
+  const int r = t - band * band_tiles;
+  const int col = r / rows;
+  int row_in_band = r - col * rows;
+  tn = col;
+  if (p.tile_order == TNX_ORDER_SERPENTINE) {
+    // Boustrophedon variant (the intent of swizzle2d_rows, tritonix/ops/matmul.py:9-27):
+    // odd columns run bottom-up, odd bands run right-to-left.
+    if (col & 1) row_in_band = rows - 1 - row_in_band;
+    if (band & 1) tn = p.tiles_n - 1 - col;
+  }
+  tm = first_row + row_in_band;
+}
+
+__device__ __forceinline__ float gate_act(float g, int epilogue) {
+  if (epilogue == TNX_EPI_GLU_LINEAR) return g;
+  const float s = __fdividef(1.0f, 1.0f + __expf(-g));
+  return epilogue == TNX_EPI_GLU_SILU ? g * s : s;
+}
+
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  if (BF16) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  } else {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+}
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c,
+                                             uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c),
+               "r"(d)
+               : "memory");
+}
+
+template <int TILE_N, int CTA_GROUP, bool GLU, bool BF16>
+__global__ void __launch_bounds__(kThreads, 1)
+umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_c, const UmmaParams p) {
+  constexpr int LOAD_N = TILE_N / CTA_GROUP;          // B columns this CTA loads per stage
+  constexpr int ACC_PER_CHUNK = GLU ? 128 : 64;       // accumulator columns per 128-byte output row
+  constexpr int OUT_PER_TILE = GLU ? TILE_N / 2 : TILE_N;
+  static_assert(LOAD_N % kAtomElems == 0, "each CTA must load whole 64-column swizzle atoms of B");
+  static_assert(TILE_N % ACC_PER_CHUNK == 0, "tile_n must cover whole output chunks");
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  const uint32_t base_addr = (raw_addr + 1023u) & ~1023u;  // 128B swizzle needs 1024-byte alignment
+  uint8_t* base_ptr = smem_raw + (base_addr - raw_addr);
+
+  const int a_stage_bytes = kRowsPerCta * p.tile_k * 2;
+  const int b_stage_bytes = LOAD_N * p.tile_k * 2;
+  const uint32_t smem_a = base_addr;
+  const uint32_t smem_b = smem_a + p.stages * a_stage_bytes;
+  const uint32_t smem_out = smem_b + p.stages * b_stage_bytes;  // 2 staging buffers
+  Ctrl* ctrl = reinterpret_cast<Ctrl*>(base_ptr + (smem_out - base_addr) + 2 * kStagingBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = CTA_GROUP == 2 ? ptx::cluster_ctarank() : 0u;
+  const bool leader = cta_rank == 0;
+  const int cluster_id = blockIdx.x / CTA_GROUP;
+  const int num_clusters = gridDim.x / CTA_GROUP;
+  const int total_units = p.tiles_m * p.tiles_n * p.split_k;
+  const uint32_t tmem_cols_needed = p.acc_stages * TILE_N;
+  uint32_t tmem_alloc_cols = 32;
+  while (tmem_alloc_cols < tmem_cols_needed) tmem_alloc_cols <<= 1;
+
+  volatile int* abort_flag = &ctrl->abort;
+
+  // ------------------------------------------------------------------ set-up
+  if (threadIdx.x == 0) {
+    ptx::prefetch_tensormap(&tmap_a);
+    ptx::prefetch_tensormap(&tmap_b);
+    ptx::prefetch_tensormap(&tmap_c);
+    for (int s = 0; s < p.stages; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&ctrl->full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&ctrl->empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(ptx::smem_u32(&ctrl->tmem_full[a]), 1);
+      ptx::mbar_init(ptx::smem_u32(&ctrl->tmem_empty[a]), 4 * CTA_GROUP);  // one arrive per epilogue warp
+    }
+    ctrl->abort = 0;
+    ctrl->is_last = 0;
+    ptx::fence_mbar_init();
+  }
+  __syncwarp();
+  if (CTA_GROUP == 2) {  // the peer's barriers must exist before anything signals them
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc<CTA_GROUP>(ptx::smem_u32(&ctrl->tmem_base), tmem_alloc_cols);
+    ptx::tmem_relinquish<CTA_GROUP>();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = ctrl->tmem_base;
+
+  // ------------------------------------------------------------------ roles
+  if (warp == 0) {
+    // ===== TMA producer =====
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      const uint32_t stage_tx = static_cast<uint32_t>(a_stage_bytes + b_stage_bytes) * CTA_GROUP;
+      bool ok = true;
+      for (int u = cluster_id; u < total_units && ok; u += num_clusters) {
+        const int t = u / p.split_k;
+        const int slice = u - t * p.split_k;
+        int tm, tn;
+        tile_coords(p, t, tm, tn);
+        const int row0 = (tm * CTA_GROUP + static_cast<int>(cta_rank)) * kRowsPerCta;
+        const int col0 = tn * TILE_N + static_cast<int>(cta_rank) * LOAD_N;
+        const int kb0 = slice * p.kb_per_slice;
+        const int kb1 = min(kb0 + p.kb_per_slice, p.num_kb);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          const uint32_t empty_bar = ptx::smem_u32(&ctrl->empty[stage]);
+          if (!ptx::mbar_wait(empty_bar, phase ^ 1u, abort_flag, p.timeout_ns)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full_bar = ptx::smem_u32(&ctrl->full[stage]);
+          const uint32_t a_dst = smem_a + stage * a_stage_bytes;
+          const uint32_t b_dst = smem_b + stage * b_stage_bytes;
+          const int k0 = kb * p.tile_k;
+          if (CTA_GROUP == 1) {
+            ptx::mbar_arrive_expect_tx(full_bar, stage_tx);
+            for (int ka = 0; ka < p.tile_k / kAtomElems; ++ka)
+              ptx::tma_load_2d(a_dst + ka * (kRowsPerCta * kAtomBytes), &tmap_a,
+                               k0 + ka * kAtomElems, row0, full_bar);
+            for (int na = 0; na < LOAD_N / kAtomElems; ++na)
+              ptx::tma_load_2d(b_dst + na * (p.tile_k * kAtomBytes), &tmap_b,
+                               col0 + na * kAtomElems, k0, full_bar);
+          } else {
+            // Both CTAs' loads complete on the leader's barrier; the leader announces the bytes.
+            const uint32_t leader_bar = ptx::mapa(full_bar, 0);
+            if (leader) ptx::mbar_arrive_expect_tx(full_bar, stage_tx);
+            for (int ka = 0; ka < p.tile_k / kAtomElems; ++ka)
+              ptx::tma_load_2d_pair(a_dst + ka * (kRowsPerCta * kAtomBytes), &tmap_a,
+                                    k0 + ka * kAtomElems, row0, leader_bar);
+            for (int na = 0; na < LOAD_N / kAtomElems; ++na)
+              ptx::tma_load_2d_pair(b_dst + na * (p.tile_k * kAtomBytes), &tmap_b,
+                                    col0 + na * kAtomElems, k0, leader_bar);
+          }
+          if (++stage == p.stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok && p.status != nullptr) atomicCAS(p.status, 0, kAbortProducer);
+    }
+  } else if (warp == 1) {
+    // ===== MMA issuer =====
+    if (leader && lane == 0) {
+      // Instruction descriptor: fp32 accumulate, A K-major, B MN-major, M x N = (128*CTA_GROUP) x TILE_N.
+      const uint32_t fmt = BF16 ? 1u : 0u;
+      const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (0u << 15) | (1u << 16) |
+                             (static_cast<uint32_t>(TILE_N >> 3) << 17) |
+                             (static_cast<uint32_t>((kRowsPerCta * CTA_GROUP) >> 4) << 24);
+      // A: rows of 128 B, 8-row groups 1024 B apart.  B: 64-column atoms of tile_k rows x 128 B;
+      // LBO = bytes between atoms along N, SBO = bytes between 8-row groups along K.
+      const uint64_t a_desc_hi = ptx::make_smem_desc(0, 0, 1024);
+      const uint64_t b_desc_hi = ptx::make_smem_desc(0, p.tile_k * kAtomBytes, 1024);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int u = cluster_id; u < total_units && ok; u += num_clusters) {
+        const int t = u / p.split_k;
+        const int slice = u - t * p.split_k;
+        const int kb0 = slice * p.kb_per_slice;
+        const int kb1 = min(kb0 + p.kb_per_slice, p.num_kb);
+        const uint32_t te_bar = ptx::smem_u32(&ctrl->tmem_empty[acc]);
+        if (!ptx::mbar_wait<CTA_GROUP == 2>(te_bar, acc_phase ^ 1u, abort_flag, p.timeout_ns)) {
+          ok = false;
+          break;
+        }
+        ptx::tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * TILE_N;
+        uint32_t accumulate = 0;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          const uint32_t full_bar = ptx::smem_u32(&ctrl->full[stage]);
+          if (!ptx::mbar_wait(full_bar, phase, abort_flag, p.timeout_ns)) {
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+          const uint32_t a_src = smem_a + stage * a_stage_bytes;
+          const uint32_t b_src = smem_b + stage * b_stage_bytes;
+          for (int k16 = 0; k16 < p.tile_k / 16; ++k16) {
+            const uint32_t a_addr = a_src + (k16 >> 2) * (kRowsPerCta * kAtomBytes) + (k16 & 3) * 32;
+            const uint32_t b_addr = b_src + k16 * (16 * kAtomBytes);
+            ptx::umma_f16<CTA_GROUP>(d_tmem, a_desc_hi | ((a_addr >> 4) & 0x3fffu),
+                                     b_desc_hi | ((b_addr >> 4) & 0x3fffu), idesc, accumulate);
+            accumulate = 1;
+          }
+          // Frees this ring slot (in both CTAs of a pair) once the MMAs above have read it.
+          if (CTA_GROUP == 1)
+            ptx::umma_commit(ptx::smem_u32(&ctrl->empty[stage]));
+          else
+            ptx::umma_commit_pair(ptx::smem_u32(&ctrl->empty[stage]), 0x3);
+          if (++stage == p.stages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        if (CTA_GROUP == 1)
+          ptx::umma_commit(ptx::smem_u32(&ctrl->tmem_full[acc]));
+        else
+          ptx::umma_commit_pair(ptx::smem_u32(&ctrl->tmem_full[acc]), 0x3);
+        if (++acc == p.acc_stages) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
+      }
+      if (!ok && p.status != nullptr) atomicCAS(p.status, 0, kAbortMma);
+    }
+  } else {
+    // ===== epilogue =====
+    const int quarter = warp & 3;                 // TMEM lanes this warp may touch
+    const int row_in_tile = quarter * 32 + lane;  // row of the CTA's 128-row tile held by this thread
+    const int epi_tid = threadIdx.x - 64;
+    const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
+    const uint32_t stage_row = static_cast<uint32_t>(row_in_tile) * kAtomBytes;
+    const uint32_t sw = static_cast<uint32_t>(row_in_tile & 7);
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    uint32_t stores = 0;  // staging buffers used so far (selects the buffer)
+    bool ok = true;
+    for (int u = cluster_id; u < total_units && ok; u += num_clusters) {
+      const int t = u / p.split_k;
+      const int slice = u - t * p.split_k;
+      int tm, tn;
+      tile_coords(p, t, tm, tn);
+      const int row_tile = tm * CTA_GROUP + static_cast<int>(cta_rank);  // 128-row tile index
+      const int row0 = row_tile * kRowsPerCta;
+      const int acc_col0 = tn * TILE_N;        // first B column of the tile
+      const int out_col0 = tn * OUT_PER_TILE;  // first C column of the tile
+      const int kb0 = slice * p.kb_per_slice;
+      const bool has_k = kb0 < p.num_kb;
+
+      const uint32_t tf_bar = ptx::smem_u32(&ctrl->tmem_full[acc]);
+      bool got = !has_k || ptx::mbar_wait(tf_bar, acc_phase, abort_flag, p.timeout_ns);
+      // All 128 epilogue threads continue or give up together (they share named barriers below).
+      if (!ptx::named_barrier_all(kEpiBarrier, kEpiThreads, got)) {
+        ok = false;
+        break;
+      }
+      ptx::tc_fence_after_sync();
+      const uint32_t t_acc = tmem_base + lane_sel + acc * TILE_N;
+
+      bool reduce_from_partials = false;
+      if (p.split_k > 1) {
+        // ---- split-K: park the fp32 partial, the last slice to arrive sums all of them ----
+        const size_t unit_slot = static_cast<size_t>(row_tile * p.tiles_n + tn) * p.split_k + slice;
+        float* part = p.partials + unit_slot * (static_cast<size_t>(TILE_N) * kRowsPerCta);
+        const bool row_ok = row0 + row_in_tile < p.m;
+        for (int c = 0; c < TILE_N / 32; ++c) {
+          if (acc_col0 + c * 32 >= p.n) break;
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(t_acc + c * 32, r);
+          ptx::tmem_ld_wait();
+          if (row_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              __stcg(part + (c * 32 + j) * kRowsPerCta + row_in_tile, __uint_as_float(r[j]));
+          }
+        }
+        // TMEM buffer can be refilled now.
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          const uint32_t te = ptx::smem_u32(&ctrl->tmem_empty[acc]);
+          if (CTA_GROUP == 1 || leader)
+            ptx::mbar_arrive(te);
+          else
+            ptx::mbar_arrive_cluster(ptx::mapa(te, 0));
+        }
+        __threadfence();
+        ptx::named_barrier_sync(kEpiBarrier, kEpiThreads);
+        if (epi_tid == 0) {
+          int* counter = p.counters + (row_tile * p.tiles_n + tn);
+          const int seen = atomicAdd(counter, 1);
+          const int last = seen == p.split_k - 1;
+          if (last) *counter = 0;  // leaves the counters clean for the next launch
+          ctrl->is_last = last;
+          __threadfence();
+        }
+        ptx::named_barrier_sync(kEpiBarrier, kEpiThreads);
+        reduce_from_partials = ctrl->is_last != 0;
+        if (!reduce_from_partials) {
+          if (++acc == p.acc_stages) {
+            acc = 0;
+            acc_phase ^= 1u;
+          }
+          continue;
+        }
+        __threadfence();
+      }
+
+      const float* part0 =
+          p.split_k > 1 ? p.partials + static_cast<size_t>(row_tile * p.tiles_n + tn) * p.split_k *
+                                           (static_cast<size_t>(TILE_N) * kRowsPerCta)
+                        : nullptr;
+
+      // ---- write the tile: chunks of 128 bytes of output per row, through swizzled staging ----
+      for (int chunk = 0; chunk < TILE_N / ACC_PER_CHUNK; ++chunk) {
+        const int out_col = out_col0 + chunk * kAtomElems;
+        if (out_col >= p.n_out) break;
+        const uint32_t buf = smem_out + (stores & 1u) * kStagingBytes;
+        // The TMA store issued two chunks ago must have finished reading this buffer.
+        if (epi_tid == 0) ptx::tma_store_wait_read<1>();
+        ptx::named_barrier_sync(kEpiBarrier, kEpiThreads);
+#pragma unroll
+        for (int sub = 0; sub < ACC_PER_CHUNK / 32; ++sub) {
+          const int col = chunk * ACC_PER_CHUNK + sub * 32;
+          float v[32];
+          if (!reduce_from_partials) {
+            uint32_t r[32];
+            ptx::tmem_ld_32x32(t_acc + col, r);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = 0.0f;
+            if (acc_col0 + col < p.n && row0 + row_in_tile < p.m) {
+              for (int s = 0; s < p.split_k; ++s) {  // fixed order => bit-reproducible sum
+                const float* src = part0 + static_cast<size_t>(s) * (TILE_N * kRowsPerCta) +
+                                   col * kRowsPerCta + row_in_tile;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] += __ldcg(src + j * kRowsPerCta);
+              }
+            }
+          }
+          if (GLU) {
+            // Columns come interleaved (gate_j, up_j): adjacent registers form one output.
+            uint32_t o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float z0 = gate_act(v[4 * j], p.epilogue) * v[4 * j + 1];
+              const float z1 = gate_act(v[4 * j + 2], p.epilogue) * v[4 * j + 3];
+              o[j] = pack2<BF16>(z0, z1);
+            }
+#pragma unroll
+            for (int piece = 0; piece < 2; ++piece) {
+              const uint32_t pos = static_cast<uint32_t>(sub * 2 + piece) ^ sw;
+              st_shared_v4(buf + stage_row + pos * 16, o[piece * 4], o[piece * 4 + 1],
+                           o[piece * 4 + 2], o[piece * 4 + 3]);
+            }
+          } else {
+            uint32_t o[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) o[j] = pack2<BF16>(v[2 * j], v[2 * j + 1]);
+#pragma unroll
+            for (int piece = 0; piece < 4; ++piece) {
+              const uint32_t pos = static_cast<uint32_t>(sub * 4 + piece) ^ sw;
+              st_shared_v4(buf + stage_row + pos * 16, o[piece * 4], o[piece * 4 + 1],
+                           o[piece * 4 + 2], o[piece * 4 + 3]);
+            }
+          }
+        }
+        ptx::fence_proxy_async_smem();
+        ptx::named_barrier_sync(kEpiBarrier, kEpiThreads);
+        if (epi_tid == 0) {
+          ptx::tma_store_2d(&tmap_c, out_col, row0, buf);
+          ptx::tma_store_commit();
+        }
+        ++stores;
+      }
+
+      if (!reduce_from_partials) {
+        // All tcgen05.ld of this accumulator are complete: hand the TMEM buffer back.
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          const uint32_t te = ptx::smem_u32(&ctrl->tmem_empty[acc]);
+          if (CTA_GROUP == 1 || leader)
+            ptx::mbar_arrive(te);
+          else
+            ptx::mbar_arrive_cluster(ptx::mapa(te, 0));
+        }
+      }
+      if (++acc == p.acc_stages) {
+        acc = 0;
+        acc_phase ^= 1u;
+      }
+    }
+    if (epi_tid == 0) ptx::tma_store_wait_all<0>();
+    if (!ok && lane == 0 && p.status != nullptr) atomicCAS(p.status, 0, kAbortEpilogue);
+  }
+
+  // ------------------------------------------------------------------ teardown
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (ctrl->abort != 0) {
+    // A wait gave up: let copies and MMAs that are still in flight drain before the shared
+    // memory and TMEM they target are released (bounded: about a millisecond).
+    const uint64_t t0 = ptx::globaltimer_ns();
+    while (ptx::globaltimer_ns() - t0 < 1000000ull) __nanosleep(1000);
+  }
+  __syncwarp();
+  if (CTA_GROUP == 2) {  // the peer may still signal barriers in, or read, this CTA's shared memory
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc<CTA_GROUP>(tmem_base, tmem_alloc_cols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e =
+        cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres);
+    if (e == cudaSuccess && qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+// 2-D row-major tensor of 16-bit elements: `cols` contiguous elements per row, `rows` rows,
+// `pitch_elems` elements between rows; box = box_cols x box_rows with the 128-byte swizzle.
+int make_tmap(CUtensorMap* out, const void* ptr, int dtype, int64_t cols, int64_t rows,
+              int64_t pitch_elems, int box_cols, int box_rows, bool is_operand) {
+  EncodeTiledFn encode = get_encode_fn();
+  if (encode == nullptr) {
+    set_error("cuTensorMapEncodeTiled is not available from the CUDA driver");
+    return TNX_ERR_CUDA;
+  }
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch_elems) * 2};
+  const cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt =
+      dtype == TNX_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = encode(out, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                      is_operand ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with CUresult %d (ptr %p, %lld x %lld, pitch %lld)",
+              static_cast<int>(r), ptr, static_cast<long long>(rows), static_cast<long long>(cols),
+              static_cast<long long>(pitch_elems));
+    return TNX_ERR_CUDA;
+  }
+  return TNX_OK;
+}
+
+using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const UmmaParams);
+
+template <int TILE_N, int CTA_GROUP, bool GLU>
+KernelFn pick_dtype(int dtype) {
+  return dtype == TNX_BF16 ? umma_gemm_kernel<TILE_N, CTA_GROUP, GLU, true>
+                           : umma_gemm_kernel<TILE_N, CTA_GROUP, GLU, false>;
+}
+
+// The set of compiled kernels.  nullptr = not built.
+KernelFn pick_kernel(int tile_n, int cta_group, bool glu, int dtype) {
+  if (cta_group == 1) {
+    if (!glu) {
+      if (tile_n == 64) return pick_dtype<64, 1, false>(dtype);
+      if (tile_n == 128) return pick_dtype<128, 1, false>(dtype);
+      if (tile_n == 256) return pick_dtype<256, 1, false>(dtype);
+    } else {
+      if (tile_n == 128) return pick_dtype<128, 1, true>(dtype);
+      if (tile_n == 256) return pick_dtype<256, 1, true>(dtype);
+    }
+  } else if (cta_group == 2) {
+    if (!glu) {
+      if (tile_n == 128) return pick_dtype<128, 2, false>(dtype);
+      if (tile_n == 256) return pick_dtype<256, 2, false>(dtype);
+    } else {
+      if (tile_n == 128) return pick_dtype<128, 2, true>(dtype);
+      if (tile_n == 256) return pick_dtype<256, 2, true>(dtype);
+    }
+  }
+  return nullptr;
+}
+
+int device_sm_count() {
+  static int sms = -1;
+  if (sms < 0) {
+    int dev = 0, v = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess &&
+        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && v > 0)
+      sms = v;
+    else
+      return 148;  // B200; used only for sizing when no device is visible (resource queries)
+  }
+  return sms;
+}
+
+unsigned long long wait_limit_ns() {
+  static unsigned long long v = 0;
+  if (v == 0) {
+    const char* e = getenv("TNX_WAIT_LIMIT_MS");
+    long ms = e ? atol(e) : 0;
+    if (ms <= 0) ms = 2000;
+    v = static_cast<unsigned long long>(ms) * 1000000ull;
+  }
+  return v;
+}
+
+inline int cdiv(int a, int b) { return (a + b - 1) / b; }
+
+}  // namespace
+
+bool umma_eligible(const tnx_problem& p, const char** why) {
+  const char* w = nullptr;
+  if (p.dtype != TNX_F16 && p.dtype != TNX_BF16)
+    w = "tcgen05 path takes fp16 or bf16 operands";
+  else if (p.stride_ak != 1 || p.stride_bn != 1 || p.stride_cn != 1)
+    w = "tcgen05 path needs unit inner strides (row-major A, B and C)";
+  else if ((p.stride_am % 8) != 0 || (p.stride_bk % 8) != 0 || (p.stride_cm % 8) != 0)
+    w = "tcgen05 path needs row pitches that are multiples of 16 bytes";
+  else if (p.k < 1 || p.m < 1 || p.n < 1)
+    w = "empty problem";
+  else if (p.stride_am < p.k || p.stride_bk < p.n)
+    w = "row pitch smaller than the row length";
+  if (why) *why = w;
+  return w == nullptr;
+}
+
+int umma_query(const tnx_problem& p, tnx_config* cfg, tnx_resources* out) {
+  const bool glu = p.epilogue != TNX_EPI_NONE;
+  if (cfg->cta_group == 0) cfg->cta_group = 1;
+  if (cfg->tile_m == 0) cfg->tile_m = kRowsPerCta * cfg->cta_group;
+  if (cfg->tile_n == 0) cfg->tile_n = (p.n >= 256) ? 256 : (p.n > 64 || glu ? 128 : 64);
+  if (cfg->tile_k == 0) cfg->tile_k = 64;
+  if (cfg->acc_stages == 0) cfg->acc_stages = 2;
+  if (cfg->split_k == 0) cfg->split_k = 1;
+  if (cfg->group_m == 0) cfg->group_m = 8;
+
+  if (cfg->cta_group != 1 && cfg->cta_group != 2) {
+    set_error("cta_group must be 1 or 2, got %d", cfg->cta_group);
+    return TNX_ERR_INVALID;
+  }
+  if (cfg->tile_m != kRowsPerCta * cfg->cta_group) {
+    set_error("tile_m=%d is not built: cta_group=%d tiles have %d rows", cfg->tile_m,
+              cfg->cta_group, kRowsPerCta * cfg->cta_group);
+    return TNX_ERR_NOT_BUILT;
+  }
+  if (cfg->tile_k != 64 && cfg->tile_k != 128) {
+    set_error("tile_k=%d is not built (64 or 128)", cfg->tile_k);
+    return TNX_ERR_NOT_BUILT;
+  }
+  if (cfg->acc_stages < 1 || cfg->acc_stages > 2 || cfg->split_k < 1 || cfg->group_m < 1 ||
+      cfg->tile_order < 0 || cfg->tile_order > TNX_ORDER_TABLE) {
+    set_error("invalid acc_stages/split_k/group_m/tile_order (%d/%d/%d/%d)", cfg->acc_stages,
+              cfg->split_k, cfg->group_m, cfg->tile_order);
+    return TNX_ERR_INVALID;
+  }
+  if (pick_kernel(cfg->tile_n, cfg->cta_group, glu, p.dtype) == nullptr) {
+    set_error("no kernel built for tile_n=%d cta_group=%d%s", cfg->tile_n, cfg->cta_group,
+              glu ? " with a GLU epilogue" : "");
+    return TNX_ERR_NOT_BUILT;
+  }
+  if (glu && (p.n % 2) != 0) {
+    set_error("GLU epilogue needs an even number of interleaved columns, got n=%d", p.n);
+    return TNX_ERR_INVALID;
+  }
+
+  const int load_n = cfg->tile_n / cfg->cta_group;
+  const int stage_bytes = (kRowsPerCta + load_n) * cfg->tile_k * 2;
+  const int fixed = 2 * kStagingBytes + kCtrlBytes + kAlignSlack;
+  if (cfg->stages == 0) {
+    int s = (kMaxDynamicSmem - fixed) / stage_bytes;
+    cfg->stages = s > 8 ? 8 : s;
+  }
+  if (cfg->stages < 2 || cfg->stages > kMaxStages) {
+    set_error("stages must be in [2, %d], got %d", kMaxStages, cfg->stages);
+    return TNX_ERR_INVALID;
+  }
+  const long long smem = static_cast<long long>(cfg->stages) * stage_bytes + fixed;
+  int tmem = 32;
+  while (tmem < cfg->acc_stages * cfg->tile_n) tmem <<= 1;
+
+  const int tile_rows = kRowsPerCta * cfg->cta_group;
+  const int tiles_m = cdiv(p.m, tile_rows);
+  const int tiles_n = cdiv(p.n, cfg->tile_n);
+  const int num_kb = cdiv(p.k, cfg->tile_k);
+  int split = cfg->split_k > num_kb ? num_kb : cfg->split_k;
+  const int kb_per = cdiv(num_kb, split);
+  split = cdiv(num_kb, kb_per);  // no empty slice
+
+  out->kernel = TNX_KERNEL_TCGEN05;
+  out->smem_bytes = static_cast<int32_t>(smem > 0x7fffffff ? 0x7fffffff : smem);
+  out->tmem_columns = tmem;
+  out->tiles_m = tiles_m;
+  out->tiles_n = tiles_n;
+  out->split_k = split;
+  out->workspace_bytes =
+      split > 1 ? kCounterBytes + static_cast<int64_t>(tiles_m) * cfg->cta_group * tiles_n * split *
+                                      cfg->tile_n * kRowsPerCta * 4
+                : 0;
+  const long long units = static_cast<long long>(tiles_m) * tiles_n * split;
+  int max_clusters = device_sm_count() / cfg->cta_group;
+  if (cfg->max_ctas > 0 && cfg->max_ctas / cfg->cta_group < max_clusters)
+    max_clusters = cfg->max_ctas / cfg->cta_group;
+  if (max_clusters < 1) max_clusters = 1;
+  out->grid = static_cast<int32_t>((units < max_clusters ? units : max_clusters) * cfg->cta_group);
+
+  if (smem > kMaxDynamicSmem) {
+    set_error("shared memory budget exceeded: %lld B needed (%d stages x %d B + %d B), %d B per SM",
+              smem, cfg->stages, stage_bytes, fixed, kMaxDynamicSmem);
+    return TNX_ERR_RESOURCES;
+  }
+  if (tmem > kTmemColumns) {
+    set_error("TMEM budget exceeded: %d accumulator buffers x %d columns > %d", cfg->acc_stages,
+              cfg->tile_n, kTmemColumns);
+    return TNX_ERR_RESOURCES;
+  }
+  if (tiles_m > 0xffff || tiles_n > 0xffff) {
+    set_error("problem has too many tiles (%d x %d)", tiles_m, tiles_n);
+    return TNX_ERR_INVALID;
+  }
+  if (split > 1 && static_cast<long long>(tiles_m) * cfg->cta_group * tiles_n > kMaxCounterTiles) {
+    set_error("split-K supports at most %d output tiles, problem has %lld", kMaxCounterTiles,
+              static_cast<long long>(tiles_m) * cfg->cta_group * tiles_n);
+    return TNX_ERR_INVALID;
+  }
+  return TNX_OK;
+}
+
+int umma_launch(const tnx_problem& p, const tnx_config& cfg, const tnx_resources& res,
+                const void* a, const void* b, void* c, void* workspace, const int32_t* tile_table,
+                int32_t* status_word, cudaStream_t stream) {
+  const bool glu = p.epilogue != TNX_EPI_NONE;
+  if ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) |
+       reinterpret_cast<uintptr_t>(c)) & 15u) {
+    set_error("tcgen05 path needs 16-byte aligned A, B and C base addresses");
+    return TNX_ERR_INVALID;
+  }
+  KernelFn fn = pick_kernel(cfg.tile_n, cfg.cta_group, glu, p.dtype);
+  if (fn == nullptr) return TNX_ERR_NOT_BUILT;
+
+  const int n_out = glu ? p.n / 2 : p.n;
+  CUtensorMap ta, tb, tc;
+  int rc = make_tmap(&ta, a, p.dtype, p.k, p.m, p.stride_am, kAtomElems, kRowsPerCta, true);
+  if (rc != TNX_OK) return rc;
+  rc = make_tmap(&tb, b, p.dtype, p.n, p.k, p.stride_bk, kAtomElems, cfg.tile_k, true);
+  if (rc != TNX_OK) return rc;
+  rc = make_tmap(&tc, c, p.dtype, n_out, p.m, p.stride_cm, kAtomElems, kRowsPerCta, false);
+  if (rc != TNX_OK) return rc;
+
+  UmmaParams kp;
+  kp.m = p.m;
+  kp.n = p.n;
+  kp.k = p.k;
+  kp.n_out = n_out;
+  kp.tiles_m = res.tiles_m;
+  kp.tiles_n = res.tiles_n;
+  kp.num_kb = cdiv(p.k, cfg.tile_k);
+  kp.split_k = res.split_k;
+  kp.kb_per_slice = cdiv(kp.num_kb, res.split_k);
+  kp.tile_k = cfg.tile_k;
+  kp.stages = cfg.stages;
+  kp.acc_stages = cfg.acc_stages;
+  kp.group_m = cfg.group_m;
+  kp.tile_order = cfg.tile_order;
+  kp.epilogue = p.epilogue;
+  kp.tile_table = tile_table;
+  kp.counters = reinterpret_cast<int*>(workspace);
+  kp.partials = workspace ? reinterpret_cast<float*>(static_cast<char*>(workspace) + kCounterBytes)
+                          : nullptr;
+  kp.status = status_word;
+  kp.timeout_ns = wait_limit_ns();
+
+  cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn),
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, res.smem_bytes);
+  if (e != cudaSuccess) {
+    set_error("cudaFuncSetAttribute(%d B dynamic smem): %s", res.smem_bytes, cudaGetErrorString(e));
+    (void)cudaGetLastError();
+    return TNX_ERR_CUDA;
+  }
+
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = dim3(res.grid, 1, 1);
+  lc.blockDim = dim3(kThreads, 1, 1);
+  lc.dynamicSmemBytes = res.smem_bytes;
+  lc.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cfg.cta_group;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  lc.attrs = attr;
+  lc.numAttrs = 1;
+  e = cudaLaunchKernelEx(&lc, fn, ta, tb, tc, kp);
+  if (e != cudaSuccess) {
+    set_error("kernel launch failed: %s", cudaGetErrorString(e));
+    (void)cudaGetLastError();
+    return TNX_ERR_CUDA;
+  }
+  return TNX_OK;
+}
+
+}  // namespace tnx
