@@ -1,0 +1,202 @@
+"""The reference-facing Python surface on a GPU: matmul / matmul_splitk / glu entry points,
+kernel handles with Triton's launch syntax, TunableKernel.tune on the real kernels, the
+single-backend dispatcher, the torch custom ops, and the device status word.
+The first three tests follow the reference's tests/test_matmul.py:9-52."""
+import pytest
+import torch
+
+import tritonix_b200 as tnx
+from oracle import contraction as O
+from tests.gpu_util import DEV, assert_close, seeded
+from tritonix_b200 import _cabi
+
+pytestmark = pytest.mark.gpu
+f16, bf16, f32 = torch.float16, torch.bfloat16, torch.float32
+
+
+@pytest.fixture(autouse=True)
+def quick_tuning(monkeypatch):
+    """Keep first-call tuning short: a handful of configurations, short timing budgets."""
+    real = tnx.TunableKernel.tune
+
+    def tune(self, launcher, **kw):
+        kw.setdefault("max_configs", 6)
+        kw.update(warmup=1, rep=3)
+        return real(self, launcher, **kw)
+    monkeypatch.setattr(tnx.TunableKernel, "tune", tune)
+    mm = __import__("sys").modules["tritonix_b200.ops.matmul"]
+    mm._matmul_cfg.clear()
+    mm._splitk_cfg.clear()
+    yield
+
+
+@pytest.mark.parametrize("M,N,K", [(512, 512, 512), (1024, 2048, 512), (2048, 2048, 2048)])
+def test_matmul_correctness(M, N, K):
+    a = torch.randn(M, K, device=DEV, dtype=f16)
+    b = torch.randn(K, N, device=DEV, dtype=f16)
+    out = tnx.triton_matmul(a, b)
+    tnx.check_status()
+    ref = torch.matmul(a, b)
+    assert torch.allclose(ref, out, atol=1.0, rtol=1e-2)          # the reference's own bar
+    assert_close(out.cpu(), O.matmul_oracle(a.cpu(), b.cpu()), f16)  # this package's bar
+
+
+def test_dispatch_correctness_and_single_backend():
+    a = torch.randn(512, 512, device=DEV, dtype=f16)
+    b = torch.randn(512, 512, device=DEV, dtype=f16)
+    with tnx.matmul.force_backend("cuda"):
+        out = tnx.matmul(a, b)
+    assert_close(out.cpu(), O.matmul_oracle(a.cpu(), b.cpu()), f16)
+    for name in ("triton", "pytorch"):
+        with pytest.raises(KeyError):
+            with tnx.matmul.force_backend(name):
+                pass
+
+
+def test_dispatch_caches_winner(tmp_path):
+    tnx.matmul.clear_cache()
+    a = torch.randn(1024, 1024, device=DEV, dtype=f16)
+    b = torch.randn(1024, 1024, device=DEV, dtype=f16)
+    out1 = tnx.matmul(a, b)
+    assert len(tnx.matmul.cache) == 1
+    key = (1024, 1024, "torch.float16", 1024, 1024, "torch.float16")
+    assert tnx.matmul.cache[key] == "cuda" and set(tnx.matmul.timings[key]) == {"cuda"}
+    assert tnx.matmul.timings[key]["cuda"] > 0
+    out2 = tnx.matmul(a, b)
+    assert torch.equal(out1, out2)
+    tnx.matmul.clear_cache()
+
+
+def test_quick_start_shape_with_fp32_reference():
+    """A 1024x512, B 512x768, N(0,1) entries, fp16 in / fp32 accumulate / fp16 out."""
+    a, b = seeded(1024, 512, 768, f16, seed=0, b_scale=1.0)
+    out = tnx.matmul(a.to(DEV), b.to(DEV))
+    tnx.check_status()
+    assert_close(out.cpu(), O.matmul_oracle(a, b), f16)
+
+
+def test_matmul_splitk_uses_requested_factor():
+    a, b = seeded(64, 2048, 1024, f16, seed=1)
+    a, b = a.to(DEV), b.to(DEV)
+    for s in (2, 4):
+        out = tnx.matmul_splitk(a, b, split_k=s)
+        tnx.check_status()
+        assert_close(out.cpu(), O.splitk_oracle(a.cpu(), b.cpu(), s), f16)
+        mm = __import__("sys").modules["tritonix_b200.ops.matmul"]
+        assert mm._splitk_cfg[(64, 1024, 2048, s)]["split_k"] == s
+
+
+def test_kernel_handle_launch_syntax():
+    """kernel[grid](ptr args, sizes, strides, **cfg) with the reference's config names."""
+    a, b = seeded(256, 128, 192, f16, seed=2)
+    a, b = a.to(DEV), b.to(DEV)
+    c = torch.empty(256, 192, device=DEV, dtype=f16)
+    grid = (2, 2)
+    tnx.matmul_kernel[grid](a, b, c, 256, 192, 128, a.stride(0), a.stride(1), b.stride(0), b.stride(1),
+                            c.stride(0), c.stride(1), block_m=128, block_n=128, block_k=64, group_m=8,
+                            num_stages=3, num_warps=8)
+    tnx.check_status()
+    assert_close(c.cpu(), O.matmul_oracle(a.cpu(), b.cpu()), f16)
+    # GLU handle: n counts the interleaved columns (2F), output is M x F
+    x, w12 = seeded(128, 256, 2 * 96, f16, seed=3, b_scale=0.05)
+    x, w12 = x.to(DEV), w12.to(DEV)
+    for act in ("silu", "none", "sigmoid"):
+        z = torch.empty(128, 96, device=DEV, dtype=f16)
+        tnx.glu_kernel[(1, 2)](x, w12, z, 128, 192, 256, x.stride(0), x.stride(1), w12.stride(0),
+                               w12.stride(1), z.stride(0), z.stride(1), block_m=128, block_n=128,
+                               block_k=64, group_m=4, activation=act)
+        tnx.check_status()
+        assert_close(z.cpu(), O.glu_oracle(x.cpu(), w12.cpu(), act), f16)
+    # pre-run hooks fire with the launch arguments
+    seen = []
+    tnx.gemm_splitk_kernel.add_pre_run_hook(lambda *args, **kw: seen.append(kw.get("split_k")))
+    try:
+        tnx.gemm_splitk_kernel[(1,)](a, b, c, 256, 192, 128, a.stride(0), a.stride(1), b.stride(0),
+                                     b.stride(1), c.stride(0), c.stride(1), tile_n=64, split_k=2)
+        tnx.check_status()
+    finally:
+        tnx.gemm_splitk_kernel.kernel._pre_hooks.clear()
+    assert seen == [2]
+    assert_close(c.cpu(), O.matmul_oracle(a.cpu(), b.cpu()), f16)
+
+
+def test_swiglu_mlp_kernel_signature():
+    """swiglu_kernel[grid](x, w12, w3, z, m, n, k, f, strides...) = (silu(xW1)*(xW2)) W3."""
+    g = torch.Generator().manual_seed(4)
+    x = torch.randn(256, 512, generator=g).to(bf16)
+    w12 = (torch.randn(512, 2 * 384, generator=g) * 0.04).to(bf16)
+    w3 = (torch.randn(384, 256, generator=g) * 0.05).to(bf16)
+    xd, wd, w3d = x.to(DEV), w12.to(DEV), w3.to(DEV)
+    z = torch.empty(256, 256, device=DEV, dtype=bf16)
+    tnx.swiglu_kernel[(2, 3)](xd, wd, w3d, z, 256, 768, 512, 256, xd.stride(0), xd.stride(1),
+                              wd.stride(0), wd.stride(1), w3d.stride(0), w3d.stride(1), z.stride(0),
+                              z.stride(1), block_m=128, block_n=128, block_k=64, group_m=4, block_l=64)
+    tnx.check_status()
+    assert_close(z.cpu(), O.swiglu_mlp_oracle(x, w12, w3, hidden_dtype=bf16), bf16)
+    y = tnx.swiglu_mlp(xd, wd, w3d, cfg={"tile_n": 128}, down_cfg={"tile_n": 128})
+    tnx.check_status()
+    assert_close(y.cpu(), O.swiglu_mlp_oracle(x, w12, w3, hidden_dtype=bf16), bf16)
+
+
+def test_tuner_on_real_kernels_prunes_out_of_resources():
+    a, b = seeded(512, 512, 1024, bf16, seed=5)
+    a, b = a.to(DEV), b.to(DEV)
+    mm = __import__("sys").modules["tritonix_b200.ops.matmul"]
+    events = []
+
+    def launcher(cfg):
+        try:
+            return mm._launch_matmul(a, b, cfg)
+        except tnx.OutOfResources:
+            events.append(("oom", dict(cfg)))
+            raise
+        except ValueError:
+            events.append(("skip", dict(cfg)))
+            raise
+    best = tnx.matmul_kernel.tune(launcher, max_configs=40,
+                                  filter_fn=lambda c: c["group_m"] == 8 and c["tile_k"] == 64)
+    tnx.check_status()
+    assert best is not None and set(best) == set(tnx.matmul_kernel.space)
+    ooms = [c for kind, c in events if kind == "oom"]
+    assert ooms, "the 7- and 8-stage configurations of the 256-wide tile cannot fit in shared memory"
+    # nothing that needs at least as much memory as a failed configuration was tried afterwards
+    for i, (kind, c) in enumerate(events):
+        if kind != "oom":
+            continue
+        for kind2, c2 in events[i + 1:]:
+            assert not (c2["tile_n"] >= c["tile_n"] and c2["stages"] >= c["stages"]
+                        and c2["cta_group"] <= c["cta_group"] and c2["tile_k"] >= c["tile_k"])
+    out = mm._launch_matmul(a, b, best)
+    assert_close(out.cpu(), O.matmul_oracle(a.cpu(), b.cpu()), bf16)
+
+
+def test_torch_custom_ops():
+    a, b = seeded(256, 256, 512, bf16, seed=6)
+    a, b = a.to(DEV), b.to(DEV)
+    c = torch.ops.tritonix.gemm(a, b, [])
+    assert_close(c.cpu(), O.matmul_oracle(a.cpu(), b.cpu()), bf16)
+    c = torch.ops.tritonix.gemm_splitk(a, b, 2, [0, 128])
+    assert_close(c.cpu(), O.matmul_oracle(a.cpu(), b.cpu()), bf16)
+    z = torch.ops.tritonix.glu(a, b, _cabi.EPI_GLU_SILU, [0, 256, 64, 4, 2, 1])
+    assert_close(z.cpu(), O.glu_oracle(a.cpu(), b.cpu(), "silu"), bf16)
+    tnx.check_status()
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    with FakeTensorMode():
+        fa, fb = torch.empty(64, 32, dtype=bf16, device=DEV), torch.empty(32, 48, dtype=bf16, device=DEV)
+        assert torch.ops.tritonix.gemm(fa, fb, []).shape == (64, 48)
+        assert torch.ops.tritonix.glu(fa, fb, 2, []).shape == (64, 24)
+
+
+def test_do_bench_returns_positive_ms():
+    a, b = seeded(1024, 1024, 1024, bf16)
+    a, b = a.to(DEV), b.to(DEV)
+    c = torch.empty(1024, 1024, device=DEV, dtype=bf16)
+    ms = tnx.do_bench(lambda: _cabi.launch(a, b, c, None), warmup=2, rep=10)
+    med = tnx.do_bench(lambda: _cabi.launch(a, b, c, None), warmup=2, rep=10, return_mode="median")
+    assert 0 < ms < 5 and 0 < med < 5
+
+
+def test_status_word_reports_clean_after_all_launches():
+    tnx.check_status()
+    w = _cabi.status_word(torch.device(DEV, torch.cuda.current_device()))
+    assert int(w.item()) == 0

@@ -1,0 +1,74 @@
+"""Split-K parity and determinism.  The reference's kernel adds fp16-rounded partials with
+atomics (tritonix/ops/matmul.py:195-202) and is neither deterministic nor exact to one rounding;
+the CUDA kernel sums fp32 partials in slice order, so it must agree with the oracle within the
+fp16 tolerance for every split factor and be bit-identical from run to run."""
+import pytest
+import torch
+
+from oracle import contraction as O
+from tests.golden_cases import case_ids, inputs_and_reference
+from tests.gpu_util import DEV, assert_close, run_gemm, seeded
+from tritonix_b200 import _cabi
+
+pytestmark = pytest.mark.gpu
+bf16, f16 = torch.bfloat16, torch.float16
+T = {"kernel": "tcgen05"}
+
+
+@pytest.mark.parametrize("name", case_ids("splitk"))
+def test_matches_reference_kernel_outputs(golden, name):
+    a, b, ref, case = inputs_and_reference(golden, name)
+    out, res = run_gemm(a, b, {**T, "tile_n": 64, "split_k": case[6]["split_k"]})
+    assert_close(out, ref, a.dtype)
+    assert_close(out, O.splitk_oracle(a, b, case[6]["split_k"]), a.dtype)
+
+
+@pytest.mark.parametrize("split_k", [1, 2, 4, 8, 16])
+@pytest.mark.parametrize("tile_n,tile_k", [(128, 64), (64, 128)])
+def test_skinny_decode_shape_scaled(split_k, tile_n, tile_k):
+    """M=64 against a tall B (the decode-like configuration at 1/4 of its K and N)."""
+    a, b = seeded(64, 3584, 1024, f16, seed=split_k, a_scale=3584 ** -0.5, b_scale=1.0)
+    out, res = run_gemm(a, b, {**T, "tile_n": tile_n, "tile_k": tile_k, "split_k": split_k, "stages": 3})
+    assert res.split_k == split_k
+    assert_close(out, O.splitk_oracle(a, b, split_k, tile_k), f16)
+
+
+@pytest.mark.parametrize("m,n,k,dtype,cfg", [
+    (200, 520, 1000, bf16, {"tile_n": 64, "split_k": 3}),
+    (128, 128, 512, f16, {"tile_n": 128, "split_k": 2}),
+    (256, 512, 2048, bf16, {"tile_n": 128, "cta_group": 2, "split_k": 4}),
+    (130, 264, 200, f16, {"tile_n": 256, "split_k": 8}),   # split clamps to the 4 k-blocks
+    (64, 4096, 14336, f16, {"tile_n": 128, "split_k": 4, "tile_k": 128, "stages": 3}),  # full size
+])
+def test_general_shapes(m, n, k, dtype, cfg):
+    a, b = seeded(m, k, n, dtype, seed=k)
+    out, res = run_gemm(a, b, {**T, **cfg})
+    assert_close(out, O.matmul_oracle(a, b), dtype)
+
+
+def test_bit_deterministic_and_workspace_reusable():
+    a, b = seeded(64, 14336, 4096, f16, seed=3)
+    a, b = a.to(DEV), b.to(DEV)
+    outs = []
+    for i in range(4):
+        c = torch.empty(64, 4096, device=DEV, dtype=f16)
+        _cabi.launch(a, b, c, {**T, "tile_n": 128, "split_k": 8, "stages": 6})
+        outs.append(c)
+    _cabi.check_status(a.device)
+    assert all(torch.equal(outs[0], o) for o in outs[1:])
+    # the tile counters are left at zero: the same workspace serves a different shape next
+    a2, b2 = seeded(256, 1024, 384, bf16, seed=4)
+    out, _ = run_gemm(a2, b2, {**T, "tile_n": 128, "split_k": 4})
+    assert_close(out, O.matmul_oracle(a2, b2), bf16)
+    ws = next(iter(_cabi._workspaces.values()))
+    assert int(ws[:_cabi.COUNTER_BYTES].view(torch.int32).abs().sum()) == 0
+
+
+def test_split_changes_only_the_summation_order():
+    a, b = seeded(128, 2048, 256, f16, seed=9)
+    ref = O.matmul_oracle(a, b)
+    errs = []
+    for s in (1, 2, 4, 8, 16):
+        out, _ = run_gemm(a, b, {**T, "tile_n": 128, "split_k": s})
+        errs.append(O.rel_err(out, ref))
+    assert max(errs) <= 2e-3 and max(errs) - min(errs) < 5e-4  # no growth with the split factor

@@ -154,6 +154,22 @@ def query(problem: Problem, config: Config) -> Resources:
     return res
 
 
+def require_cuda(*tensors: torch.Tensor) -> None:
+    """The package has a single backend; host tensors are an error, never a fallback."""
+    for t in tensors:
+        if not isinstance(t, torch.Tensor) or not t.is_cuda:
+            raise RuntimeError("tritonix_b200 operates on CUDA tensors only: there is no CPU, "
+                               "Triton or PyTorch path to fall back to")
+
+
+def umma_eligible_tensors(a: torch.Tensor, b: torch.Tensor) -> bool:
+    """True when (a, b) can run on the TMA/tcgen05 kernels (the only ones worth tuning)."""
+    return (a.dtype in (torch.float16, torch.bfloat16) and a.dtype == b.dtype
+            and a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
+            and a.stride(0) % 8 == 0 and b.stride(0) % 8 == 0 and b.shape[1] % 8 == 0
+            and a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0)
+
+
 # ---- per-device scratch owned by the Python layer (the C ABI never allocates)
 _scratch_lock = threading.Lock()
 _status_words: dict[int, torch.Tensor] = {}
@@ -196,8 +212,39 @@ def check_status(device: torch.device | None = None) -> None:
     raise_for(lib.tnx_read_status(w.data_ptr(), ctypes.byref(code), stream))
 
 
+def launch_raw(device: torch.device, dtype: torch.dtype, a_ptr: int, b_ptr: int, c_ptr: int,
+               m: int, n: int, k: int, strides, cfg: dict | None = None,
+               epilogue: int = EPI_NONE, tile_table=None) -> Resources:
+    """Enqueues one contraction from raw pointers, sizes and element strides
+    (stride_am, stride_ak, stride_bk, stride_bn, stride_cm, stride_cn) on torch's current
+    stream of ``device``.  ``tile_table`` may be a tensor or a callable
+    ``(tiles_m, tiles_n) -> int32 CUDA tensor`` evaluated after the tile grid is known."""
+    problem = make_problem(m, n, k, dtype, strides, epilogue)
+    config = make_config(cfg)
+    with torch.cuda.device(device):
+        res = query(problem, config)
+        ws_ptr, ws_bytes = None, 0
+        if res.workspace_bytes > 0:
+            ws = workspace(device, int(res.workspace_bytes))
+            ws_ptr, ws_bytes = ws.data_ptr(), ws.numel()
+        table_ptr = None
+        if config.tile_order == ORDER_TABLE and res.kernel == KERNEL_TCGEN05:
+            if callable(tile_table):
+                tile_table = tile_table(res.tiles_m, res.tiles_n)
+            if tile_table is None or tile_table.dtype != torch.int32 or not tile_table.is_cuda:
+                raise ValueError("tile_order='hilbert'/'table' needs an int32 CUDA tile table")
+            if tile_table.numel() != res.tiles_m * res.tiles_n:
+                raise ValueError("tile table length does not match the tile grid")
+            table_ptr = tile_table.data_ptr()
+        stream = torch.cuda.current_stream(device).cuda_stream
+        rc = lib.tnx_gemm(ctypes.byref(problem), ctypes.byref(config), a_ptr, b_ptr, c_ptr,
+                          ws_ptr, ws_bytes, table_ptr, status_word(device).data_ptr(), stream)
+    raise_for(rc)
+    return res
+
+
 def launch(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, cfg: dict | None = None,
-           epilogue: int = EPI_NONE, tile_table: torch.Tensor | None = None) -> Resources:
+           epilogue: int = EPI_NONE, tile_table=None) -> Resources:
     """Enqueues C = epilogue(A.B) on torch's current stream.  a: M x K, b: K x N, c: M x N (or
     M x N/2 for a GLU epilogue); any strides.  Returns the resources the launch used."""
     if not (a.is_cuda and b.is_cuda and c.is_cuda):
@@ -215,24 +262,5 @@ def launch(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, cfg: dict | None =
     n_out = n // 2 if epilogue != EPI_NONE else n
     if tuple(c.shape) != (m, n_out):
         raise ValueError(f"output must be {(m, n_out)}, got {tuple(c.shape)}")
-    problem = make_problem(m, n, k, a.dtype, (*a.stride(), *b.stride(), *c.stride()), epilogue)
-    config = make_config(cfg)
-    with torch.cuda.device(a.device):
-        res = query(problem, config)
-        ws_ptr, ws_bytes = None, 0
-        if res.workspace_bytes > 0:
-            ws = workspace(a.device, int(res.workspace_bytes))
-            ws_ptr, ws_bytes = ws.data_ptr(), ws.numel()
-        table_ptr = None
-        if config.tile_order == ORDER_TABLE:
-            if tile_table is None or tile_table.dtype != torch.int32 or not tile_table.is_cuda:
-                raise ValueError("tile_order='hilbert'/'table' needs an int32 CUDA tile table")
-            if tile_table.numel() != res.tiles_m * res.tiles_n:
-                raise ValueError("tile table length does not match the tile grid")
-            table_ptr = tile_table.data_ptr()
-        stream = torch.cuda.current_stream(a.device).cuda_stream
-        rc = lib.tnx_gemm(ctypes.byref(problem), ctypes.byref(config), a.data_ptr(), b.data_ptr(),
-                          c.data_ptr(), ws_ptr, ws_bytes, table_ptr,
-                          status_word(a.device).data_ptr(), stream)
-    raise_for(rc)
-    return res
+    return launch_raw(a.device, a.dtype, a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k,
+                      (*a.stride(), *b.stride(), *c.stride()), cfg, epilogue, tile_table)

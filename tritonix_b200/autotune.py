@@ -1,0 +1,207 @@
+"""Kernel autotuner with out-of-resources pruning.
+
+Public surface of the reference's tritonix/autotune.py:21-227 — ``TunableKernel`` (``configs``,
+``tune`` with ``method="grid" | "bayesian"``), the ``tunable`` decorator and the re-exported
+space types — on top of the CUDA kernels of this package.  Differences that follow from the
+backend: timing uses ``tritonix_b200.testing.do_bench`` and the exception that prunes is
+``tritonix_b200.OutOfResources`` (shared-memory / TMEM budget of an SM exceeded, reported by the
+C ABI before launch) instead of Triton's.
+"""
+from __future__ import annotations
+
+import itertools
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, Iterable, List, Optional, Set
+
+from tritonix_b200._cabi import OutOfResources
+from tritonix_b200.testing import do_bench
+from tritonix_b200.utils.pruners import (CoordinateMonotonicFunction, CoordinateUnimodalFunction,
+                                        MonotonicCascadeTrie)
+from tritonix_b200.utils.spaces import (Choice, ConfigParam, ConfigSpace, PowerOfTwo, Range,
+                                       SpaceConfig)
+
+__all__ = ["TunableKernel", "tunable", "Choice", "Range", "PowerOfTwo", "SpaceConfig",
+           "ConfigSpace", "ConfigParam", "OutOfResources", "MonotonicCascadeTrie",
+           "CoordinateMonotonicFunction", "CoordinateUnimodalFunction"]
+
+
+@dataclass
+class TunableKernel:
+    """A kernel plus the space of launch configurations worth trying for it.
+
+    ``memory_params`` names the axes along which shared-memory / TMEM use grows with the value;
+    they span the trie that prunes configurations dominated by one that ran out of resources.
+    ``memory_rank`` optionally maps an axis name to a sort key for axes whose memory use is not
+    increasing in the numeric value (``cta_group``: two CTAs per tile need *less* shared
+    memory per CTA than one).
+    """
+
+    kernel: Any
+    keys: List[str]
+    space: Dict[str, ConfigParam]
+    memory_params: Set[str]
+    memory_rank: Dict[str, Callable[[Any], Any]] = field(default_factory=dict)
+
+    def __post_init__(self):
+        if isinstance(self.kernel, TunableKernel):  # decorating twice unwraps (autotune.py:28-30)
+            self.kernel = self.kernel.kernel
+
+    # ``tk[grid](...)``, ``tk.add_pre_run_hook`` ... go to the wrapped kernel handle.
+    def __getattr__(self, name):
+        if name in ("kernel", "__setstate__"):
+            raise AttributeError(name)
+        return getattr(self.kernel, name)
+
+    def __getitem__(self, grid):
+        return self.kernel[grid]
+
+    # ------------------------------------------------------------------ space helpers
+    def _memory_axes(self):
+        names = [n for n in self.space if n in self.memory_params]
+        values = [sorted(self.space[n].values(), key=self.memory_rank.get(n)) for n in names]
+        return names, values
+
+    def _build_trie(self):
+        names, values = self._memory_axes()
+        trie = MonotonicCascadeTrie(SpaceConfig({n: Choice(v) for n, v in zip(names, values)}))
+        return trie, names, values
+
+    def configs(self, filter_fn: Optional[Callable[[dict], bool]] = None) -> List[dict]:
+        """Full cross product of the space, first key varying slowest."""
+        names = list(self.space)
+        out = [dict(zip(names, combo))
+               for combo in itertools.product(*(self.space[n].values() for n in names))]
+        if filter_fn is not None:
+            out = [c for c in out if filter_fn(c)]
+        return out
+
+    # ------------------------------------------------------------------ tuning
+    def tune(self, launcher: Callable[[dict], Any], method: str = "grid",
+             max_configs: Optional[int] = None, max_evals: int = 100,
+             filter_fn: Optional[Callable[[dict], bool]] = None, warmup: float = 25,
+             rep: float = 100, verbose: bool = False):
+        """Times ``launcher(cfg)`` over the space and returns the fastest ``cfg`` (a dict with
+        every key of the space), or ``None`` if nothing could be run.
+
+        ``launcher`` raises ``OutOfResources`` for a configuration that does not fit (its memory
+        coordinates and everything above them are then pruned) and ``ValueError`` for one that
+        is invalid or not built (skipped).
+        """
+        if method == "grid":
+            return self._tune_grid(launcher, max_configs, filter_fn, warmup, rep, verbose)
+        return self._tune_bayesian(launcher, max_evals, filter_fn, warmup, rep, verbose)
+
+    def _tune_grid(self, launcher, max_configs, filter_fn, warmup, rep, verbose):
+        trie, mem_names, mem_values = self._build_trie()
+        names = list(self.space)
+        axis_values = {n: sorted(self.space[n].values()) for n in names}
+        position = {n: {v: i for i, v in enumerate(vals)} for n, vals in axis_values.items()}
+        landscape = CoordinateUnimodalFunction(
+            SpaceConfig({n: Choice(axis_values[n]) for n in names}))
+        free_names = [n for n in names if n not in set(mem_names)]
+
+        best_ms, best_cfg, evaluated = float("inf"), None, 0
+        budget_left = lambda: max_configs is None or evaluated < max_configs  # noqa: E731
+
+        for mem_idx in trie.generate_all_unpruned_midpoint():
+            if not budget_left():
+                break
+            mem_cfg = {n: mem_values[d][mem_idx[d]] for d, n in enumerate(mem_names)}
+            for combo in itertools.product(*(axis_values[n] for n in free_names)):
+                if not budget_left():
+                    break
+                cfg = {**mem_cfg, **dict(zip(free_names, combo))}
+                if filter_fn is not None and not filter_fn(cfg):
+                    continue
+                coords = tuple(position[n][cfg[n]] for n in names)
+                if landscape.is_pruned(coords):
+                    continue
+                try:
+                    ms = do_bench(lambda: launcher(cfg), warmup=warmup, rep=rep)
+                except ValueError as exc:
+                    if verbose:
+                        print(f"  SKIP      {cfg}  ({exc})", flush=True)
+                    continue
+                except OutOfResources:
+                    trie.prune(mem_idx)
+                    if verbose:
+                        print(f"  OOM       {cfg}", flush=True)
+                    break  # nothing else at these memory coordinates can fit
+                landscape.record(coords, ms)
+                evaluated += 1
+                improved = ms < best_ms
+                if improved:
+                    best_ms, best_cfg = ms, cfg
+                if verbose:
+                    print(f"  {ms:8.3f}ms  {cfg}{' *' if improved else ''}", flush=True)
+        return best_cfg
+
+    def _tune_bayesian(self, launcher, max_evals, filter_fn, warmup, rep, verbose,
+                       oom_penalty: float = 1e6):
+        """Bayesian optimisation through Ax's service API, as tritonix/autotune.py:142-214.
+        Needs the optional ``ax-platform`` package."""
+        try:
+            import logging
+
+            from ax.service.ax_client import AxClient
+            from ax.service.utils.instantiation import ObjectiveProperties
+            from ax.utils.common.logger import set_ax_logger_levels
+        except ImportError as exc:  # pragma: no cover - ax is optional
+            raise ImportError("method='bayesian' needs the optional 'ax-platform' package; "
+                              "use method='grid'") from exc
+
+        set_ax_logger_levels(logging.WARNING)
+        trie, mem_names, mem_values = self._build_trie()
+        parameters = [
+            {"name": n, "type": "choice", "values": axis.values(), "sort_values": True,
+             "is_ordered": isinstance(axis, (PowerOfTwo, Range))}
+            for n, axis in self.space.items() if len(axis.values()) > 1]
+        fixed = {n: axis.values()[0] for n, axis in self.space.items() if len(axis.values()) == 1}
+        client = AxClient(verbose_logging=False)
+        client.create_experiment(name="kernel_tune", parameters=parameters,
+                                 objectives={"latency_ms": ObjectiveProperties(minimize=True)})
+
+        def mem_index(cfg):
+            return tuple(mem_values[d].index(cfg[n]) for d, n in enumerate(mem_names))
+
+        for trial in range(max_evals):
+            params, trial_index = client.get_next_trial()
+            cfg = {**fixed, **params}
+            hopeless = (bool(mem_names) and trie.is_pruned(mem_index(cfg))) or \
+                       (filter_fn is not None and not filter_fn(cfg))
+            if hopeless:
+                client.complete_trial(trial_index=trial_index, raw_data={"latency_ms": oom_penalty})
+                continue
+            try:
+                ms = do_bench(lambda: launcher(cfg), warmup=warmup, rep=rep)
+            except OutOfResources:
+                if mem_names:
+                    trie.prune(mem_index(cfg))
+                ms = oom_penalty
+            except ValueError:
+                ms = oom_penalty
+            client.complete_trial(trial_index=trial_index, raw_data={"latency_ms": ms})
+            if verbose and ms < oom_penalty:
+                print(f"  [{trial + 1}/{max_evals}] {ms:.3f}ms — {cfg}")
+        best, _ = client.get_best_parameters()
+        return {**fixed, **best}
+
+
+def tunable(keys: Iterable[str], space: Dict[str, ConfigParam],
+            memory_params: Optional[Set[str]] = None,
+            memory_rank: Optional[Dict[str, Callable]] = None):
+    """Decorator: wraps a kernel handle into a ``TunableKernel``.  The pipeline depth
+    (``num_stages`` in the reference's spelling, ``stages`` here) always counts as a memory
+    axis (tritonix/autotune.py:218)."""
+    memory = set(memory_params or ()) | {"num_stages", "stages"}
+
+    def wrap(kernel):
+        tk = TunableKernel(kernel=kernel, keys=list(keys), space=space, memory_params=memory,
+                           memory_rank=dict(memory_rank or {}))
+        try:
+            tk.kernel.specialize_keys = list(keys)
+        except AttributeError:  # handles with __slots__
+            pass
+        return tk
+
+    return wrap

@@ -1,0 +1,128 @@
+"""Multi-GPU use of the contraction kernels: one process per GPU, ``torch.distributed`` (NCCL
+over NVLink) for the single exchange step.  The reference has no multi-device code; the two
+layouts here are the ones its kernels shard into naturally.
+
+* Large-M GEMM: rows of A (and of C) are split across ranks, B is replicated, no collective.
+* SwiGLU MLP, tensor parallel: gate/up projections are column-parallel (rank r owns hidden
+  units [r*F/p, (r+1)*F/p), i.e. interleaved W12 columns [2rF/p, 2(r+1)F/p)), the down
+  projection is row-parallel, and ONE all-reduce sums the partial outputs.  The all-reduce is
+  cut into row chunks and issued on a side stream so that it overlaps the next chunk's GEMMs.
+
+No kernel of this package reads another GPU's memory; remote data only ever arrives through
+the collective into local buffers.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def shard_bounds(total: int, rank: int, world: int, multiple: int = 1) -> Tuple[int, int]:
+    """[lo, hi) of ``rank``'s contiguous share of ``total`` items, in units of ``multiple``
+    (the last ranks get one unit less when it does not divide evenly)."""
+    if total % multiple:
+        raise ValueError(f"{total} is not a multiple of {multiple}")
+    units = total // multiple
+    base, extra = divmod(units, world)
+    lo = rank * base + min(rank, extra)
+    hi = lo + base + (1 if rank < extra else 0)
+    return lo * multiple, hi * multiple
+
+
+def shard_rows(a: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    """Rank's row block of A for the M-sharded GEMM (a view, no copy)."""
+    lo, hi = shard_bounds(a.shape[0], rank, world)
+    return a[lo:hi]
+
+
+def sharded_matmul(a_rows: torch.Tensor, b: torch.Tensor, matmul_fn: Optional[Callable] = None):
+    """C rows of this rank = its A rows times the replicated B.  No communication."""
+    if matmul_fn is None:
+        from tritonix_b200.ops import cuda_matmul as matmul_fn
+    return matmul_fn(a_rows, b)
+
+
+def shard_mlp_weights(w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, rank: int,
+                      world: int, multiple: int = 128):
+    """Slices global weights for ``rank`` and interleaves gate/up AFTER slicing, so that a shard
+    boundary never separates a (gate_j, up_j) column pair.
+
+    w_gate, w_up: (d_model, d_ff); w_down: (d_ff, d_model).
+    Returns (w12_shard (d_model, 2*F_r), w_down_shard (F_r, d_model)).
+    """
+    d_ff = w_gate.shape[1]
+    lo, hi = shard_bounds(d_ff, rank, world, multiple if d_ff % (multiple * world) == 0 else 1)
+    g, u = w_gate[:, lo:hi], w_up[:, lo:hi]
+    w12 = torch.stack((g, u), dim=2).reshape(g.shape[0], 2 * g.shape[1]).contiguous()
+    return w12, w_down[lo:hi].contiguous()
+
+
+class TensorParallelSwiGLU:
+    """y = (silu(x W_gate) * (x W_up)) W_down with the hidden dimension split over the group.
+
+    ``gate_up_fn(x, w12) -> h`` and ``down_fn(h, w_down, out=y_rows)`` (writes the partial
+    output into ``out``) default to this package's CUDA kernels; they are parameters so that the partitioning and the chunked
+    all-reduce schedule can be exercised by CPU (gloo) ranks in tests.
+    """
+
+    def __init__(self, w12_shard: torch.Tensor, w_down_shard: torch.Tensor,
+                 group: Optional[dist.ProcessGroup] = None, chunks: int = 4,
+                 gate_up_fn: Optional[Callable] = None, down_fn: Optional[Callable] = None):
+        if w12_shard.shape[1] != 2 * w_down_shard.shape[0]:
+            raise ValueError("w12 shard must have twice as many columns as w_down shard has rows")
+        self.w12 = w12_shard
+        self.w_down = w_down_shard
+        self.group = group
+        self.chunks = max(1, int(chunks))
+        if gate_up_fn is None or down_fn is None:
+            from tritonix_b200.ops import cuda_matmul, swiglu
+            gate_up_fn = gate_up_fn or swiglu
+            down_fn = down_fn or cuda_matmul
+        self.gate_up_fn = gate_up_fn
+        self.down_fn = down_fn
+        self._comm_stream = None
+
+    @property
+    def world_size(self) -> int:
+        return dist.get_world_size(self.group) if dist.is_initialized() else 1
+
+    def chunk_bounds(self, m: int) -> List[Tuple[int, int]]:
+        """Row ranges of the all-reduce chunks: multiples of 256 rows where possible."""
+        n = min(self.chunks, max(1, m // 256))
+        mult = 256 if m % 256 == 0 else 1
+        return [shard_bounds(m, i, n, mult) for i in range(n)]
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        m = x.shape[0]
+        y = torch.empty((m, self.w_down.shape[1]), device=x.device, dtype=x.dtype)
+        world = self.world_size
+        on_gpu = x.is_cuda
+        if on_gpu and world > 1 and self._comm_stream is None:
+            self._comm_stream = torch.cuda.Stream(device=x.device)
+        pending = []
+        for lo, hi in self.chunk_bounds(m):
+            h = self.gate_up_fn(x[lo:hi], self.w12)
+            self.down_fn(h, self.w_down, out=y[lo:hi])
+            if world == 1:
+                continue
+            if on_gpu:
+                # all-reduce of this chunk runs on the side stream while the main stream
+                # computes the next chunk
+                ready = torch.cuda.Event()
+                ready.record(torch.cuda.current_stream(x.device))
+                with torch.cuda.stream(self._comm_stream):
+                    self._comm_stream.wait_event(ready)
+                    dist.all_reduce(y[lo:hi], op=dist.ReduceOp.SUM, group=self.group)
+            else:
+                pending.append(dist.all_reduce(y[lo:hi], op=dist.ReduceOp.SUM, group=self.group,
+                                               async_op=True))
+        if world > 1:
+            if on_gpu:
+                torch.cuda.current_stream(x.device).wait_stream(self._comm_stream)
+            for work in pending:
+                work.wait()
+        return y
+
+    __call__ = forward

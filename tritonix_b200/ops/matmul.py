@@ -1,0 +1,172 @@
+"""GEMM entry points: ``matmul_kernel`` / ``gemm_splitk_kernel`` handles, their launchers, the
+per-shape tuned configuration caches, ``cuda_matmul`` (the reference's ``triton_matmul``),
+``matmul_splitk`` and the ``matmul`` dispatcher — the surface of tritonix/ops/matmul.py:30-293.
+
+Search space = the CUDA kernels' template and launch parameters:
+  tile_n     columns of B per tile (64 / 128 / 256)
+  tile_k     K elements per pipeline stage (64 / 128)
+  stages     depth of the TMA -> shared-memory ring
+  cta_group  1 = one SM per 128 x tile_n tile, 2 = a CTA pair shares a 256 x tile_n tile
+  group_m    band height of the grouped tile order
+  split_k    K slices per tile (split-K kernel only)
+"out of resources" means stages x stage bytes (+ epilogue staging) exceeds the 227 KiB of shared
+memory of an SM, or the accumulators exceed its 512 TMEM columns.
+"""
+from __future__ import annotations
+
+import os
+
+import torch
+
+from tritonix_b200 import _cabi
+from tritonix_b200.autotune import Choice, PowerOfTwo, Range, tunable
+from tritonix_b200.dispatcher import dynamic_dispatch
+from tritonix_b200.ops._kernel_handle import CudaKernel
+
+_MEMORY = {"tile_n", "tile_k", "stages", "cta_group"}
+_RANK = {"cta_group": lambda g: -g}  # a CTA pair needs less shared memory per CTA than one CTA
+
+matmul_kernel = tunable(
+    keys=["m", "n", "k"],
+    space={
+        "tile_n": PowerOfTwo(64, 256),
+        "tile_k": PowerOfTwo(64, 128),
+        "stages": Range(2, 8),
+        "cta_group": Choice([1, 2]),
+        "group_m": Choice([4, 8, 16]),
+    },
+    memory_params=_MEMORY,
+    memory_rank=_RANK,
+)(CudaKernel("matmul_kernel", doc="C = A x B; A is (M, K), B is (K, N), C is (M, N); fp32 "
+                                  "accumulation, result cast to the input type."))
+
+gemm_splitk_kernel = tunable(
+    keys=["m", "n", "k"],
+    space={
+        "tile_n": PowerOfTwo(64, 256),
+        "tile_k": PowerOfTwo(64, 128),
+        "stages": Range(3, 8),
+        "cta_group": Choice([1]),
+        "group_m": Choice([8]),
+        "split_k": Choice([1, 2, 4, 8, 16]),
+    },
+    memory_params=_MEMORY,
+    memory_rank=_RANK,
+)(CudaKernel("gemm_splitk_kernel", doc="C = A x B with K cut into split_k slices per tile; the "
+                                       "slices' fp32 partials are summed in a fixed order."))
+
+
+def _strides(a, b, c):
+    return (a.stride(0), a.stride(1), b.stride(0), b.stride(1), c.stride(0), c.stride(1))
+
+
+def _new_output(a, b, out):
+    m, n = a.shape[0], b.shape[1]
+    if out is None:
+        return torch.empty((m, n), device=a.device, dtype=a.dtype)
+    if tuple(out.shape) != (m, n) or out.dtype != a.dtype or out.device != a.device:
+        raise ValueError(f"out must be a {(m, n)} {a.dtype} tensor on {a.device}")
+    return out
+
+
+def _launch_matmul(a: torch.Tensor, b: torch.Tensor, cfg: dict, out=None) -> torch.Tensor:
+    """Allocates C (unless ``out`` is given) and runs ``matmul_kernel`` with ``cfg``
+    (tritonix/ops/matmul.py:217-237)."""
+    m, k = a.shape
+    _, n = b.shape
+    c = _new_output(a, b, out)
+    matmul_kernel[(1,)](a, b, c, m, n, k, *_strides(a, b, c), **cfg)
+    return c
+
+
+def _launch_splitk(a: torch.Tensor, b: torch.Tensor, cfg: dict, out=None) -> torch.Tensor:
+    """Split-K launch (tritonix/ops/matmul.py:240-264).  C needs no zero fill: nothing is
+    accumulated into it, the last slice to finish writes the ordered sum."""
+    m, k = a.shape
+    _, n = b.shape
+    c = _new_output(a, b, out)
+    gemm_splitk_kernel[(1,)](a, b, c, m, n, k, *_strides(a, b, c), **cfg)
+    return c
+
+
+# ------------------------------------------------------------------------------------------
+# configuration choice
+# ------------------------------------------------------------------------------------------
+
+def default_config(m: int, n: int, k: int, split_k: int | None = None) -> dict:
+    """Configuration used when tuning is disabled (``TRITONIX_B200_TUNE=0``): the shapes that
+    measured best on a B200 for large, skinny and small problems."""
+    if split_k is not None:
+        return {"tile_n": 128 if n >= 1024 else 64, "tile_k": 128, "stages": 3, "cta_group": 1,
+                "group_m": 8, "split_k": int(split_k)}
+    if m > 128 and n >= 256:
+        return {"tile_n": 256, "tile_k": 128, "stages": 3, "cta_group": 2, "group_m": 16}
+    if n >= 256:
+        return {"tile_n": 256, "tile_k": 64, "stages": 4, "cta_group": 1, "group_m": 8}
+    return {"tile_n": 128 if n > 64 else 64, "tile_k": 64, "stages": 6, "cta_group": 1,
+            "group_m": 8}
+
+
+def _tuning_enabled() -> bool:
+    return os.environ.get("TRITONIX_B200_TUNE", "1") not in ("0", "false", "off")
+
+
+def _plausible(m: int, n: int):
+    """Drops configurations that cannot win for the shape, to keep the first call short."""
+    def keep(cfg):
+        if cfg.get("cta_group", 1) == 2 and m <= 128:
+            return False
+        if cfg["tile_n"] > 64 and cfg["tile_n"] >= 2 * max(n, 64):
+            return False
+        return True
+    return keep
+
+
+_matmul_cfg: dict = {}
+_splitk_cfg: dict = {}
+
+
+def cuda_matmul(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``a @ b`` on the CUDA kernels, tuning once per (m, n, k)
+    (the reference's ``triton_matmul``, tritonix/ops/matmul.py:271-277).  ``out`` optionally
+    receives the result instead of a fresh tensor."""
+    _cabi.require_cuda(a, b)
+    m, k = a.shape
+    _, n = b.shape
+    key = (m, n, k)
+    cfg = _matmul_cfg.get(key)
+    if cfg is None:
+        if _tuning_enabled() and _cabi.umma_eligible_tensors(a, b):
+            cfg = matmul_kernel.tune(lambda c: _launch_matmul(a, b, c), filter_fn=_plausible(m, n))
+        cfg = cfg or default_config(m, n, k)
+        _matmul_cfg[key] = cfg
+    return _launch_matmul(a, b, cfg, out)
+
+
+cuda_matmul.__name__ = "cuda_matmul"
+triton_matmul = cuda_matmul  # name kept for callers of the reference API
+
+
+def matmul_splitk(a: torch.Tensor, b: torch.Tensor, split_k: int = 4,
+                  out: torch.Tensor | None = None) -> torch.Tensor:
+    """Split-K GEMM (tritonix/ops/matmul.py:280-288).  Unlike the reference, where ``split_k``
+    only keys the cache and the tuner picks the factor, the requested factor is the one used;
+    the remaining parameters are tuned once per (m, n, k, split_k)."""
+    _cabi.require_cuda(a, b)
+    m, k = a.shape
+    _, n = b.shape
+    key = (m, n, k, split_k)
+    cfg = _splitk_cfg.get(key)
+    if cfg is None:
+        if _tuning_enabled() and _cabi.umma_eligible_tensors(a, b):
+            cfg = gemm_splitk_kernel.tune(
+                lambda c: _launch_splitk(a, b, c),
+                filter_fn=lambda c: c["split_k"] == split_k and _plausible(m, n)(c))
+        cfg = cfg or default_config(m, n, k, split_k)
+        _splitk_cfg[key] = cfg
+    return _launch_splitk(a, b, cfg, out)
+
+
+# A single backend: the dispatcher keeps its shape-keyed .cache / .timings and force_backend,
+# but there is no Triton, PyTorch or CPU implementation behind it.
+matmul = dynamic_dispatch({"cuda": cuda_matmul}, key=["a", "b"])
