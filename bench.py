@@ -54,7 +54,7 @@ GLU_CFG = {"kernel": "tcgen05", "tile_n": 256, "tile_k": 128, "stages": 3, "cta_
 
 # DRAM traffic of the dominant kernel per launch, from the ncu captures summarised under
 # profiles/ (None until a capture of that workload exists).
-NCU_TRAFFIC_BYTES = {"gemm": None, "splitk": None, "glu": None, "mlp": None}
+NCU_TRAFFIC_BYTES = {"gemm": 1_389_138_048, "splitk": None, "glu": None, "mlp": None}
 
 
 def measured_peaks():
@@ -336,6 +336,9 @@ def main():
     ap.add_argument("--workload", choices=list(WORKLOADS), default="gemm")
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cfg", type=str, default=None,
+                    help="JSON object overriding kernel-config keys of the workload, e.g. "
+                         "'{\"group_m\": 8}'")
     ap.add_argument("--no-e2e", action="store_true",
                     help="skip the host-buffer leg (used for profiler captures of the kernel)")
     args = ap.parse_args()
@@ -368,6 +371,10 @@ def main():
         return float(t.item())
 
     import tritonix_b200 as tnx
+    if args.cfg:
+        override = json.loads(args.cfg)
+        for base in (GEMM_CFG, SPLITK_CFG, GLU_CFG):
+            base.update(override)
     if args.workload == "mlp":
         step, e2e_step, work = setup_mlp(rank, world, dev)
     else:

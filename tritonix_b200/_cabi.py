@@ -178,12 +178,14 @@ _workspaces: dict[tuple[int, int], torch.Tensor] = {}
 
 def status_word(device: torch.device) -> torch.Tensor:
     idx = device.index if device.index is not None else torch.cuda.current_device()
-    with _scratch_lock:
-        w = _status_words.get(idx)
-        if w is None:
-            w = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
-            _status_words[idx] = w
-        return w
+    w = _status_words.get(idx)
+    if w is None:
+        with _scratch_lock:
+            w = _status_words.get(idx)
+            if w is None:
+                w = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+                _status_words[idx] = w
+    return w
 
 
 def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
@@ -212,34 +214,76 @@ def check_status(device: torch.device | None = None) -> None:
     raise_for(lib.tnx_read_status(w.data_ptr(), ctypes.byref(code), stream))
 
 
+_hilbert_tables: dict = {}
+
+
+def hilbert_table(device: torch.device, tiles_m: int, tiles_n: int) -> torch.Tensor:
+    """Device copy of the Hilbert tile order for a tiles_m x tiles_n grid (cached)."""
+    from tritonix_b200.utils.hilbert import hilbert_tile_table
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    key = (idx, tiles_m, tiles_n)
+    table = _hilbert_tables.get(key)
+    if table is None:
+        table = torch.tensor(hilbert_tile_table(tiles_m, tiles_n), dtype=torch.int32,
+                             device=torch.device("cuda", idx))
+        _hilbert_tables[key] = table
+    return table
+
+
+_plans: dict = {}
+
+
+def _plan(m, n, k, dtype, strides, cfg, epilogue):
+    """(problem, config, resources) for a launch signature; validated once, then reused."""
+    key = (m, n, k, dtype, strides, epilogue, tuple(sorted(cfg.items())) if cfg else ())
+    plan = _plans.get(key)
+    if plan is None:
+        problem = make_problem(m, n, k, dtype, strides, epilogue)
+        config = make_config(cfg)
+        plan = (problem, config, query(problem, config))
+        if len(_plans) > 4096:
+            _plans.clear()
+        _plans[key] = plan
+    return plan
+
+
 def launch_raw(device: torch.device, dtype: torch.dtype, a_ptr: int, b_ptr: int, c_ptr: int,
                m: int, n: int, k: int, strides, cfg: dict | None = None,
                epilogue: int = EPI_NONE, tile_table=None) -> Resources:
     """Enqueues one contraction from raw pointers, sizes and element strides
     (stride_am, stride_ak, stride_bk, stride_bn, stride_cm, stride_cn) on torch's current
-    stream of ``device``.  ``tile_table`` may be a tensor or a callable
-    ``(tiles_m, tiles_n) -> int32 CUDA tensor`` evaluated after the tile grid is known."""
-    problem = make_problem(m, n, k, dtype, strides, epilogue)
-    config = make_config(cfg)
-    with torch.cuda.device(device):
-        res = query(problem, config)
+    stream of ``device``.  With ``tile_order="hilbert"`` the tile table is generated here;
+    ``tile_order="table"`` takes it from ``tile_table`` (int32 CUDA tensor, one packed
+    ``(row << 16) | col`` word per tile)."""
+    problem, config, res = _plan(int(m), int(n), int(k), dtype, tuple(int(s) for s in strides),
+                                 cfg, int(epilogue))
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    switch = idx != torch.cuda.current_device()
+    if switch:
+        previous = torch.cuda.current_device()
+        torch.cuda.set_device(idx)
+    try:
         ws_ptr, ws_bytes = None, 0
         if res.workspace_bytes > 0:
             ws = workspace(device, int(res.workspace_bytes))
             ws_ptr, ws_bytes = ws.data_ptr(), ws.numel()
         table_ptr = None
         if config.tile_order == ORDER_TABLE and res.kernel == KERNEL_TCGEN05:
-            if callable(tile_table):
-                tile_table = tile_table(res.tiles_m, res.tiles_n)
+            if tile_table is None and (cfg or {}).get("tile_order") == "hilbert":
+                tile_table = hilbert_table(device, res.tiles_m, res.tiles_n)
             if tile_table is None or tile_table.dtype != torch.int32 or not tile_table.is_cuda:
                 raise ValueError("tile_order='hilbert'/'table' needs an int32 CUDA tile table")
             if tile_table.numel() != res.tiles_m * res.tiles_n:
                 raise ValueError("tile table length does not match the tile grid")
             table_ptr = tile_table.data_ptr()
-        stream = torch.cuda.current_stream(device).cuda_stream
+        stream = torch.cuda.current_stream(idx).cuda_stream
         rc = lib.tnx_gemm(ctypes.byref(problem), ctypes.byref(config), a_ptr, b_ptr, c_ptr,
                           ws_ptr, ws_bytes, table_ptr, status_word(device).data_ptr(), stream)
-    raise_for(rc)
+    finally:
+        if switch:
+            torch.cuda.set_device(previous)
+    if rc != OK:
+        raise_for(rc)
     return res
 
 

@@ -23,6 +23,8 @@
 #include <cuda_runtime.h>
 
 #include <mutex>
+#include <utility>
+#include <vector>
 
 #include "tnx_internal.h"
 #include "tnx_ptx.cuh"
@@ -55,6 +57,7 @@ struct UmmaParams {
   int kb_per_slice;     // K blocks per split-K slice
   int split_k;
   int tile_k;
+  int a_rows;           // rows of A that TMA brings in per stage (128, or fewer for a skinny M)
   int stages;
   int acc_stages;
   int group_m;
@@ -129,7 +132,7 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
                : "memory");
 }
 
-template <int TILE_N, int CTA_GROUP, bool GLU, bool BF16>
+template <int TILE_N, int TILE_K, int CTA_GROUP, bool GLU, bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_c, const UmmaParams p) {
@@ -144,8 +147,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const uint32_t base_addr = (raw_addr + 1023u) & ~1023u;  // 128B swizzle needs 1024-byte alignment
   uint8_t* base_ptr = smem_raw + (base_addr - raw_addr);
 
-  const int a_stage_bytes = kRowsPerCta * p.tile_k * 2;
-  const int b_stage_bytes = LOAD_N * p.tile_k * 2;
+  // When M < 128 only a_rows rows of A are loaded and stored per stage.  The MMA still reads 128
+  // rows: the extra ones come from whatever follows in shared memory and only feed accumulator
+  // rows >= M, which are never written out.
+  const int a_stage_bytes = p.a_rows * TILE_K * 2;
+  const int a_atom_bytes = p.a_rows * kAtomBytes;  // one 64-element K slab of the A stage
+  const int b_stage_bytes = LOAD_N * TILE_K * 2;
   const uint32_t smem_a = base_addr;
   const uint32_t smem_b = smem_a + p.stages * a_stage_bytes;
   const uint32_t smem_out = smem_b + p.stages * b_stage_bytes;  // 2 staging buffers
@@ -221,24 +228,28 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const uint32_t full_bar = ptx::smem_u32(&ctrl->full[stage]);
           const uint32_t a_dst = smem_a + stage * a_stage_bytes;
           const uint32_t b_dst = smem_b + stage * b_stage_bytes;
-          const int k0 = kb * p.tile_k;
+          const int k0 = kb * TILE_K;
           if (CTA_GROUP == 1) {
             ptx::mbar_arrive_expect_tx(full_bar, stage_tx);
-            for (int ka = 0; ka < p.tile_k / kAtomElems; ++ka)
-              ptx::tma_load_2d(a_dst + ka * (kRowsPerCta * kAtomBytes), &tmap_a,
+#pragma unroll
+            for (int ka = 0; ka < TILE_K / kAtomElems; ++ka)
+              ptx::tma_load_2d(a_dst + ka * a_atom_bytes, &tmap_a,
                                k0 + ka * kAtomElems, row0, full_bar);
+#pragma unroll
             for (int na = 0; na < LOAD_N / kAtomElems; ++na)
-              ptx::tma_load_2d(b_dst + na * (p.tile_k * kAtomBytes), &tmap_b,
+              ptx::tma_load_2d(b_dst + na * (TILE_K * kAtomBytes), &tmap_b,
                                col0 + na * kAtomElems, k0, full_bar);
           } else {
             // Both CTAs' loads complete on the leader's barrier; the leader announces the bytes.
             const uint32_t leader_bar = ptx::mapa(full_bar, 0);
             if (leader) ptx::mbar_arrive_expect_tx(full_bar, stage_tx);
-            for (int ka = 0; ka < p.tile_k / kAtomElems; ++ka)
-              ptx::tma_load_2d_pair(a_dst + ka * (kRowsPerCta * kAtomBytes), &tmap_a,
+#pragma unroll
+            for (int ka = 0; ka < TILE_K / kAtomElems; ++ka)
+              ptx::tma_load_2d_pair(a_dst + ka * a_atom_bytes, &tmap_a,
                                     k0 + ka * kAtomElems, row0, leader_bar);
+#pragma unroll
             for (int na = 0; na < LOAD_N / kAtomElems; ++na)
-              ptx::tma_load_2d_pair(b_dst + na * (p.tile_k * kAtomBytes), &tmap_b,
+              ptx::tma_load_2d_pair(b_dst + na * (TILE_K * kAtomBytes), &tmap_b,
                                     col0 + na * kAtomElems, k0, leader_bar);
           }
           if (++stage == p.stages) {
@@ -260,7 +271,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       // A: rows of 128 B, 8-row groups 1024 B apart.  B: 64-column atoms of tile_k rows x 128 B;
       // LBO = bytes between atoms along N, SBO = bytes between 8-row groups along K.
       const uint64_t a_desc_hi = ptx::make_smem_desc(0, 0, 1024);
-      const uint64_t b_desc_hi = ptx::make_smem_desc(0, p.tile_k * kAtomBytes, 1024);
+      const uint64_t b_desc_hi = ptx::make_smem_desc(0, TILE_K * kAtomBytes, 1024);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -288,8 +299,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           ptx::tc_fence_after_sync();
           const uint32_t a_src = smem_a + stage * a_stage_bytes;
           const uint32_t b_src = smem_b + stage * b_stage_bytes;
-          for (int k16 = 0; k16 < p.tile_k / 16; ++k16) {
-            const uint32_t a_addr = a_src + (k16 >> 2) * (kRowsPerCta * kAtomBytes) + (k16 & 3) * 32;
+#pragma unroll
+          for (int k16 = 0; k16 < TILE_K / 16; ++k16) {
+            const uint32_t a_addr = a_src + (k16 >> 2) * a_atom_bytes + (k16 & 3) * 32;
             const uint32_t b_addr = b_src + k16 * (16 * kAtomBytes);
             ptx::umma_f16<CTA_GROUP>(d_tmem, a_desc_hi | ((a_addr >> 4) & 0x3fffu),
                                      b_desc_hi | ((b_addr >> 4) & 0x3fffu), idesc, accumulate);
@@ -567,32 +579,53 @@ int make_tmap(CUtensorMap* out, const void* ptr, int dtype, int64_t cols, int64_
 using KernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const UmmaParams);
 
 template <int TILE_N, int CTA_GROUP, bool GLU>
-KernelFn pick_dtype(int dtype) {
-  return dtype == TNX_BF16 ? umma_gemm_kernel<TILE_N, CTA_GROUP, GLU, true>
-                           : umma_gemm_kernel<TILE_N, CTA_GROUP, GLU, false>;
+KernelFn pick_dtype(int tile_k, int dtype) {
+  if (tile_k == 64)
+    return dtype == TNX_BF16 ? umma_gemm_kernel<TILE_N, 64, CTA_GROUP, GLU, true>
+                             : umma_gemm_kernel<TILE_N, 64, CTA_GROUP, GLU, false>;
+  if (tile_k == 128)
+    return dtype == TNX_BF16 ? umma_gemm_kernel<TILE_N, 128, CTA_GROUP, GLU, true>
+                             : umma_gemm_kernel<TILE_N, 128, CTA_GROUP, GLU, false>;
+  return nullptr;
 }
 
 // The set of compiled kernels.  nullptr = not built.
-KernelFn pick_kernel(int tile_n, int cta_group, bool glu, int dtype) {
+KernelFn pick_kernel(int tile_n, int tile_k, int cta_group, bool glu, int dtype) {
   if (cta_group == 1) {
     if (!glu) {
-      if (tile_n == 64) return pick_dtype<64, 1, false>(dtype);
-      if (tile_n == 128) return pick_dtype<128, 1, false>(dtype);
-      if (tile_n == 256) return pick_dtype<256, 1, false>(dtype);
+      if (tile_n == 64) return pick_dtype<64, 1, false>(tile_k, dtype);
+      if (tile_n == 128) return pick_dtype<128, 1, false>(tile_k, dtype);
+      if (tile_n == 256) return pick_dtype<256, 1, false>(tile_k, dtype);
     } else {
-      if (tile_n == 128) return pick_dtype<128, 1, true>(dtype);
-      if (tile_n == 256) return pick_dtype<256, 1, true>(dtype);
+      if (tile_n == 128) return pick_dtype<128, 1, true>(tile_k, dtype);
+      if (tile_n == 256) return pick_dtype<256, 1, true>(tile_k, dtype);
     }
   } else if (cta_group == 2) {
     if (!glu) {
-      if (tile_n == 128) return pick_dtype<128, 2, false>(dtype);
-      if (tile_n == 256) return pick_dtype<256, 2, false>(dtype);
+      if (tile_n == 128) return pick_dtype<128, 2, false>(tile_k, dtype);
+      if (tile_n == 256) return pick_dtype<256, 2, false>(tile_k, dtype);
     } else {
-      if (tile_n == 128) return pick_dtype<128, 2, true>(dtype);
-      if (tile_n == 256) return pick_dtype<256, 2, true>(dtype);
+      if (tile_n == 128) return pick_dtype<128, 2, true>(tile_k, dtype);
+      if (tile_n == 256) return pick_dtype<256, 2, true>(tile_k, dtype);
     }
   }
   return nullptr;
+}
+
+// Opts a kernel into the full 227 KiB of dynamic shared memory, once per (kernel, device).
+cudaError_t allow_full_smem(KernelFn fn) {
+  static std::mutex mu;
+  static std::vector<std::pair<KernelFn, int>> done;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> lock(mu);
+  for (const auto& d : done)
+    if (d.first == fn && d.second == dev) return cudaSuccess;
+  e = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn),
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, kMaxDynamicSmem);
+  if (e == cudaSuccess) done.emplace_back(fn, dev);
+  return e;
 }
 
 int device_sm_count() {
@@ -620,6 +653,13 @@ unsigned long long wait_limit_ns() {
 }
 
 inline int cdiv(int a, int b) { return (a + b - 1) / b; }
+
+// Rows of A fetched per stage: a single-CTA tile over a problem with fewer than 128 rows only
+// needs (and only pays shared memory for) M rounded up to the 8-row swizzle group.
+inline int a_box_rows(const tnx_problem& p, const tnx_config& cfg) {
+  if (cfg.cta_group == 1 && p.m < kRowsPerCta) return ((p.m + 7) / 8) * 8;
+  return kRowsPerCta;
+}
 
 }  // namespace
 
@@ -668,7 +708,7 @@ int umma_query(const tnx_problem& p, tnx_config* cfg, tnx_resources* out) {
               cfg->split_k, cfg->group_m, cfg->tile_order);
     return TNX_ERR_INVALID;
   }
-  if (pick_kernel(cfg->tile_n, cfg->cta_group, glu, p.dtype) == nullptr) {
+  if (pick_kernel(cfg->tile_n, cfg->tile_k, cfg->cta_group, glu, p.dtype) == nullptr) {
     set_error("no kernel built for tile_n=%d cta_group=%d%s", cfg->tile_n, cfg->cta_group,
               glu ? " with a GLU epilogue" : "");
     return TNX_ERR_NOT_BUILT;
@@ -679,7 +719,7 @@ int umma_query(const tnx_problem& p, tnx_config* cfg, tnx_resources* out) {
   }
 
   const int load_n = cfg->tile_n / cfg->cta_group;
-  const int stage_bytes = (kRowsPerCta + load_n) * cfg->tile_k * 2;
+  const int stage_bytes = (a_box_rows(p, *cfg) + load_n) * cfg->tile_k * 2;
   const int fixed = 2 * kStagingBytes + kCtrlBytes + kAlignSlack;
   if (cfg->stages == 0) {
     int s = (kMaxDynamicSmem - fixed) / stage_bytes;
@@ -749,12 +789,13 @@ int umma_launch(const tnx_problem& p, const tnx_config& cfg, const tnx_resources
     set_error("tcgen05 path needs 16-byte aligned A, B and C base addresses");
     return TNX_ERR_INVALID;
   }
-  KernelFn fn = pick_kernel(cfg.tile_n, cfg.cta_group, glu, p.dtype);
+  KernelFn fn = pick_kernel(cfg.tile_n, cfg.tile_k, cfg.cta_group, glu, p.dtype);
   if (fn == nullptr) return TNX_ERR_NOT_BUILT;
 
   const int n_out = glu ? p.n / 2 : p.n;
   CUtensorMap ta, tb, tc;
-  int rc = make_tmap(&ta, a, p.dtype, p.k, p.m, p.stride_am, kAtomElems, kRowsPerCta, true);
+  const int a_rows = a_box_rows(p, cfg);
+  int rc = make_tmap(&ta, a, p.dtype, p.k, p.m, p.stride_am, kAtomElems, a_rows, true);
   if (rc != TNX_OK) return rc;
   rc = make_tmap(&tb, b, p.dtype, p.n, p.k, p.stride_bk, kAtomElems, cfg.tile_k, true);
   if (rc != TNX_OK) return rc;
@@ -772,6 +813,7 @@ int umma_launch(const tnx_problem& p, const tnx_config& cfg, const tnx_resources
   kp.split_k = res.split_k;
   kp.kb_per_slice = cdiv(kp.num_kb, res.split_k);
   kp.tile_k = cfg.tile_k;
+  kp.a_rows = a_rows;
   kp.stages = cfg.stages;
   kp.acc_stages = cfg.acc_stages;
   kp.group_m = cfg.group_m;
@@ -784,10 +826,9 @@ int umma_launch(const tnx_problem& p, const tnx_config& cfg, const tnx_resources
   kp.status = status_word;
   kp.timeout_ns = wait_limit_ns();
 
-  cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn),
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, res.smem_bytes);
+  cudaError_t e = allow_full_smem(fn);
   if (e != cudaSuccess) {
-    set_error("cudaFuncSetAttribute(%d B dynamic smem): %s", res.smem_bytes, cudaGetErrorString(e));
+    set_error("cudaFuncSetAttribute(%d B dynamic smem): %s", kMaxDynamicSmem, cudaGetErrorString(e));
     (void)cudaGetLastError();
     return TNX_ERR_CUDA;
   }

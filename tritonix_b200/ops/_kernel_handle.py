@@ -15,25 +15,6 @@ from typing import Callable, List
 import torch
 
 from tritonix_b200 import _cabi
-from tritonix_b200.utils.hilbert import hilbert_tile_table
-
-_table_cache: dict = {}
-
-
-def tile_table_for(device: torch.device) -> Callable[[int, int], torch.Tensor]:
-    """Returns a factory of Hilbert tile tables on ``device`` (cached per grid size)."""
-
-    def make(tiles_m: int, tiles_n: int) -> torch.Tensor:
-        key = (device.index, tiles_m, tiles_n)
-        table = _table_cache.get(key)
-        if table is None:
-            table = torch.tensor(hilbert_tile_table(tiles_m, tiles_n), dtype=torch.int32,
-                                 device=device)
-            _table_cache[key] = table
-        return table
-
-    return make
-
 
 class CudaKernel:
     """One entry of the kernel family.  ``epilogue`` is fixed per handle except for the GLU
@@ -75,7 +56,7 @@ class CudaKernel:
             # (tritonix/ops/swiglu.py:100-102); "sigmoid" is this package's addition.
             activation = cfg.pop("activation", "silu")
             epilogue = _cabi.ACTIVATIONS.get(activation, _cabi.EPI_GLU_LINEAR)
-        table = tile_table_for(a.device) if cfg.get("tile_order") in ("hilbert", "table") else None
+        table = cfg.pop("tile_table", None)
         return _cabi.launch_raw(a.device, a.dtype, a.data_ptr(), b.data_ptr(), c.data_ptr(),
                                 m, n, k, (stride_am, stride_ak, stride_bk, stride_bn, stride_cm,
                                           stride_cn), cfg, epilogue, table)
