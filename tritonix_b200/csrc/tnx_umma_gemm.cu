@@ -68,7 +68,14 @@ struct UmmaParams {
   int* counters;        // split-K: one arrival counter per 128-row output tile
   int* status;
   unsigned long long timeout_ns;
+  int flags;  // experiment switches (TNX_DEBUG_FLAGS), 0 in normal use
+  unsigned long long* trace;  // optional per-CTA timestamp slots (64 per CTA), nullptr in normal use
 };
+
+#define TNX_TRACE(slot)                                                                   \
+  do {                                                                                    \
+    if (p.trace != nullptr && (slot) < 64) p.trace[blockIdx.x * 64 + (slot)] = ptx::globaltimer_ns(); \
+  } while (0)
 
 // Control block at the end of dynamic shared memory.
 struct Ctrl {
@@ -201,6 +208,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   __syncthreads();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = ctrl->tmem_base;
+  if (threadIdx.x == 0) TNX_TRACE(0);
 
   // ------------------------------------------------------------------ roles
   if (warp == 0) {
@@ -252,12 +260,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               ptx::tma_load_2d_pair(b_dst + na * (TILE_K * kAtomBytes), &tmap_b,
                                     col0 + na * kAtomElems, k0, leader_bar);
           }
+          if (u == cluster_id && kb == kb0) TNX_TRACE(1);
           if (++stage == p.stages) {
             stage = 0;
             phase ^= 1u;
           }
         }
       }
+      TNX_TRACE(2);
       if (!ok && p.status != nullptr) atomicCAS(p.status, 0, kAbortProducer);
     }
   } else if (warp == 1) {
@@ -290,23 +300,39 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * TILE_N;
         uint32_t accumulate = 0;
+        TNX_TRACE(32 + (u - cluster_id) / num_clusters);
+        bool waited = false;  // experiment (flags & 8): the wait for this stage already happened
         for (int kb = kb0; kb < kb1; ++kb) {
-          const uint32_t full_bar = ptx::smem_u32(&ctrl->full[stage]);
-          if (!ptx::mbar_wait(full_bar, phase, abort_flag, p.timeout_ns)) {
-            ok = false;
-            break;
+          if (!waited) {
+            const uint32_t full_bar = ptx::smem_u32(&ctrl->full[stage]);
+            if (!ptx::mbar_wait(full_bar, phase, abort_flag, p.timeout_ns)) {
+              ok = false;
+              break;
+            }
           }
-          ptx::tc_fence_after_sync();
+          waited = false;
+          if (!(p.flags & 2)) ptx::tc_fence_after_sync();
           const uint32_t a_src = smem_a + stage * a_stage_bytes;
           const uint32_t b_src = smem_b + stage * b_stage_bytes;
 #pragma unroll
           for (int k16 = 0; k16 < TILE_K / 16; ++k16) {
+            if (k16 == TILE_K / 16 - 1 && (p.flags & 8) && kb + 1 < kb1) {
+              // look ahead: make sure the next slot has landed while MMAs are still queued
+              const int ns = stage + 1 == p.stages ? 0 : stage + 1;
+              const uint32_t nph = stage + 1 == p.stages ? phase ^ 1u : phase;
+              if (!ptx::mbar_wait(ptx::smem_u32(&ctrl->full[ns]), nph, abort_flag, p.timeout_ns)) {
+                ok = false;
+                break;
+              }
+              waited = true;
+            }
             const uint32_t a_addr = a_src + (k16 >> 2) * a_atom_bytes + (k16 & 3) * 32;
             const uint32_t b_addr = b_src + k16 * (16 * kAtomBytes);
             ptx::umma_f16<CTA_GROUP>(d_tmem, a_desc_hi | ((a_addr >> 4) & 0x3fffu),
                                      b_desc_hi | ((b_addr >> 4) & 0x3fffu), idesc, accumulate);
             accumulate = 1;
           }
+          if (!ok) break;
           // Frees this ring slot (in both CTAs of a pair) once the MMAs above have read it.
           if (CTA_GROUP == 1)
             ptx::umma_commit(ptx::smem_u32(&ctrl->empty[stage]));
@@ -327,6 +353,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           acc_phase ^= 1u;
         }
       }
+      TNX_TRACE(30);
       if (!ok && p.status != nullptr) atomicCAS(p.status, 0, kAbortMma);
     }
   } else {
@@ -354,13 +381,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const bool has_k = kb0 < p.num_kb;
 
       const uint32_t tf_bar = ptx::smem_u32(&ctrl->tmem_full[acc]);
-      bool got = !has_k || ptx::mbar_wait(tf_bar, acc_phase, abort_flag, p.timeout_ns);
+      bool got = !has_k || ptx::mbar_wait(tf_bar, acc_phase, abort_flag, p.timeout_ns,
+                                          (p.flags & 4) ? 500u : 0u);
       // All 128 epilogue threads continue or give up together (they share named barriers below).
       if (!ptx::named_barrier_all(kEpiBarrier, kEpiThreads, got)) {
         ok = false;
         break;
       }
       ptx::tc_fence_after_sync();
+      if (epi_tid == 0) TNX_TRACE(3 + (u - cluster_id) / num_clusters);
       const uint32_t t_acc = tmem_base + lane_sel + acc * TILE_N;
 
       bool reduce_from_partials = false;
@@ -402,6 +431,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
         ptx::named_barrier_sync(kEpiBarrier, kEpiThreads);
         reduce_from_partials = ctrl->is_last != 0;
+        if (epi_tid == 0) TNX_TRACE(28);
         if (!reduce_from_partials) {
           if (++acc == p.acc_stages) {
             acc = 0;
@@ -420,7 +450,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       // ---- write the tile: chunks of 128 bytes of output per row, through swizzled staging ----
       for (int chunk = 0; chunk < TILE_N / ACC_PER_CHUNK; ++chunk) {
         const int out_col = out_col0 + chunk * kAtomElems;
-        if (out_col >= p.n_out) break;
+        if (out_col >= p.n_out || (p.flags & 1)) break;
         const uint32_t buf = smem_out + (stores & 1u) * kStagingBytes;
         // The TMA store issued two chunks ago must have finished reading this buffer.
         if (epi_tid == 0) ptx::tma_store_wait_read<1>();
@@ -501,6 +531,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
     }
     if (epi_tid == 0) ptx::tma_store_wait_all<0>();
+    if (epi_tid == 0) TNX_TRACE(31);
     if (!ok && lane == 0 && p.status != nullptr) atomicCAS(p.status, 0, kAbortEpilogue);
   }
 
@@ -825,6 +856,12 @@ int umma_launch(const tnx_problem& p, const tnx_config& cfg, const tnx_resources
                           : nullptr;
   kp.status = status_word;
   kp.timeout_ns = wait_limit_ns();
+  {
+    const char* f = getenv("TNX_DEBUG_FLAGS");
+    kp.flags = f ? atoi(f) : 0;
+    const char* t = getenv("TNX_TRACE_PTR");
+    kp.trace = t ? reinterpret_cast<unsigned long long*>(strtoull(t, nullptr, 0)) : nullptr;
+  }
 
   cudaError_t e = allow_full_smem(fn);
   if (e != cudaSuccess) {
