@@ -74,3 +74,34 @@ def test_split_changes_only_the_summation_order():
         out, _ = run_gemm(a, b, {**T, "tile_n": 128, "split_k": s})
         errs.append(O.rel_err(out, ref))
     assert max(errs) <= 2e-3 and max(errs) - min(errs) < 5e-4  # no growth with the split factor
+
+
+@pytest.mark.parametrize("split_k", [1, 3])
+@pytest.mark.parametrize("n", [104, 100, 98, 9])
+def test_column_counts_inside_pitched_views(split_k, n):
+    """Column-sliced views: TMA clips in 16-byte units, so only N % 8 == 0 may take the tcgen05
+    path; other widths go to the strided kernel.  Either way nothing is written past column n."""
+    g = torch.Generator().manual_seed(n)
+    a = (torch.randn(72, 320, generator=g) * 320 ** -0.5).to(f16)
+    b_full = torch.randn(320, 128, generator=g).to(f16)
+    a_d, b_d = a.to(DEV), b_full.to(DEV)[:, :n]
+    c_full = torch.full((72, 104), float("nan"), device=DEV, dtype=f16)
+    c = c_full[:, :n]
+    res = _cabi.launch(a_d, b_d, c, {"tile_n": 64, "split_k": split_k})
+    _cabi.check_status(c.device)
+    assert res.kernel == (_cabi.KERNEL_TCGEN05 if n % 8 == 0 else _cabi.KERNEL_STRIDED)
+    assert_close(c.cpu(), O.matmul_oracle(a, b_full[:, :n]), f16)
+    assert torch.isnan(c_full[:, n:]).all()  # nothing written past column n
+
+
+def test_split_k_with_glu_epilogue():
+    x, w12 = seeded(200, 1024, 2 * 88, bf16, seed=21, b_scale=0.04)
+    w_d = torch.zeros(1024, 192, dtype=bf16)
+    w_d[:, :176] = w12
+    out = torch.full((200, 96), float("nan"), device=DEV, dtype=bf16)
+    z = out[:, :88]
+    res = _cabi.launch(x.to(DEV), w_d.to(DEV)[:, :176], z, {**T, "tile_n": 128, "split_k": 4}, _cabi.EPI_GLU_SILU)
+    _cabi.check_status(z.device)
+    assert res.split_k == 4
+    assert_close(z.cpu(), O.glu_oracle(x, w12, "silu"), bf16)
+    assert torch.isnan(out[:, 88:]).all()

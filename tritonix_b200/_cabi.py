@@ -167,6 +167,7 @@ def umma_eligible_tensors(a: torch.Tensor, b: torch.Tensor) -> bool:
     return (a.dtype in (torch.float16, torch.bfloat16) and a.dtype == b.dtype
             and a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and b.stride(1) == 1
             and a.stride(0) % 8 == 0 and b.stride(0) % 8 == 0 and b.shape[1] % 8 == 0
+            and a.shape[1] % 8 == 0
             and a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0)
 
 

@@ -90,13 +90,12 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t par
 // is set, and every other wait of the CTA returns false promptly.  Returns true on success.
 template <bool kClusterScope = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          uint64_t limit_ns, uint32_t backoff_ns = 0) {
+                                          uint64_t limit_ns) {
   if (kClusterScope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   for (uint32_t it = 1;; ++it) {
     if (kClusterScope ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity))
       return true;
-    if (backoff_ns) __nanosleep(backoff_ns);
     if ((it & 0xffu) == 0) {
       if (*abort_flag != 0) return false;
       if (globaltimer_ns() - t0 > limit_ns) {

@@ -64,18 +64,13 @@ struct UmmaParams {
   int tile_order;
   int epilogue;
   const int32_t* tile_table;
+  void* c_ptr;          // C base and row pitch (elements): the split-K fix-up stores C directly
+  long long ldc;
   float* partials;      // split-K: fp32 partial tiles
   int* counters;        // split-K: one arrival counter per 128-row output tile
   int* status;
   unsigned long long timeout_ns;
-  int flags;  // experiment switches (TNX_DEBUG_FLAGS), 0 in normal use
-  unsigned long long* trace;  // optional per-CTA timestamp slots (64 per CTA), nullptr in normal use
 };
-
-#define TNX_TRACE(slot)                                                                   \
-  do {                                                                                    \
-    if (p.trace != nullptr && (slot) < 64) p.trace[blockIdx.x * 64 + (slot)] = ptx::globaltimer_ns(); \
-  } while (0)
 
 // Control block at the end of dynamic shared memory.
 struct Ctrl {
@@ -208,7 +203,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   __syncthreads();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = ctrl->tmem_base;
-  if (threadIdx.x == 0) TNX_TRACE(0);
 
   // ------------------------------------------------------------------ roles
   if (warp == 0) {
@@ -260,14 +254,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               ptx::tma_load_2d_pair(b_dst + na * (TILE_K * kAtomBytes), &tmap_b,
                                     col0 + na * kAtomElems, k0, leader_bar);
           }
-          if (u == cluster_id && kb == kb0) TNX_TRACE(1);
           if (++stage == p.stages) {
             stage = 0;
             phase ^= 1u;
           }
         }
       }
-      TNX_TRACE(2);
       if (!ok && p.status != nullptr) atomicCAS(p.status, 0, kAbortProducer);
     }
   } else if (warp == 1) {
@@ -300,39 +292,23 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         ptx::tc_fence_after_sync();
         const uint32_t d_tmem = tmem_base + acc * TILE_N;
         uint32_t accumulate = 0;
-        TNX_TRACE(32 + (u - cluster_id) / num_clusters);
-        bool waited = false;  // experiment (flags & 8): the wait for this stage already happened
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!waited) {
-            const uint32_t full_bar = ptx::smem_u32(&ctrl->full[stage]);
-            if (!ptx::mbar_wait(full_bar, phase, abort_flag, p.timeout_ns)) {
-              ok = false;
-              break;
-            }
+          const uint32_t full_bar = ptx::smem_u32(&ctrl->full[stage]);
+          if (!ptx::mbar_wait(full_bar, phase, abort_flag, p.timeout_ns)) {
+            ok = false;
+            break;
           }
-          waited = false;
-          if (!(p.flags & 2)) ptx::tc_fence_after_sync();
+          ptx::tc_fence_after_sync();
           const uint32_t a_src = smem_a + stage * a_stage_bytes;
           const uint32_t b_src = smem_b + stage * b_stage_bytes;
 #pragma unroll
           for (int k16 = 0; k16 < TILE_K / 16; ++k16) {
-            if (k16 == TILE_K / 16 - 1 && (p.flags & 8) && kb + 1 < kb1) {
-              // look ahead: make sure the next slot has landed while MMAs are still queued
-              const int ns = stage + 1 == p.stages ? 0 : stage + 1;
-              const uint32_t nph = stage + 1 == p.stages ? phase ^ 1u : phase;
-              if (!ptx::mbar_wait(ptx::smem_u32(&ctrl->full[ns]), nph, abort_flag, p.timeout_ns)) {
-                ok = false;
-                break;
-              }
-              waited = true;
-            }
             const uint32_t a_addr = a_src + (k16 >> 2) * a_atom_bytes + (k16 & 3) * 32;
             const uint32_t b_addr = b_src + k16 * (16 * kAtomBytes);
             ptx::umma_f16<CTA_GROUP>(d_tmem, a_desc_hi | ((a_addr >> 4) & 0x3fffu),
                                      b_desc_hi | ((b_addr >> 4) & 0x3fffu), idesc, accumulate);
             accumulate = 1;
           }
-          if (!ok) break;
           // Frees this ring slot (in both CTAs of a pair) once the MMAs above have read it.
           if (CTA_GROUP == 1)
             ptx::umma_commit(ptx::smem_u32(&ctrl->empty[stage]));
@@ -353,7 +329,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           acc_phase ^= 1u;
         }
       }
-      TNX_TRACE(30);
       if (!ok && p.status != nullptr) atomicCAS(p.status, 0, kAbortMma);
     }
   } else {
@@ -381,22 +356,21 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const bool has_k = kb0 < p.num_kb;
 
       const uint32_t tf_bar = ptx::smem_u32(&ctrl->tmem_full[acc]);
-      bool got = !has_k || ptx::mbar_wait(tf_bar, acc_phase, abort_flag, p.timeout_ns,
-                                          (p.flags & 4) ? 500u : 0u);
+      bool got = !has_k || ptx::mbar_wait(tf_bar, acc_phase, abort_flag, p.timeout_ns);
       // All 128 epilogue threads continue or give up together (they share named barriers below).
       if (!ptx::named_barrier_all(kEpiBarrier, kEpiThreads, got)) {
         ok = false;
         break;
       }
       ptx::tc_fence_after_sync();
-      if (epi_tid == 0) TNX_TRACE(3 + (u - cluster_id) / num_clusters);
       const uint32_t t_acc = tmem_base + lane_sel + acc * TILE_N;
 
-      bool reduce_from_partials = false;
       if (p.split_k > 1) {
-        // ---- split-K: park the fp32 partial, the last slice to arrive sums all of them ----
-        const size_t unit_slot = static_cast<size_t>(row_tile * p.tiles_n + tn) * p.split_k + slice;
-        float* part = p.partials + unit_slot * (static_cast<size_t>(TILE_N) * kRowsPerCta);
+        // ---- split-K: park the fp32 partial; the last slice to arrive sums all of them ----
+        // Partials are row-major [128 rows][TILE_N] per (tile, slice).
+        const size_t tile_slot = static_cast<size_t>(row_tile * p.tiles_n + tn) * p.split_k;
+        constexpr size_t kPartFloats = static_cast<size_t>(TILE_N) * kRowsPerCta;
+        float* part = p.partials + (tile_slot + slice) * kPartFloats;
         const bool row_ok = row0 + row_in_tile < p.m;
         for (int c = 0; c < TILE_N / 32; ++c) {
           if (acc_col0 + c * 32 >= p.n) break;
@@ -404,9 +378,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           ptx::tmem_ld_32x32(t_acc + c * 32, r);
           ptx::tmem_ld_wait();
           if (row_ok) {
+            float4* dst = reinterpret_cast<float4*>(part + row_in_tile * TILE_N + c * 32);
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              __stcg(part + (c * 32 + j) * kRowsPerCta + row_in_tile, __uint_as_float(r[j]));
+            for (int j = 0; j < 8; ++j)
+              __stcg(dst + j, make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                          __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])));
           }
         }
         // TMEM buffer can be refilled now.
@@ -419,6 +395,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           else
             ptx::mbar_arrive_cluster(ptx::mapa(te, 0));
         }
+        if (++acc == p.acc_stages) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
         __threadfence();
         ptx::named_barrier_sync(kEpiBarrier, kEpiThreads);
         if (epi_tid == 0) {
@@ -430,27 +410,86 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           __threadfence();
         }
         ptx::named_barrier_sync(kEpiBarrier, kEpiThreads);
-        reduce_from_partials = ctrl->is_last != 0;
-        if (epi_tid == 0) TNX_TRACE(28);
-        if (!reduce_from_partials) {
-          if (++acc == p.acc_stages) {
-            acc = 0;
-            acc_phase ^= 1u;
-          }
-          continue;
-        }
+        const bool is_last = ctrl->is_last != 0;
+        if (!is_last) continue;
         __threadfence();
-      }
 
-      const float* part0 =
-          p.split_k > 1 ? p.partials + static_cast<size_t>(row_tile * p.tiles_n + tn) * p.split_k *
-                                           (static_cast<size_t>(TILE_N) * kRowsPerCta)
-                        : nullptr;
+        // Fix-up by the last arriver: all 128 threads walk the valid part of the tile in float4
+        // steps, several steps in flight, and add the slices in slice order (bit-reproducible).
+        // The result goes straight to C with 8-byte (plain) or 4-byte (GLU) stores.
+        const float* part0 = p.partials + tile_slot * kPartFloats;
+        const int rows_valid = min(kRowsPerCta, p.m - row0);
+        const int cols_valid = min(TILE_N, p.n - acc_col0);
+        const int vec_per_row = (cols_valid + 3) >> 2;
+        const int total_vec = rows_valid * vec_per_row;
+        constexpr int kInFlight = 4;
+        for (int base = epi_tid; base < total_vec; base += kEpiThreads * kInFlight) {
+          float4 sum[kInFlight];
+          int rr[kInFlight], cc[kInFlight];
+#pragma unroll
+          for (int u2 = 0; u2 < kInFlight; ++u2) {
+            const int idx = base + u2 * kEpiThreads;
+            const int safe = idx < total_vec ? idx : base;
+            rr[u2] = safe / vec_per_row;
+            cc[u2] = (safe - rr[u2] * vec_per_row) << 2;
+            sum[u2] = make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+          for (int s0 = 0; s0 < p.split_k; s0 += 4) {
+            float4 v[4][kInFlight];
+#pragma unroll
+            for (int ds = 0; ds < 4; ++ds)
+#pragma unroll
+              for (int u2 = 0; u2 < kInFlight; ++u2)
+                v[ds][u2] = s0 + ds < p.split_k
+                                ? __ldcg(reinterpret_cast<const float4*>(
+                                      part0 + (s0 + ds) * kPartFloats + rr[u2] * TILE_N + cc[u2]))
+                                : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int ds = 0; ds < 4; ++ds)
+#pragma unroll
+              for (int u2 = 0; u2 < kInFlight; ++u2) {
+                sum[u2].x += v[ds][u2].x;
+                sum[u2].y += v[ds][u2].y;
+                sum[u2].z += v[ds][u2].z;
+                sum[u2].w += v[ds][u2].w;
+              }
+          }
+#pragma unroll
+          for (int u2 = 0; u2 < kInFlight; ++u2) {
+            if (base + u2 * kEpiThreads >= total_vec) continue;
+            const size_t row_off = static_cast<size_t>(row0 + rr[u2]) * p.ldc;
+            const int left = cols_valid - cc[u2];  // valid accumulator columns from here on
+            uint16_t* c16 = reinterpret_cast<uint16_t*>(p.c_ptr);
+            if (GLU) {
+              const uint32_t z = pack2<BF16>(gate_act(sum[u2].x, p.epilogue) * sum[u2].y,
+                                             gate_act(sum[u2].z, p.epilogue) * sum[u2].w);
+              const size_t o = row_off + ((acc_col0 + cc[u2]) >> 1);
+              if (left >= 4) {
+                *reinterpret_cast<uint32_t*>(c16 + o) = z;
+              } else {  // n is even: exactly one (gate, up) pair is left
+                c16[o] = static_cast<uint16_t>(z & 0xffffu);
+              }
+            } else {
+              const uint32_t lo = pack2<BF16>(sum[u2].x, sum[u2].y);
+              const uint32_t hi = pack2<BF16>(sum[u2].z, sum[u2].w);
+              const size_t o = row_off + acc_col0 + cc[u2];
+              if (left >= 4) {
+                *reinterpret_cast<uint2*>(c16 + o) = make_uint2(lo, hi);
+              } else {
+                c16[o] = static_cast<uint16_t>(lo & 0xffffu);
+                if (left > 1) c16[o + 1] = static_cast<uint16_t>(lo >> 16);
+                if (left > 2) c16[o + 2] = static_cast<uint16_t>(hi & 0xffffu);
+              }
+            }
+          }
+        }
+        continue;
+      }
 
       // ---- write the tile: chunks of 128 bytes of output per row, through swizzled staging ----
       for (int chunk = 0; chunk < TILE_N / ACC_PER_CHUNK; ++chunk) {
         const int out_col = out_col0 + chunk * kAtomElems;
-        if (out_col >= p.n_out || (p.flags & 1)) break;
+        if (out_col >= p.n_out) break;
         const uint32_t buf = smem_out + (stores & 1u) * kStagingBytes;
         // The TMA store issued two chunks ago must have finished reading this buffer.
         if (epi_tid == 0) ptx::tma_store_wait_read<1>();
@@ -459,23 +498,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         for (int sub = 0; sub < ACC_PER_CHUNK / 32; ++sub) {
           const int col = chunk * ACC_PER_CHUNK + sub * 32;
           float v[32];
-          if (!reduce_from_partials) {
+          {
             uint32_t r[32];
             ptx::tmem_ld_32x32(t_acc + col, r);
             ptx::tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = 0.0f;
-            if (acc_col0 + col < p.n && row0 + row_in_tile < p.m) {
-              for (int s = 0; s < p.split_k; ++s) {  // fixed order => bit-reproducible sum
-                const float* src = part0 + static_cast<size_t>(s) * (TILE_N * kRowsPerCta) +
-                                   col * kRowsPerCta + row_in_tile;
-#pragma unroll
-                for (int j = 0; j < 32; ++j) v[j] += __ldcg(src + j * kRowsPerCta);
-              }
-            }
           }
           if (GLU) {
             // Columns come interleaved (gate_j, up_j): adjacent registers form one output.
@@ -513,17 +541,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         ++stores;
       }
 
-      if (!reduce_from_partials) {
-        // All tcgen05.ld of this accumulator are complete: hand the TMEM buffer back.
-        ptx::tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) {
-          const uint32_t te = ptx::smem_u32(&ctrl->tmem_empty[acc]);
-          if (CTA_GROUP == 1 || leader)
-            ptx::mbar_arrive(te);
-          else
-            ptx::mbar_arrive_cluster(ptx::mapa(te, 0));
-        }
+      // All tcgen05.ld of this accumulator are complete: hand the TMEM buffer back.
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) {
+        const uint32_t te = ptx::smem_u32(&ctrl->tmem_empty[acc]);
+        if (CTA_GROUP == 1 || leader)
+          ptx::mbar_arrive(te);
+        else
+          ptx::mbar_arrive_cluster(ptx::mapa(te, 0));
       }
       if (++acc == p.acc_stages) {
         acc = 0;
@@ -531,7 +557,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
     }
     if (epi_tid == 0) ptx::tma_store_wait_all<0>();
-    if (epi_tid == 0) TNX_TRACE(31);
     if (!ok && lane == 0 && p.status != nullptr) atomicCAS(p.status, 0, kAbortEpilogue);
   }
 
@@ -704,6 +729,9 @@ bool umma_eligible(const tnx_problem& p, const char** why) {
     w = "tcgen05 path needs row pitches that are multiples of 16 bytes";
   else if (p.k < 1 || p.m < 1 || p.n < 1)
     w = "empty problem";
+  else if ((p.k % 8) != 0 || (p.n % 8) != 0 || (p.epilogue != TNX_EPI_NONE && (p.n % 16) != 0))
+    // TMA clips and zero-fills in 16-byte units along the contiguous dimension
+    w = "tcgen05 path needs K, N (and N/2 for a GLU epilogue) to be multiples of 8 elements";
   else if (p.stride_am < p.k || p.stride_bk < p.n)
     w = "row pitch smaller than the row length";
   if (why) *why = w;
@@ -851,17 +879,13 @@ int umma_launch(const tnx_problem& p, const tnx_config& cfg, const tnx_resources
   kp.tile_order = cfg.tile_order;
   kp.epilogue = p.epilogue;
   kp.tile_table = tile_table;
+  kp.c_ptr = c;
+  kp.ldc = p.stride_cm;
   kp.counters = reinterpret_cast<int*>(workspace);
   kp.partials = workspace ? reinterpret_cast<float*>(static_cast<char*>(workspace) + kCounterBytes)
                           : nullptr;
   kp.status = status_word;
   kp.timeout_ns = wait_limit_ns();
-  {
-    const char* f = getenv("TNX_DEBUG_FLAGS");
-    kp.flags = f ? atoi(f) : 0;
-    const char* t = getenv("TNX_TRACE_PTR");
-    kp.trace = t ? reinterpret_cast<unsigned long long*>(strtoull(t, nullptr, 0)) : nullptr;
-  }
 
   cudaError_t e = allow_full_smem(fn);
   if (e != cudaSuccess) {
