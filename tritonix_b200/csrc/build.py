@@ -1,6 +1,7 @@
 """Builds libtritonix_b200.so (the C-ABI library) in-tree with nvcc for sm_100a.
 
-Usage: python -m tritonix_b200.csrc.build [--force] [--verbose]
+Usage: python tritonix_b200/csrc/build.py [--force] [--verbose]
+(run as a script: importing the tritonix_b200 package itself requires the built library)
 """
 from __future__ import annotations
 
