@@ -3,9 +3,8 @@
  * for NVIDIA B200 (sm_100a).
  *
  * Every entry point takes plain pointers and sizes.  The library never allocates or frees
- * device memory (with the single documented exception of nothing: outputs, the split-K
- * workspace and the status word all belong to the caller) and never synchronises the host
- * with the device unless the function's comment says so.  Kernels are enqueued on the
+ * device memory (outputs, the split-K workspace and the status word all belong to the caller)
+ * and never synchronises the host with the device unless the function's comment says so.  Kernels are enqueued on the
  * stream handle that is passed in (a cudaStream_t cast to void*; NULL = default stream).
  *
  * Status codes (returned by every function that returns int):
@@ -153,6 +152,40 @@ int tnx_gemm(const tnx_problem* problem, const tnx_config* config, const void* a
 int tnx_glu(const tnx_problem* problem, const tnx_config* config, int activation, const void* x,
             const void* w12, void* z, const int32_t* tile_table, int32_t* status_word,
             void* stream);
+
+/* Size of the split-K scratch built into the library (per GPU): 64 KiB of tile counters plus
+ * 16 MiB of fp32 partial tiles. */
+#define TNX_STATIC_SCRATCH_BYTES (16u * 1024u * 1024u + 65536u)
+
+/*
+ * Split-K GEMM for callers that cannot provide a workspace.  No counterpart in the reference:
+ * its split-K accumulates into C with atomics and needs no scratch
+ * (tritonix/ops/matmul.py:195-202); the ordered reduction here does.
+ *
+ * Same computation and arguments as tnx_gemm with epilogue, split_k and the other config fields
+ * honoured, but the scratch is a fixed array inside the library instead of a caller-owned
+ * buffer, and the call performs no device-memory allocation of any kind (no cudaMalloc, no
+ * cudaFree, no allocating library routine).  It is meant for hosts that must not allocate once
+ * they are running — e.g. a serving runtime whose device memory is fully owned by its own
+ * arena, or a latency-critical loop that cannot afford the device-wide synchronisation an
+ * allocation may cause.
+ *
+ * Limits and rules:
+ *   - the scratch the problem needs at the chosen split_k (tnx_resources.workspace_bytes from
+ *     tnx_gemm_query) must not exceed TNX_STATIC_SCRATCH_BYTES, else TNX_ERR_INVALID with the
+ *     required and available sizes in tnx_last_error(); the array costs that much memory on
+ *     every GPU that loads the library, for the life of the process;
+ *   - only the tcgen05 kernel family is served (operands that would need the strided kernel are
+ *     rejected with TNX_ERR_INVALID); tile_order TNX_ORDER_TABLE is not available;
+ *   - the first call on each device looks up the array's device address (a one-time set-up
+ *     under that device); make that first call before any stream capture begins;
+ *   - all calls on a device share the one array, which still holds the previous call's
+ *     contents: the counters are cleared on `stream` at the start of every call, the rest is
+ *     overwritten before it is read.  Two calls whose kernels can overlap on the GPU (different
+ *     streams, no ordering between them) race on it — order them.
+ */
+int tnx_gemm_splitk_static(const tnx_problem* problem, const tnx_config* config, const void* a,
+                           const void* b, void* c, int32_t* status_word, void* stream);
 
 /*
  * Synchronises `stream`, copies *status_word to the host and returns TNX_OK if it is zero,

@@ -66,15 +66,20 @@ class Resources(ctypes.Structure):
 
 
 EXPORTS = ("tnx_version", "tnx_last_error", "tnx_sm_count", "tnx_gemm_query", "tnx_gemm",
-           "tnx_glu", "tnx_read_status")
+           "tnx_glu", "tnx_read_status", "tnx_gemm_splitk_static")
+STATIC_SCRATCH_BYTES = 16 * 1024 * 1024 + 65536
 
 
 def _load() -> ctypes.CDLL:
     if not _LIB_PATH.exists():
         raise ImportError(
-            f"{_LIB_PATH} is missing: build it with `python -m tritonix_b200.csrc.build` "
+            f"{_LIB_PATH} is missing: build it with `python tritonix_b200/csrc/build.py` "
             "(needs nvcc). tritonix_b200 has no CPU or PyTorch fallback.")
     lib = ctypes.CDLL(str(_LIB_PATH))
+    missing = [name for name in EXPORTS if not hasattr(lib, name)]
+    if missing:
+        raise ImportError(f"{_LIB_PATH} is out of date (no {', '.join(missing)}): rebuild it with "
+                          "`python tritonix_b200/csrc/build.py`")
     lib.tnx_version.restype = ctypes.c_char_p
     lib.tnx_last_error.restype = ctypes.c_char_p
     lib.tnx_sm_count.restype = ctypes.c_int
@@ -89,6 +94,10 @@ def _load() -> ctypes.CDLL:
     lib.tnx_glu.argtypes = [ctypes.POINTER(Problem), ctypes.POINTER(Config), ctypes.c_int,
                             ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                             ctypes.c_void_p, ctypes.c_void_p]
+    lib.tnx_gemm_splitk_static.restype = ctypes.c_int
+    lib.tnx_gemm_splitk_static.argtypes = [ctypes.POINTER(Problem), ctypes.POINTER(Config),
+                                           ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                           ctypes.c_void_p, ctypes.c_void_p]
     lib.tnx_read_status.restype = ctypes.c_int
     lib.tnx_read_status.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32),
                                     ctypes.c_void_p]
@@ -309,3 +318,23 @@ def launch(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, cfg: dict | None =
         raise ValueError(f"output must be {(m, n_out)}, got {tuple(c.shape)}")
     return launch_raw(a.device, a.dtype, a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k,
                       (*a.stride(), *b.stride(), *c.stride()), cfg, epilogue, tile_table)
+
+
+def launch_splitk_static(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor,
+                         cfg: dict | None = None, epilogue: int = EPI_NONE) -> None:
+    """C = epilogue(A.B) through ``tnx_gemm_splitk_static``: the split-K scratch is the fixed
+    array inside the library, so nothing is allocated by this call or by the library (``c`` is
+    the caller's).  For hosts that must not allocate device memory while running; problems
+    whose scratch exceeds ``STATIC_SCRATCH_BYTES`` raise ``ValueError``.  Calls on one device
+    share the array and must be ordered on the GPU."""
+    require_cuda(a, b, c)
+    m, k = a.shape
+    n = b.shape[1]
+    problem = make_problem(m, n, k, a.dtype, (*a.stride(), *b.stride(), *c.stride()), epilogue)
+    config = make_config(cfg)
+    stream = torch.cuda.current_stream(a.device).cuda_stream
+    with torch.cuda.device(a.device):
+        rc = lib.tnx_gemm_splitk_static(ctypes.byref(problem), ctypes.byref(config), a.data_ptr(),
+                                        b.data_ptr(), c.data_ptr(),
+                                        status_word(a.device).data_ptr(), stream)
+    raise_for(rc)

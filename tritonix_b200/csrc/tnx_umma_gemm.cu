@@ -22,6 +22,8 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <string.h>
+
 #include <mutex>
 #include <utility>
 #include <vector>
@@ -916,3 +918,98 @@ int umma_launch(const tnx_problem& p, const tnx_config& cfg, const tnx_resources
 }
 
 }  // namespace tnx
+
+// ---------------------------------------------------------------------------------------------
+// Split-K GEMM on scratch that lives inside the library
+// ---------------------------------------------------------------------------------------------
+// Some hosts cannot hand this library a workspace: a serving runtime that gave its whole
+// device-memory budget to its own arena at start-up and forbids further driver allocations, or
+// a latency-critical loop where an allocation call is unacceptable because cudaMalloc may
+// synchronise the whole device.  For them the split-K scratch is this fixed array, which every
+// GPU that loads the library carries until the process exits.
+static __device__ __align__(256) unsigned char tnx_builtin_scratch[TNX_STATIC_SCRATCH_BYTES];
+
+namespace {
+
+// `tnx_builtin_scratch` names a host-side handle here, not a device address.  The address the
+// kernel needs is looked up once per device, with that device current.
+int builtin_scratch_address(void** out) {
+  static std::mutex mu;
+  static void* address[64] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    tnx::set_error("cannot identify the current device: %s", cudaGetErrorString(e));
+    (void)cudaGetLastError();
+    return TNX_ERR_CUDA;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  if (address[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, tnx_builtin_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      tnx::set_error("cudaGetSymbolAddress(built-in scratch) failed on device %d: %s", dev,
+                     cudaGetErrorString(e));
+      (void)cudaGetLastError();
+      return TNX_ERR_CUDA;
+    }
+    address[dev] = ptr;
+  }
+  *out = address[dev];
+  return TNX_OK;
+}
+
+}  // namespace
+
+extern "C" int tnx_gemm_splitk_static(const tnx_problem* problem, const tnx_config* config,
+                                      const void* a, const void* b, void* c,
+                                      int32_t* status_word, void* stream) {
+  tnx_resources res;
+  int rc = tnx_gemm_query(problem, config, &res);  // full validation of problem and config
+  if (rc != TNX_OK) return rc;
+  if (res.kernel != TNX_KERNEL_TCGEN05) {
+    tnx::set_error("tnx_gemm_splitk_static runs the tcgen05 kernel only and these operands do not "
+                   "qualify for it (fp16/bf16, row-major, 16-byte pitches, K and N multiples of 8)");
+    return TNX_ERR_INVALID;
+  }
+  tnx_config cfg;
+  if (config != nullptr)
+    cfg = *config;
+  else
+    memset(&cfg, 0, sizeof(cfg));
+  rc = tnx::umma_query(*problem, &cfg, &res);  // same answer, plus the defaults filled into cfg
+  if (rc != TNX_OK) return rc;
+  if (cfg.tile_order == TNX_ORDER_TABLE) {
+    tnx::set_error("tnx_gemm_splitk_static takes no tile table; use a grouped or serpentine order");
+    return TNX_ERR_INVALID;
+  }
+  if (res.workspace_bytes > static_cast<int64_t>(TNX_STATIC_SCRATCH_BYTES)) {
+    tnx::set_error("this problem needs %lld bytes of split-K scratch at split_k=%d but the built-in "
+                   "scratch holds %lld; lower split_k or tile_n, or call tnx_gemm with a workspace "
+                   "of your own",
+                   static_cast<long long>(res.workspace_bytes), res.split_k,
+                   static_cast<long long>(TNX_STATIC_SCRATCH_BYTES));
+    return TNX_ERR_INVALID;
+  }
+  if (problem->m == 0 || problem->n == 0) return TNX_OK;
+  if (a == nullptr || b == nullptr || c == nullptr) {
+    tnx::set_error("NULL operand pointer");
+    return TNX_ERR_INVALID;
+  }
+  void* scratch = nullptr;
+  rc = builtin_scratch_address(&scratch);
+  if (rc != TNX_OK) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (res.split_k > 1) {
+    // The array keeps whatever the previous call (or an interrupted one) left behind; the tile
+    // counters are the only part that has to start at zero.
+    const size_t counters = static_cast<size_t>(res.tiles_m) * cfg.cta_group * res.tiles_n * 4;
+    cudaError_t e = cudaMemsetAsync(scratch, 0, (counters + 255) & ~static_cast<size_t>(255), s);
+    if (e != cudaSuccess) {
+      tnx::set_error("clearing the split-K counters failed: %s", cudaGetErrorString(e));
+      (void)cudaGetLastError();
+      return TNX_ERR_CUDA;
+    }
+  }
+  return tnx::umma_launch(*problem, cfg, res, a, b, c, scratch, nullptr, status_word, s);
+}
