@@ -54,7 +54,7 @@ GLU_CFG = {"kernel": "tcgen05", "tile_n": 256, "tile_k": 128, "stages": 3, "cta_
 
 # DRAM traffic of the dominant kernel per launch, from the ncu captures summarised under
 # profiles/ (None until a capture of that workload exists).
-NCU_TRAFFIC_BYTES = {"gemm": 1_389_138_048, "splitk": None, "glu": None, "mlp": None}
+NCU_TRAFFIC_BYTES = {"gemm": 1_389_138_048, "splitk": 123_602_432, "glu": 885_355_520, "mlp": None}
 
 
 def measured_peaks():
@@ -252,6 +252,8 @@ def time_steps(fn, steps, warmup, barrier):
 def cpu_baseline_sample(workload, seconds_target=15.0):
     """The reference's CPU path on a bounded sample of the workload, all host threads."""
     from oracle import contraction as O
+    if torch.get_num_threads() < (os.cpu_count() or 1):
+        torch.set_num_threads(os.cpu_count() or 1)
     threads = torch.get_num_threads()
     g = torch.Generator().manual_seed(0)
     w = WORKLOADS[workload]
@@ -305,6 +307,8 @@ def run_reference(args, rank):
     """CPU arm: rank 0 only; every step is one pass over the bounded sample."""
     if rank != 0:
         return
+    # launchers such as torchrun pin OMP_NUM_THREADS=1; the CPU arm uses every host core
+    torch.set_num_threads(os.cpu_count() or 1)
     metric, unit = metric_of(args.workload)
     base = cpu_baseline_sample(args.workload, seconds_target=2.0)
     fn = base["fn"]

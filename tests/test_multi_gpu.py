@@ -1,0 +1,67 @@
+"""Two-GPU runs of the sharded layouts with the real kernels and NCCL: the tensor-parallel
+SwiGLU MLP (column-parallel fused gate/up, row-parallel down projection, one chunked
+all-reduce) and the row-sharded GEMM (no collective).  Skipped with fewer than two GPUs."""
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")]
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out_dir):
+    import torch.distributed as dist
+
+    import tritonix_b200 as tnx
+    from oracle import contraction as O
+    from tritonix_b200.distributed import (TensorParallelSwiGLU, shard_bounds, shard_mlp_weights,
+                                           shard_rows, sharded_matmul)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), TRITONIX_B200_TUNE="0")
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        g = torch.Generator().manual_seed(99)  # identical global tensors on every rank
+        m, d, ff = 2048, 512, 2048
+        bf16 = torch.bfloat16
+        x = torch.randn(m, d, generator=g).to(bf16)
+        wg = (torch.randn(d, ff, generator=g) * 0.05).to(bf16)
+        wu = (torch.randn(d, ff, generator=g) * 0.05).to(bf16)
+        wd = (torch.randn(ff, d, generator=g) * 0.05).to(bf16)
+        w12, wdr = shard_mlp_weights(wg, wu, wd, rank, world)
+        mlp = TensorParallelSwiGLU(w12.to(dev), wdr.to(dev), chunks=4)
+        y = mlp(x.to(dev))
+        tnx.check_status(dev)
+        ref = O.swiglu_mlp_oracle(x, torch.stack((wg, wu), 2).reshape(d, 2 * ff), wd)
+        err_mlp = O.rel_err(y.cpu(), ref)
+        gathered = [torch.empty_like(y) for _ in range(world)]
+        dist.all_gather(gathered, y)
+        same = all(torch.equal(gathered[0], t) for t in gathered)   # every rank holds the same sum
+
+        b = (torch.randn(d, 768, generator=g) * d ** -0.5).to(bf16)
+        rows = shard_rows(x, rank, world).to(dev)
+        c_rows = sharded_matmul(rows, b.to(dev))
+        tnx.check_status(dev)
+        lo, hi = shard_bounds(m, rank, world)
+        err_mm = O.rel_err(c_rows.cpu(), O.matmul_oracle(x[lo:hi], b))
+        torch.save({"err_mlp": err_mlp, "err_mm": err_mm, "same": same},
+                   os.path.join(out_dir, f"r{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tensor_parallel_mlp_and_row_sharded_gemm(tmp_path):
+    import torch.multiprocessing as mp
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        res = torch.load(tmp_path / f"r{r}.pt")
+        assert res["err_mlp"] <= 8e-3 and res["err_mm"] <= 8e-3 and res["same"], res
