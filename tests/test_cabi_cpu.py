@@ -95,9 +95,16 @@ def test_family_selection_and_aliases():
 
 
 def test_split_k_resources():
+    # skinny M, 2/4/8 slices: the slices form a cluster and exchange partials through shared
+    # memory, so no workspace is needed
     r = q(64, 4096, 14336, {"tile_n": 128, "split_k": 4, "stages": 6}, dtype=torch.float16)
-    assert r.split_k == 4 and r.grid == 128
-    assert r.workspace_bytes == 65536 + 32 * 4 * 128 * 128 * 4
+    assert r.split_k == 4 and r.grid == 128 and r.workspace_bytes == 0
+    # otherwise: 64 KiB of counters + one fp32 partial tile per (tile, slice)
+    r = q(64, 4096, 14336, {"tile_n": 128, "split_k": 3, "stages": 6}, dtype=torch.float16)
+    assert r.split_k == 3 and r.grid == 96
+    assert r.workspace_bytes == 65536 + 32 * 3 * 128 * 128 * 4
+    r = q(256, 4096, 14336, {"tile_n": 128, "split_k": 4}, dtype=torch.float16)
+    assert r.workspace_bytes == 65536 + 2 * 32 * 4 * 128 * 128 * 4
     # never more slices than k-blocks, and no empty slice
     assert q(128, 128, 64 * 3, {"tile_n": 128, "split_k": 8}).split_k == 3
     assert q(128, 128, 64 * 5, {"tile_n": 128, "split_k": 4}).split_k == 3

@@ -105,3 +105,27 @@ def test_split_k_with_glu_epilogue():
     assert res.split_k == 4
     assert_close(z.cpu(), O.glu_oracle(x, w12, "silu"), bf16)
     assert torch.isnan(out[:, 88:]).all()
+
+
+@pytest.mark.parametrize("m,n,k,split_k,tile_n", [(64, 1024, 2048, 4, 128), (64, 512, 4096, 8, 128), (8, 256, 1024, 2, 256),
+                                                  (128, 256, 2048, 4, 64), (40, 136, 1024, 4, 128), (300, 192, 1536, 2, 64)])
+def test_cluster_exchange_matches_workspace_path(m, n, k, split_k, tile_n, monkeypatch):
+    """2, 4 or 8 slices of a small tile exchange partials through cluster shared memory; the
+    result must be bit-identical to the workspace path (same fp32 sum, same order)."""
+    a, b = seeded(m, k, n, f16, seed=m + n)
+    cfg = {**T, "tile_n": tile_n, "split_k": split_k}
+    prob = _cabi.make_problem(m, n, k, f16, (k, 1, n, 1, n, 1))
+    assert _cabi.query(prob, _cabi.make_config(cfg)).workspace_bytes == 0   # cluster exchange
+    out_cluster, _ = run_gemm(a, b, cfg)
+    out_cluster2, _ = run_gemm(a, b, cfg)
+    assert_close(out_cluster, O.splitk_oracle(a, b, split_k), f16)
+    assert torch.equal(out_cluster, out_cluster2)
+    monkeypatch.setenv("TNX_NO_CLUSTER_SPLITK", "1")
+    _cabi._plans.clear()
+    try:
+        assert _cabi.query(prob, _cabi.make_config(cfg)).workspace_bytes > 0
+        out_ws, _ = run_gemm(a, b, cfg)
+    finally:
+        monkeypatch.delenv("TNX_NO_CLUSTER_SPLITK")
+        _cabi._plans.clear()
+    assert torch.equal(out_cluster, out_ws)

@@ -34,7 +34,7 @@ def call_static(a, b, c, cfg, epilogue=_cabi.EPI_NONE):
 
 
 @pytest.mark.parametrize("m,n,k,dtype,cfg", [
-    (64, 1024, 3584, f16, {"tile_n": 128, "tile_k": 128, "split_k": 4, "stages": 3}),
+    (64, 1024, 3584, f16, {"tile_n": 128, "tile_k": 128, "split_k": 6, "stages": 3}),
     (200, 520, 1000, bf16, {"tile_n": 64, "split_k": 3}),
 ])
 def test_matches_regular_entry_point_twice_in_a_row(m, n, k, dtype, cfg):

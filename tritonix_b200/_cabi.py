@@ -12,7 +12,11 @@ from pathlib import Path
 
 import torch
 
-_LIB_PATH = Path(__file__).resolve().parent / "lib" / "libtritonix_b200.so"
+import os
+
+# TRITONIX_B200_LIB points at an alternative build of the library (e.g. a development build).
+_LIB_PATH = Path(os.environ.get("TRITONIX_B200_LIB") or
+                 Path(__file__).resolve().parent / "lib" / "libtritonix_b200.so")
 
 # ---- constants mirrored from include/tritonix_b200.h
 OK, ERR_INVALID, ERR_RESOURCES, ERR_NOT_BUILT, ERR_CUDA, ERR_DEVICE = range(6)

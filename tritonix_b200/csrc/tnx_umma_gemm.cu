@@ -58,6 +58,8 @@ struct UmmaParams {
   int num_kb;           // K blocks of tile_k in total
   int kb_per_slice;     // K blocks per split-K slice
   int split_k;
+  int cluster_split;    // > 0: the split_k slices of a tile form one cluster and exchange their
+                        // partials through distributed shared memory (no workspace)
   int tile_k;
   int a_rows;           // rows of A that TMA brings in per stage (128, or fewer for a skinny M)
   int stages;
@@ -72,7 +74,21 @@ struct UmmaParams {
   int* counters;        // split-K: one arrival counter per 128-row output tile
   int* status;
   unsigned long long timeout_ns;
+#ifdef TNX_DEV_TRACE
+  unsigned long long* trace;  // development builds only: 256 timestamp slots per CTA
+#endif
 };
+
+// Development aid, compiled only with -DTNX_DEV_TRACE: records %globaltimer into a per-CTA slot.
+#ifdef TNX_DEV_TRACE
+#define TNX_TRACE(slot)                                                                       \
+  do {                                                                                        \
+    if (p.trace != nullptr && (slot) < 256)                                                   \
+      p.trace[blockIdx.x * 256 + (slot)] = ptx::globaltimer_ns();                             \
+  } while (0)
+#else
+#define TNX_TRACE(slot) do { } while (0)
+#endif
 
 // Control block at the end of dynamic shared memory.
 struct Ctrl {
@@ -80,6 +96,8 @@ struct Ctrl {
   uint64_t empty[kMaxStages];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
+  uint64_t xchg_full;   // cluster split-K: every slice's partial is in its shared memory
+  uint64_t xchg_free;   // cluster split-K: every slice has finished reading the partials
   uint32_t tmem_base;
   int abort;
   int is_last;
@@ -136,6 +154,36 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
                : "memory");
 }
 
+// Split-K fix-up output: four summed accumulator columns of one row -> epilogue -> C.
+// `left` = valid accumulator columns from `acc_col` on (a ragged N leaves fewer than four).
+template <bool GLU, bool BF16>
+__device__ __forceinline__ void store_fixup(const UmmaParams& p, int row, int acc_col, int left,
+                                            const float4& sum) {
+  const size_t row_off = static_cast<size_t>(row) * p.ldc;
+  uint16_t* c16 = reinterpret_cast<uint16_t*>(p.c_ptr);
+  if (GLU) {
+    const uint32_t z = pack2<BF16>(gate_act(sum.x, p.epilogue) * sum.y,
+                                   gate_act(sum.z, p.epilogue) * sum.w);
+    const size_t o = row_off + (acc_col >> 1);
+    if (left >= 4) {
+      *reinterpret_cast<uint32_t*>(c16 + o) = z;
+    } else {  // n is even: exactly one (gate, up) pair is left
+      c16[o] = static_cast<uint16_t>(z & 0xffffu);
+    }
+  } else {
+    const uint32_t lo = pack2<BF16>(sum.x, sum.y);
+    const uint32_t hi = pack2<BF16>(sum.z, sum.w);
+    const size_t o = row_off + acc_col;
+    if (left >= 4) {
+      *reinterpret_cast<uint2*>(c16 + o) = make_uint2(lo, hi);
+    } else {
+      c16[o] = static_cast<uint16_t>(lo & 0xffffu);
+      if (left > 1) c16[o + 1] = static_cast<uint16_t>(lo >> 16);
+      if (left > 2) c16[o + 2] = static_cast<uint16_t>(hi & 0xffffu);
+    }
+  }
+}
+
 template <int TILE_N, int TILE_K, int CTA_GROUP, bool GLU, bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -164,11 +212,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const uint32_t cta_rank = CTA_GROUP == 2 ? ptx::cluster_ctarank() : 0u;
+  // Cluster layouts: CTA pair (CTA_GROUP == 2), or the K slices of one tile (cluster_split).
+  const bool xchg = CTA_GROUP == 1 && p.cluster_split > 0;
+  const uint32_t cluster_size = xchg ? static_cast<uint32_t>(p.cluster_split) : CTA_GROUP;
+  const uint32_t cluster_rank = (CTA_GROUP == 2 || xchg) ? ptx::cluster_ctarank() : 0u;
+  const uint32_t cta_rank = CTA_GROUP == 2 ? cluster_rank : 0u;  // position inside a CTA pair
   const bool leader = cta_rank == 0;
-  const int cluster_id = blockIdx.x / CTA_GROUP;
-  const int num_clusters = gridDim.x / CTA_GROUP;
-  const int total_units = p.tiles_m * p.tiles_n * p.split_k;
+  const int cluster_id = blockIdx.x / cluster_size;
+  const int num_clusters = gridDim.x / cluster_size;
+  // Work units: (tile, slice) pairs, or whole tiles when the cluster's CTAs are the slices.
+  const int total_units = p.tiles_m * p.tiles_n * (xchg ? 1 : p.split_k);
   const uint32_t tmem_cols_needed = p.acc_stages * TILE_N;
   uint32_t tmem_alloc_cols = 32;
   while (tmem_alloc_cols < tmem_cols_needed) tmem_alloc_cols <<= 1;
@@ -188,12 +241,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       ptx::mbar_init(ptx::smem_u32(&ctrl->tmem_full[a]), 1);
       ptx::mbar_init(ptx::smem_u32(&ctrl->tmem_empty[a]), 4 * CTA_GROUP);  // one arrive per epilogue warp
     }
+    ptx::mbar_init(ptx::smem_u32(&ctrl->xchg_full), xchg ? cluster_size : 1);
+    ptx::mbar_init(ptx::smem_u32(&ctrl->xchg_free), xchg ? cluster_size : 1);
     ctrl->abort = 0;
     ctrl->is_last = 0;
     ptx::fence_mbar_init();
   }
   __syncwarp();
-  if (CTA_GROUP == 2) {  // the peer's barriers must exist before anything signals them
+  if (CTA_GROUP == 2 || xchg) {  // the peers' barriers must exist before anything signals them
     ptx::cluster_arrive();
     ptx::cluster_wait();
   }
@@ -205,6 +260,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   __syncthreads();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = ctrl->tmem_base;
+  if (threadIdx.x == 0) TNX_TRACE(0);
 
   // ------------------------------------------------------------------ roles
   if (warp == 0) {
@@ -215,8 +271,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const uint32_t stage_tx = static_cast<uint32_t>(a_stage_bytes + b_stage_bytes) * CTA_GROUP;
       bool ok = true;
       for (int u = cluster_id; u < total_units && ok; u += num_clusters) {
-        const int t = u / p.split_k;
-        const int slice = u - t * p.split_k;
+        const int t = xchg ? u : u / p.split_k;
+        const int slice = xchg ? static_cast<int>(cluster_rank) : u - t * p.split_k;
         int tm, tn;
         tile_coords(p, t, tm, tn);
         const int row0 = (tm * CTA_GROUP + static_cast<int>(cta_rank)) * kRowsPerCta;
@@ -256,12 +312,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               ptx::tma_load_2d_pair(b_dst + na * (TILE_K * kAtomBytes), &tmap_b,
                                     col0 + na * kAtomElems, k0, leader_bar);
           }
+          if (u == cluster_id) TNX_TRACE(64 + (kb - kb0));
           if (++stage == p.stages) {
             stage = 0;
             phase ^= 1u;
           }
         }
       }
+      TNX_TRACE(2);
       if (!ok && p.status != nullptr) atomicCAS(p.status, 0, kAbortProducer);
     }
   } else if (warp == 1) {
@@ -282,8 +340,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int u = cluster_id; u < total_units && ok; u += num_clusters) {
-        const int t = u / p.split_k;
-        const int slice = u - t * p.split_k;
+        const int slice = xchg ? static_cast<int>(cluster_rank) : u % p.split_k;
         const int kb0 = slice * p.kb_per_slice;
         const int kb1 = min(kb0 + p.kb_per_slice, p.num_kb);
         const uint32_t te_bar = ptx::smem_u32(&ctrl->tmem_empty[acc]);
@@ -301,6 +358,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             break;
           }
           ptx::tc_fence_after_sync();
+          if (u == cluster_id) TNX_TRACE(128 + (kb - kb0));
           const uint32_t a_src = smem_a + stage * a_stage_bytes;
           const uint32_t b_src = smem_b + stage * b_stage_bytes;
 #pragma unroll
@@ -331,6 +389,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           acc_phase ^= 1u;
         }
       }
+      TNX_TRACE(3);
       if (!ok && p.status != nullptr) atomicCAS(p.status, 0, kAbortMma);
     }
   } else {
@@ -344,10 +403,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     int acc = 0;
     uint32_t acc_phase = 0;
     uint32_t stores = 0;  // staging buffers used so far (selects the buffer)
+    uint32_t xchg_round = 0;  // tiles this cluster has exchanged so far (barrier parity)
     bool ok = true;
     for (int u = cluster_id; u < total_units && ok; u += num_clusters) {
-      const int t = u / p.split_k;
-      const int slice = u - t * p.split_k;
+      const int t = xchg ? u : u / p.split_k;
+      const int slice = xchg ? static_cast<int>(cluster_rank) : u - t * p.split_k;
       int tm, tn;
       tile_coords(p, t, tm, tn);
       const int row_tile = tm * CTA_GROUP + static_cast<int>(cta_rank);  // 128-row tile index
@@ -365,7 +425,114 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         break;
       }
       ptx::tc_fence_after_sync();
+      if (epi_tid == 0 && u == cluster_id) TNX_TRACE(4);
       const uint32_t t_acc = tmem_base + lane_sel + acc * TILE_N;
+
+      if (xchg) {
+        // ---- split-K inside a cluster: the S slices of this tile are the S CTAs of the cluster.
+        // Each parks its fp32 partial in its own shared memory (the staging area), all of them
+        // meet on an mbarrier, and each then sums ITS share of the tile from all S shared
+        // memories (slice order, so the result is bit-reproducible) and stores it to C.
+        constexpr uint32_t kChunkMask = TILE_N / 4 - 1;  // 16-byte chunks per row, XOR-swizzled by row
+        const uint32_t S = cluster_size;
+        const uint32_t full_bar = ptx::smem_u32(&ctrl->xchg_full);
+        const uint32_t free_bar = ptx::smem_u32(&ctrl->xchg_free);
+        if (xchg_round > 0) {  // peers must be done reading the previous partial
+          const bool got_free = ptx::mbar_wait<true>(free_bar, (xchg_round - 1) & 1u, abort_flag, p.timeout_ns);
+          if (!ptx::named_barrier_all(kEpiBarrier, kEpiThreads, got_free)) {
+            ok = false;
+            break;
+          }
+        }
+        const uint32_t my_row = smem_out + static_cast<uint32_t>(row_in_tile) * (TILE_N * 4);
+        if (quarter * 32 < p.a_rows) {  // warp-uniform: this warp's lanes hold loaded rows
+          for (int c = 0; c < TILE_N / 32; ++c) {
+            if (acc_col0 + c * 32 >= p.n) break;
+            uint32_t r[32];
+            ptx::tmem_ld_32x32(t_acc + c * 32, r);  // whole warp, converged
+            ptx::tmem_ld_wait();
+            if (row_in_tile < p.a_rows) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const uint32_t chunk =
+                    (static_cast<uint32_t>(c * 8 + j) ^ static_cast<uint32_t>(row_in_tile)) & kChunkMask;
+                st_shared_v4(my_row + chunk * 16, r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+              }
+            }
+            __syncwarp();
+          }
+        }
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctrl->tmem_empty[acc]));
+        if (++acc == p.acc_stages) {
+          acc = 0;
+          acc_phase ^= 1u;
+        }
+        ptx::fence_acq_rel_cluster();
+        ptx::named_barrier_sync(kEpiBarrier, kEpiThreads);
+        if (epi_tid == 0)
+          for (uint32_t r = 0; r < S; ++r) ptx::mbar_arrive_cluster(ptx::mapa(full_bar, r));
+        const bool got_full = ptx::mbar_wait<true>(full_bar, xchg_round & 1u, abort_flag, p.timeout_ns);
+        if (!ptx::named_barrier_all(kEpiBarrier, kEpiThreads, got_full)) {
+          ok = false;
+          break;
+        }
+        if (epi_tid == 0 && u == cluster_id) TNX_TRACE(5);
+        const int rows_valid = min(p.a_rows, p.m - row0);
+        const int cols_valid = min(TILE_N, p.n - acc_col0);
+        const int vec_per_row = (cols_valid + 3) >> 2;
+        const int total_vec = rows_valid * vec_per_row;
+        const int share = (total_vec + static_cast<int>(S) - 1) / static_cast<int>(S);
+        const int lo_vec = static_cast<int>(cluster_rank) * share;
+        const int hi_vec = min(total_vec, lo_vec + share);
+        constexpr int kInFlight = 4;
+        for (int base = lo_vec + epi_tid; base < hi_vec; base += kEpiThreads * kInFlight) {
+          float4 sum[kInFlight];
+          int rr[kInFlight], cc[kInFlight];
+          uint32_t off[kInFlight];
+#pragma unroll
+          for (int u2 = 0; u2 < kInFlight; ++u2) {
+            const int idx = base + u2 * kEpiThreads;
+            const int safe = idx < hi_vec ? idx : base;
+            rr[u2] = safe / vec_per_row;
+            const int c4 = safe - rr[u2] * vec_per_row;
+            cc[u2] = c4 << 2;
+            off[u2] = smem_out + static_cast<uint32_t>(rr[u2]) * (TILE_N * 4) +
+                      (((static_cast<uint32_t>(c4) ^ static_cast<uint32_t>(rr[u2])) & kChunkMask) << 4);
+            sum[u2] = make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+          for (uint32_t s0 = 0; s0 < S; s0 += 4) {
+            float4 v[4][kInFlight];
+#pragma unroll
+            for (int ds = 0; ds < 4; ++ds)
+#pragma unroll
+              for (int u2 = 0; u2 < kInFlight; ++u2)
+                v[ds][u2] = s0 + ds < S ? ptx::ld_shared_cluster_v4(ptx::mapa(off[u2], s0 + ds))
+                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int ds = 0; ds < 4; ++ds)
+#pragma unroll
+              for (int u2 = 0; u2 < kInFlight; ++u2) {
+                sum[u2].x += v[ds][u2].x;
+                sum[u2].y += v[ds][u2].y;
+                sum[u2].z += v[ds][u2].z;
+                sum[u2].w += v[ds][u2].w;
+              }
+          }
+#pragma unroll
+          for (int u2 = 0; u2 < kInFlight; ++u2) {
+            if (base + u2 * kEpiThreads >= hi_vec) continue;
+            store_fixup<GLU, BF16>(p, row0 + rr[u2], acc_col0 + cc[u2], cols_valid - cc[u2], sum[u2]);
+          }
+        }
+        // Tell every slice that this one no longer reads their shared memory.
+        ptx::named_barrier_sync(kEpiBarrier, kEpiThreads);
+        if (epi_tid == 0)
+          for (uint32_t r = 0; r < S; ++r) ptx::mbar_arrive_cluster(ptx::mapa(free_bar, r));
+        ++xchg_round;
+        continue;
+      }
 
       if (p.split_k > 1) {
         // ---- split-K: park the fp32 partial; the last slice to arrive sums all of them ----
@@ -413,6 +580,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
         ptx::named_barrier_sync(kEpiBarrier, kEpiThreads);
         const bool is_last = ctrl->is_last != 0;
+        if (epi_tid == 0 && u == cluster_id) TNX_TRACE(5);
         if (!is_last) continue;
         __threadfence();
 
@@ -459,30 +627,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
           for (int u2 = 0; u2 < kInFlight; ++u2) {
             if (base + u2 * kEpiThreads >= total_vec) continue;
-            const size_t row_off = static_cast<size_t>(row0 + rr[u2]) * p.ldc;
-            const int left = cols_valid - cc[u2];  // valid accumulator columns from here on
-            uint16_t* c16 = reinterpret_cast<uint16_t*>(p.c_ptr);
-            if (GLU) {
-              const uint32_t z = pack2<BF16>(gate_act(sum[u2].x, p.epilogue) * sum[u2].y,
-                                             gate_act(sum[u2].z, p.epilogue) * sum[u2].w);
-              const size_t o = row_off + ((acc_col0 + cc[u2]) >> 1);
-              if (left >= 4) {
-                *reinterpret_cast<uint32_t*>(c16 + o) = z;
-              } else {  // n is even: exactly one (gate, up) pair is left
-                c16[o] = static_cast<uint16_t>(z & 0xffffu);
-              }
-            } else {
-              const uint32_t lo = pack2<BF16>(sum[u2].x, sum[u2].y);
-              const uint32_t hi = pack2<BF16>(sum[u2].z, sum[u2].w);
-              const size_t o = row_off + acc_col0 + cc[u2];
-              if (left >= 4) {
-                *reinterpret_cast<uint2*>(c16 + o) = make_uint2(lo, hi);
-              } else {
-                c16[o] = static_cast<uint16_t>(lo & 0xffffu);
-                if (left > 1) c16[o + 1] = static_cast<uint16_t>(lo >> 16);
-                if (left > 2) c16[o + 2] = static_cast<uint16_t>(hi & 0xffffu);
-              }
-            }
+            store_fixup<GLU, BF16>(p, row0 + rr[u2], acc_col0 + cc[u2], cols_valid - cc[u2], sum[u2]);
           }
         }
         continue;
@@ -559,6 +704,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
     }
     if (epi_tid == 0) ptx::tma_store_wait_all<0>();
+    if (epi_tid == 0) TNX_TRACE(6);
     if (!ok && lane == 0 && p.status != nullptr) atomicCAS(p.status, 0, kAbortEpilogue);
   }
 
@@ -572,7 +718,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     while (ptx::globaltimer_ns() - t0 < 1000000ull) __nanosleep(1000);
   }
   __syncwarp();
-  if (CTA_GROUP == 2) {  // the peer may still signal barriers in, or read, this CTA's shared memory
+  if (CTA_GROUP == 2 || xchg) {  // peers may still signal barriers in, or read, this CTA's shared memory
     ptx::cluster_arrive();
     ptx::cluster_wait();
   }
@@ -721,6 +867,15 @@ inline int a_box_rows(const tnx_problem& p, const tnx_config& cfg) {
 
 }  // namespace
 
+// Split-K slices can exchange partials through distributed shared memory when they fit one
+// portable cluster (2, 4 or 8 CTAs, one SM each) and a slice's fp32 partial fits the epilogue
+// staging area.  Then no workspace is needed at all.
+static bool use_cluster_split(const tnx_problem& p, const tnx_config& cfg, int split) {
+  if (cfg.cta_group != 1 || (split != 2 && split != 4 && split != 8)) return false;
+  if (getenv("TNX_NO_CLUSTER_SPLITK") != nullptr) return false;
+  return static_cast<long long>(a_box_rows(p, cfg)) * cfg.tile_n * 4 <= 2 * kStagingBytes;
+}
+
 bool umma_eligible(const tnx_problem& p, const char** why) {
   const char* w = nullptr;
   if (p.dtype != TNX_F16 && p.dtype != TNX_BF16)
@@ -808,16 +963,19 @@ int umma_query(const tnx_problem& p, tnx_config* cfg, tnx_resources* out) {
   out->tiles_m = tiles_m;
   out->tiles_n = tiles_n;
   out->split_k = split;
+  const bool xchg = split > 1 && use_cluster_split(p, *cfg, split);
   out->workspace_bytes =
-      split > 1 ? kCounterBytes + static_cast<int64_t>(tiles_m) * cfg->cta_group * tiles_n * split *
-                                      cfg->tile_n * kRowsPerCta * 4
-                : 0;
-  const long long units = static_cast<long long>(tiles_m) * tiles_n * split;
-  int max_clusters = device_sm_count() / cfg->cta_group;
-  if (cfg->max_ctas > 0 && cfg->max_ctas / cfg->cta_group < max_clusters)
-    max_clusters = cfg->max_ctas / cfg->cta_group;
+      split > 1 && !xchg ? kCounterBytes + static_cast<int64_t>(tiles_m) * cfg->cta_group * tiles_n *
+                                               split * cfg->tile_n * kRowsPerCta * 4
+                         : 0;
+  // Persistent grid: one cluster per SM group; a cluster is a CTA pair, the slices of a tile, or 1 CTA.
+  const int cluster_size = xchg ? split : cfg->cta_group;
+  const long long units = static_cast<long long>(tiles_m) * tiles_n * (xchg ? 1 : split);
+  int max_clusters = device_sm_count() / cluster_size;
+  if (cfg->max_ctas > 0 && cfg->max_ctas / cluster_size < max_clusters)
+    max_clusters = cfg->max_ctas / cluster_size;
   if (max_clusters < 1) max_clusters = 1;
-  out->grid = static_cast<int32_t>((units < max_clusters ? units : max_clusters) * cfg->cta_group);
+  out->grid = static_cast<int32_t>((units < max_clusters ? units : max_clusters) * cluster_size);
 
   if (smem > kMaxDynamicSmem) {
     set_error("shared memory budget exceeded: %lld B needed (%d stages x %d B + %d B), %d B per SM",
@@ -872,6 +1030,8 @@ int umma_launch(const tnx_problem& p, const tnx_config& cfg, const tnx_resources
   kp.tiles_n = res.tiles_n;
   kp.num_kb = cdiv(p.k, cfg.tile_k);
   kp.split_k = res.split_k;
+  const bool xchg = res.split_k > 1 && res.workspace_bytes == 0;
+  kp.cluster_split = xchg ? res.split_k : 0;
   kp.kb_per_slice = cdiv(kp.num_kb, res.split_k);
   kp.tile_k = cfg.tile_k;
   kp.a_rows = a_rows;
@@ -888,6 +1048,12 @@ int umma_launch(const tnx_problem& p, const tnx_config& cfg, const tnx_resources
                           : nullptr;
   kp.status = status_word;
   kp.timeout_ns = wait_limit_ns();
+#ifdef TNX_DEV_TRACE
+  {
+    const char* t = getenv("TNX_TRACE_PTR");
+    kp.trace = t ? reinterpret_cast<unsigned long long*>(strtoull(t, nullptr, 0)) : nullptr;
+  }
+#endif
 
   cudaError_t e = allow_full_smem(fn);
   if (e != cudaSuccess) {
@@ -903,11 +1069,24 @@ int umma_launch(const tnx_problem& p, const tnx_config& cfg, const tnx_resources
   lc.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = cfg.cta_group;
+  attr[0].val.clusterDim.x = xchg ? res.split_k : cfg.cta_group;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   lc.attrs = attr;
   lc.numAttrs = 1;
+  if (xchg) {
+    // Clusters of split_k CTAs do not always tile the GPU evenly: ask how many fit at once.
+    int fit = 0;
+    e = cudaOccupancyMaxActiveClusters(&fit, reinterpret_cast<const void*>(fn), &lc);
+    if (e != cudaSuccess || fit < 1) {
+      set_error("clusters of %d CTAs cannot be scheduled for the split-K exchange: %s", res.split_k,
+                e != cudaSuccess ? cudaGetErrorString(e) : "none fit");
+      (void)cudaGetLastError();
+      return TNX_ERR_CUDA;
+    }
+    const int want = res.grid / res.split_k;
+    lc.gridDim.x = static_cast<unsigned>((want < fit ? want : fit) * res.split_k);
+  }
   e = cudaLaunchKernelEx(&lc, fn, ta, tb, tc, kp);
   if (e != cudaSuccess) {
     set_error("kernel launch failed: %s", cudaGetErrorString(e));
