@@ -200,3 +200,24 @@ def test_status_word_reports_clean_after_all_launches():
     tnx.check_status()
     w = _cabi.status_word(torch.device(DEV, torch.cuda.current_device()))
     assert int(w.item()) == 0
+
+
+def test_tuned_configuration_is_persisted(tmp_path, monkeypatch):
+    """The winner of the first call's tuning is written to disk and reused by a fresh cache."""
+    monkeypatch.setenv("TRITONIX_B200_CACHE_DIR", str(tmp_path))
+    mm = __import__("sys").modules["tritonix_b200.ops.matmul"]
+    a = torch.randn(384, 512, device=DEV, dtype=bf16)
+    b = torch.randn(512, 640, device=DEV, dtype=bf16)
+    out1 = tnx.triton_matmul(a, b)
+    files = list((tmp_path / "tuned").glob("matmul_kernel.json"))
+    assert len(files) == 1
+    stored = __import__("json").loads(files[0].read_text())
+    (key, cfg), = stored.items()
+    assert key.startswith("384,640,512|torch.bfloat16|") and cfg == mm._matmul_cfg[(384, 640, 512)]
+    mm._matmul_cfg.clear()
+
+    def no_tuning(self, *args, **kwargs):
+        raise AssertionError("the stored configuration should have been used")
+    monkeypatch.setattr(tnx.TunableKernel, "tune", no_tuning)
+    out2 = tnx.triton_matmul(a, b)
+    assert torch.equal(out1, out2) and mm._matmul_cfg[(384, 640, 512)] == cfg

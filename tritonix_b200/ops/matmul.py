@@ -18,7 +18,7 @@ import os
 
 import torch
 
-from tritonix_b200 import _cabi
+from tritonix_b200 import _cabi, tuning_cache
 from tritonix_b200.autotune import Choice, PowerOfTwo, Range, tunable
 from tritonix_b200.dispatcher import dynamic_dispatch
 from tritonix_b200.ops._kernel_handle import CudaKernel
@@ -126,6 +126,21 @@ _matmul_cfg: dict = {}
 _splitk_cfg: dict = {}
 
 
+def _disk_key(shape_key: tuple, a: torch.Tensor) -> str:
+    return tuning_cache.make_key(shape_key, a.dtype, torch.cuda.get_device_name(a.device),
+                                 _cabi.lib.tnx_version().decode())
+
+
+def _tuned(kernel, launcher, shape_key: tuple, a: torch.Tensor, filter_fn):
+    """Disk hit, else tune and persist.  Returns None when nothing could be run."""
+    key = _disk_key(shape_key, a)
+    cfg = tuning_cache.load(kernel.kernel.__name__, key)
+    if cfg is None:
+        cfg = kernel.tune(launcher, filter_fn=filter_fn)
+        tuning_cache.save(kernel.kernel.__name__, key, cfg)
+    return cfg
+
+
 def cuda_matmul(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """``a @ b`` on the CUDA kernels, tuning once per (m, n, k)
     (the reference's ``triton_matmul``, tritonix/ops/matmul.py:271-277).  ``out`` optionally
@@ -137,7 +152,7 @@ def cuda_matmul(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = Non
     cfg = _matmul_cfg.get(key)
     if cfg is None:
         if _tuning_enabled() and _cabi.umma_eligible_tensors(a, b):
-            cfg = matmul_kernel.tune(lambda c: _launch_matmul(a, b, c), filter_fn=_plausible(m, n))
+            cfg = _tuned(matmul_kernel, lambda c: _launch_matmul(a, b, c), key, a, _plausible(m, n))
         cfg = cfg or default_config(m, n, k)
         _matmul_cfg[key] = cfg
     return _launch_matmul(a, b, cfg, out)
@@ -159,9 +174,8 @@ def matmul_splitk(a: torch.Tensor, b: torch.Tensor, split_k: int = 4,
     cfg = _splitk_cfg.get(key)
     if cfg is None:
         if _tuning_enabled() and _cabi.umma_eligible_tensors(a, b):
-            cfg = gemm_splitk_kernel.tune(
-                lambda c: _launch_splitk(a, b, c),
-                filter_fn=lambda c: c["split_k"] == split_k and _plausible(m, n)(c))
+            cfg = _tuned(gemm_splitk_kernel, lambda c: _launch_splitk(a, b, c), key, a,
+                         lambda c: c["split_k"] == split_k and _plausible(m, n)(c))
         cfg = cfg or default_config(m, n, k, split_k)
         _splitk_cfg[key] = cfg
     return _launch_splitk(a, b, cfg, out)

@@ -113,8 +113,8 @@ def glu(x: torch.Tensor, w12: torch.Tensor, activation: str = "sigmoid",
         if cfg is None:
             tune = os.environ.get("TRITONIX_B200_TUNE", "1") not in ("0", "false", "off")
             if tune and _cabi.umma_eligible_tensors(x, w12) and (n // 2) % 8 == 0:
-                cfg = glu_kernel.tune(lambda c: _launch_glu(x, w12, c, activation),
-                                      filter_fn=_mm._plausible(m, n))
+                cfg = _mm._tuned(glu_kernel, lambda c: _launch_glu(x, w12, c, activation), key, x,
+                                 _mm._plausible(m, n))
             cfg = cfg or default_glu_config(m, n, k)
             _glu_cfg[key] = cfg
     return _launch_glu(x, w12, cfg, activation, out)
