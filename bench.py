@@ -49,7 +49,7 @@ WORKLOADS = {
 }
 
 GEMM_CFG = {"kernel": "tcgen05", "tile_n": 256, "tile_k": 128, "stages": 3, "cta_group": 2, "group_m": 16}
-SPLITK_CFG = {"kernel": "tcgen05", "tile_n": 128, "tile_k": 128, "stages": 3, "cta_group": 1, "split_k": 4}
+SPLITK_CFG = {"kernel": "tcgen05", "tile_n": 128, "tile_k": 128, "stages": 4, "cta_group": 1, "split_k": 4}
 GLU_CFG = {"kernel": "tcgen05", "tile_n": 256, "tile_k": 128, "stages": 3, "cta_group": 2, "group_m": 16}
 
 # DRAM traffic of the dominant kernel per launch, from the ncu captures summarised under
@@ -188,7 +188,7 @@ def setup_contraction(workload, rank, world, dev):
     return step, e2e_step, work
 
 
-def setup_mlp(rank, world, dev):
+def setup_mlp(rank, world, dev, chunks=0):
     """SwiGLU MLP, tensor parallel: column-parallel fused gate/up, row-parallel down, one
     all-reduce.  Global weights come from fixed seeds and are sliced, so every world size
     computes the same function."""
@@ -208,7 +208,7 @@ def setup_mlp(rank, world, dev):
     sw = sys.modules["tritonix_b200.ops.swiglu"]
     mm = sys.modules["tritonix_b200.ops.matmul"]
     mlp = TensorParallelSwiGLU(
-        w12, wd, chunks=1 if world == 1 else 4,
+        w12, wd, chunks=chunks if chunks > 0 else (1 if world == 1 else 4),
         gate_up_fn=lambda xx, ww: sw._launch_glu(xx, ww, GLU_CFG, "silu"),
         down_fn=lambda h, ww, out: mm._launch_matmul(h, ww, GEMM_CFG, out))
     state = {}
@@ -343,6 +343,9 @@ def main():
     ap.add_argument("--cfg", type=str, default=None,
                     help="JSON object overriding kernel-config keys of the workload, e.g. "
                          "'{\"group_m\": 8}'")
+    ap.add_argument("--chunks", type=int, default=0,
+                    help="mlp: row chunks whose all-reduce overlaps the next chunk's GEMMs "
+                         "(default: 1 on one GPU, 4 otherwise)")
     ap.add_argument("--no-e2e", action="store_true",
                     help="skip the host-buffer leg (used for profiler captures of the kernel)")
     args = ap.parse_args()
@@ -380,7 +383,7 @@ def main():
         for base in (GEMM_CFG, SPLITK_CFG, GLU_CFG):
             base.update(override)
     if args.workload == "mlp":
-        step, e2e_step, work = setup_mlp(rank, world, dev)
+        step, e2e_step, work = setup_mlp(rank, world, dev, args.chunks)
     else:
         step, e2e_step, work = setup_contraction(args.workload, rank, world, dev)
 

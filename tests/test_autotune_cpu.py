@@ -131,6 +131,6 @@ def test_shipped_kernel_spaces_are_consistent():
     for tk in (t.matmul_kernel, t.gemm_splitk_kernel, t.glu_kernel, t.swiglu_kernel):
         assert isinstance(tk, TunableKernel) and tk.keys == ["m", "n", "k"]
         names, values = tk._memory_axes()
-        assert set(names) == {"tile_n", "tile_k", "stages", "cta_group"}
-        assert values[names.index("cta_group")][0] == max(tk.space["cta_group"].values())
-    assert len(t.matmul_kernel.configs()) == 3 * 2 * 7 * 2 * 3
+        assert set(names) == {"block_m", "block_n", "block_k", "num_stages"}  # the reference's axes
+        assert values[names.index("block_m")][0] == max(tk.space["block_m"].values())
+    assert len(t.matmul_kernel.configs()) == 2 * 3 * 2 * 3 * 7

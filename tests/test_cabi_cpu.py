@@ -84,6 +84,8 @@ def test_invalid_and_unbuilt_configs_are_value_errors():
         _cabi.make_problem(1, 1, 1, torch.int8, (1, 1, 1, 1, 1, 1))
     with pytest.raises(ValueError, match="unit inner strides"):
         q(512, 512, 512, {"kernel": "tcgen05"}, strides=(1, 512, 512, 1, 512, 1))
+    # a transposed B (stored N x K) is a legal tcgen05 operand
+    assert q(512, 512, 512, {"kernel": "tcgen05"}, strides=(512, 1, 1, 512, 512, 1)).kernel == _cabi.KERNEL_TCGEN05
 
 
 def test_family_selection_and_aliases():
@@ -92,6 +94,10 @@ def test_family_selection_and_aliases():
     assert q(128, 128, 128, {"kernel": "strided"}).kernel == _cabi.KERNEL_STRIDED
     c = _cabi.make_config({"block_n": 128, "block_k": 64, "num_stages": 4, "num_warps": 8, "group_m": 4})
     assert (c.tile_n, c.tile_k, c.stages, c.group_m) == (128, 64, 4, 4)
+    # a 256-row tile means a CTA pair (the reference's block_m axis carries the 1-SM / 2-SM choice)
+    pair = q(4096, 4096, 4096, {"block_m": 256, "block_n": 256, "block_k": 64, "num_stages": 6})
+    single = q(4096, 4096, 4096, {"block_m": 128, "block_n": 256, "block_k": 64, "num_stages": 4})
+    assert (pair.tiles_m, single.tiles_m) == (16, 32) and pair.smem_bytes == 6 * 256 * 64 * 2 + 34304
 
 
 def test_split_k_resources():

@@ -63,7 +63,7 @@ def test_arbitrary_strides_like_the_reference_accepts():
     """Transposed and column-sliced views: the reference's kernels take any strides
     (tritonix/ops/matmul.py:50-55)."""
     a0, b0 = seeded(192, 160, 224, f16, seed=11)
-    a = a0.to(DEV).t().contiguous().t()          # column-major A
+    a = a0.to(DEV).t().contiguous().t()          # column-major A: no TMA layout for it
     b = b0.to(DEV).t().contiguous().t()          # column-major B
     c_full = torch.full((192, 448), float("nan"), device=DEV, dtype=f16)
     c = c_full[:, ::2]                           # output with column stride 2
@@ -81,6 +81,30 @@ def test_arbitrary_strides_like_the_reference_accepts():
     _cabi.check_status(c2.device)
     assert res.kernel == _cabi.KERNEL_TCGEN05
     assert_close(c2.cpu(), O.matmul_oracle(a_view.cpu(), bmat.cpu()), bf16)
+
+
+@pytest.mark.parametrize("m,n,k,dtype,cfg,epi", [
+    (256, 384, 512, bf16, {"tile_n": 128}, 0),
+    (1000, 520, 264, f16, {"tile_n": 256, "tile_k": 128, "stages": 2}, 0),
+    (2048, 1024, 1024, bf16, {"tile_n": 256, "cta_group": 2, "tile_k": 128, "stages": 3}, 0),
+    (512, 768, 512, bf16, {"tile_n": 128, "cta_group": 2}, 0),
+    (64, 1024, 2048, f16, {"tile_n": 128, "split_k": 4}, 0),
+    (300, 512, 512, bf16, {"tile_n": 256}, _cabi.EPI_GLU_SILU),
+])
+def test_transposed_b_operand(m, n, k, dtype, cfg, epi):
+    """B given as the transpose of an (N, K) row-major tensor — the usual layout of a linear
+    layer's weight — runs on the tcgen05 kernel as a K-major operand, without a copy."""
+    a, b = seeded(m, k, n, dtype, seed=n + 1, b_scale=0.05 if epi else None)
+    bt = b.t().contiguous().to(DEV)          # stored (N, K)
+    b_view = bt.t()                          # logical (K, N), strides (1, K)
+    assert b_view.stride() == (1, k)
+    n_out = n // 2 if epi else n
+    c = torch.full((m, n_out), float("nan"), device=DEV, dtype=dtype)
+    res = _cabi.launch(a.to(DEV), b_view, c, {**T, **cfg}, epi)
+    _cabi.check_status(c.device)
+    assert res.kernel == _cabi.KERNEL_TCGEN05
+    ref = O.glu_oracle(a, b, "silu") if epi else O.matmul_oracle(a, b)
+    assert_close(c.cpu(), ref, dtype)
 
 
 def test_output_tails_are_not_overwritten():

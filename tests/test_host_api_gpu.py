@@ -154,7 +154,7 @@ def test_tuner_on_real_kernels_prunes_out_of_resources():
             events.append(("skip", dict(cfg)))
             raise
     best = tnx.matmul_kernel.tune(launcher, max_configs=40,
-                                  filter_fn=lambda c: c["group_m"] == 8 and c["tile_k"] == 64)
+                                  filter_fn=lambda c: c["group_m"] == 8 and c["block_k"] == 64)
     tnx.check_status()
     assert best is not None and set(best) == set(tnx.matmul_kernel.space)
     ooms = [c for kind, c in events if kind == "oom"]
@@ -164,8 +164,8 @@ def test_tuner_on_real_kernels_prunes_out_of_resources():
         if kind != "oom":
             continue
         for kind2, c2 in events[i + 1:]:
-            assert not (c2["tile_n"] >= c["tile_n"] and c2["stages"] >= c["stages"]
-                        and c2["cta_group"] <= c["cta_group"] and c2["tile_k"] >= c["tile_k"])
+            assert not (c2["block_n"] >= c["block_n"] and c2["num_stages"] >= c["num_stages"]
+                        and c2["block_m"] <= c["block_m"] and c2["block_k"] >= c["block_k"])
     out = mm._launch_matmul(a, b, best)
     assert_close(out.cpu(), O.matmul_oracle(a.cpu(), b.cpu()), bf16)
 

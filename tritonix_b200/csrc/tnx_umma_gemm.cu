@@ -61,6 +61,7 @@ struct UmmaParams {
   int cluster_split;    // > 0: the split_k slices of a tile form one cluster and exchange their
                         // partials through distributed shared memory (no workspace)
   int tile_k;
+  int b_kmajor;         // 1: B is stored N x K (K contiguous, e.g. a transposed weight view)
   int a_rows;           // rows of A that TMA brings in per stage (128, or fewer for a skinny M)
   int stages;
   int acc_stages;
@@ -295,10 +296,17 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             for (int ka = 0; ka < TILE_K / kAtomElems; ++ka)
               ptx::tma_load_2d(a_dst + ka * a_atom_bytes, &tmap_a,
                                k0 + ka * kAtomElems, row0, full_bar);
+            if (p.b_kmajor) {
 #pragma unroll
-            for (int na = 0; na < LOAD_N / kAtomElems; ++na)
-              ptx::tma_load_2d(b_dst + na * (TILE_K * kAtomBytes), &tmap_b,
-                               col0 + na * kAtomElems, k0, full_bar);
+              for (int ka = 0; ka < TILE_K / kAtomElems; ++ka)
+                ptx::tma_load_2d(b_dst + ka * (LOAD_N * kAtomBytes), &tmap_b, k0 + ka * kAtomElems,
+                                 col0, full_bar);
+            } else {
+#pragma unroll
+              for (int na = 0; na < LOAD_N / kAtomElems; ++na)
+                ptx::tma_load_2d(b_dst + na * (TILE_K * kAtomBytes), &tmap_b,
+                                 col0 + na * kAtomElems, k0, full_bar);
+            }
           } else {
             // Both CTAs' loads complete on the leader's barrier; the leader announces the bytes.
             const uint32_t leader_bar = ptx::mapa(full_bar, 0);
@@ -307,10 +315,17 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             for (int ka = 0; ka < TILE_K / kAtomElems; ++ka)
               ptx::tma_load_2d_pair(a_dst + ka * a_atom_bytes, &tmap_a,
                                     k0 + ka * kAtomElems, row0, leader_bar);
+            if (p.b_kmajor) {
 #pragma unroll
-            for (int na = 0; na < LOAD_N / kAtomElems; ++na)
-              ptx::tma_load_2d_pair(b_dst + na * (TILE_K * kAtomBytes), &tmap_b,
-                                    col0 + na * kAtomElems, k0, leader_bar);
+              for (int ka = 0; ka < TILE_K / kAtomElems; ++ka)
+                ptx::tma_load_2d_pair(b_dst + ka * (LOAD_N * kAtomBytes), &tmap_b,
+                                      k0 + ka * kAtomElems, col0, leader_bar);
+            } else {
+#pragma unroll
+              for (int na = 0; na < LOAD_N / kAtomElems; ++na)
+                ptx::tma_load_2d_pair(b_dst + na * (TILE_K * kAtomBytes), &tmap_b,
+                                      col0 + na * kAtomElems, k0, leader_bar);
+            }
           }
           if (u == cluster_id) TNX_TRACE(64 + (kb - kb0));
           if (++stage == p.stages) {
@@ -327,13 +342,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     if (leader && lane == 0) {
       // Instruction descriptor: fp32 accumulate, A K-major, B MN-major, M x N = (128*CTA_GROUP) x TILE_N.
       const uint32_t fmt = BF16 ? 1u : 0u;
-      const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (0u << 15) | (1u << 16) |
+      const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (0u << 15) |
+                             ((p.b_kmajor ? 0u : 1u) << 16) |
                              (static_cast<uint32_t>(TILE_N >> 3) << 17) |
                              (static_cast<uint32_t>((kRowsPerCta * CTA_GROUP) >> 4) << 24);
       // A: rows of 128 B, 8-row groups 1024 B apart.  B: 64-column atoms of tile_k rows x 128 B;
       // LBO = bytes between atoms along N, SBO = bytes between 8-row groups along K.
       const uint64_t a_desc_hi = ptx::make_smem_desc(0, 0, 1024);
-      const uint64_t b_desc_hi = ptx::make_smem_desc(0, TILE_K * kAtomBytes, 1024);
+      // A K-major B (stored N x K) is laid out like A: rows of 128 B, one slab per 64 K elements.
+      const uint64_t b_desc_hi =
+          p.b_kmajor ? ptx::make_smem_desc(0, 0, 1024) : ptx::make_smem_desc(0, TILE_K * kAtomBytes, 1024);
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -364,7 +382,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
           for (int k16 = 0; k16 < TILE_K / 16; ++k16) {
             const uint32_t a_addr = a_src + (k16 >> 2) * a_atom_bytes + (k16 & 3) * 32;
-            const uint32_t b_addr = b_src + k16 * (16 * kAtomBytes);
+            const uint32_t b_addr = p.b_kmajor
+                                        ? b_src + (k16 >> 2) * (LOAD_N * kAtomBytes) + (k16 & 3) * 32
+                                        : b_src + k16 * (16 * kAtomBytes);
             ptx::umma_f16<CTA_GROUP>(d_tmem, a_desc_hi | ((a_addr >> 4) & 0x3fffu),
                                      b_desc_hi | ((b_addr >> 4) & 0x3fffu), idesc, accumulate);
             accumulate = 1;
@@ -880,16 +900,17 @@ bool umma_eligible(const tnx_problem& p, const char** why) {
   const char* w = nullptr;
   if (p.dtype != TNX_F16 && p.dtype != TNX_BF16)
     w = "tcgen05 path takes fp16 or bf16 operands";
-  else if (p.stride_ak != 1 || p.stride_bn != 1 || p.stride_cn != 1)
-    w = "tcgen05 path needs unit inner strides (row-major A, B and C)";
-  else if ((p.stride_am % 8) != 0 || (p.stride_bk % 8) != 0 || (p.stride_cm % 8) != 0)
+  else if (p.stride_ak != 1 || p.stride_cn != 1 || (p.stride_bn != 1 && p.stride_bk != 1))
+    w = "tcgen05 path needs unit inner strides (row-major A and C; B row-major or its transpose)";
+  else if ((p.stride_am % 8) != 0 || (p.stride_cm % 8) != 0 ||
+           ((p.stride_bn == 1 ? p.stride_bk : p.stride_bn) % 8) != 0)
     w = "tcgen05 path needs row pitches that are multiples of 16 bytes";
   else if (p.k < 1 || p.m < 1 || p.n < 1)
     w = "empty problem";
   else if ((p.k % 8) != 0 || (p.n % 8) != 0 || (p.epilogue != TNX_EPI_NONE && (p.n % 16) != 0))
     // TMA clips and zero-fills in 16-byte units along the contiguous dimension
     w = "tcgen05 path needs K, N (and N/2 for a GLU epilogue) to be multiples of 8 elements";
-  else if (p.stride_am < p.k || p.stride_bk < p.n)
+  else if (p.stride_am < p.k || (p.stride_bn == 1 ? p.stride_bk < p.n : p.stride_bn < p.k))
     w = "row pitch smaller than the row length";
   if (why) *why = w;
   return w == nullptr;
@@ -897,7 +918,7 @@ bool umma_eligible(const tnx_problem& p, const char** why) {
 
 int umma_query(const tnx_problem& p, tnx_config* cfg, tnx_resources* out) {
   const bool glu = p.epilogue != TNX_EPI_NONE;
-  if (cfg->cta_group == 0) cfg->cta_group = 1;
+  if (cfg->cta_group == 0) cfg->cta_group = cfg->tile_m == 2 * kRowsPerCta ? 2 : 1;  // 256 rows = a CTA pair
   if (cfg->tile_m == 0) cfg->tile_m = kRowsPerCta * cfg->cta_group;
   if (cfg->tile_n == 0) cfg->tile_n = (p.n >= 256) ? 256 : (p.n > 64 || glu ? 128 : 64);
   if (cfg->tile_k == 0) cfg->tile_k = 64;
@@ -1016,7 +1037,13 @@ int umma_launch(const tnx_problem& p, const tnx_config& cfg, const tnx_resources
   const int a_rows = a_box_rows(p, cfg);
   int rc = make_tmap(&ta, a, p.dtype, p.k, p.m, p.stride_am, kAtomElems, a_rows, true);
   if (rc != TNX_OK) return rc;
-  rc = make_tmap(&tb, b, p.dtype, p.n, p.k, p.stride_bk, kAtomElems, cfg.tile_k, true);
+  // B row-major (K x N): boxes of 64 columns x tile_k rows.  B stored N x K (a transposed view):
+  // boxes of 64 K elements x the CTA's B columns, like A.
+  const bool b_kmajor = p.stride_bn != 1;
+  if (b_kmajor)
+    rc = make_tmap(&tb, b, p.dtype, p.k, p.n, p.stride_bn, kAtomElems, cfg.tile_n / cfg.cta_group, true);
+  else
+    rc = make_tmap(&tb, b, p.dtype, p.n, p.k, p.stride_bk, kAtomElems, cfg.tile_k, true);
   if (rc != TNX_OK) return rc;
   rc = make_tmap(&tc, c, p.dtype, n_out, p.m, p.stride_cm, kAtomElems, kRowsPerCta, false);
   if (rc != TNX_OK) return rc;
@@ -1035,6 +1062,7 @@ int umma_launch(const tnx_problem& p, const tnx_config& cfg, const tnx_resources
   kp.kb_per_slice = cdiv(kp.num_kb, res.split_k);
   kp.tile_k = cfg.tile_k;
   kp.a_rows = a_rows;
+  kp.b_kmajor = b_kmajor ? 1 : 0;
   kp.stages = cfg.stages;
   kp.acc_stages = cfg.acc_stages;
   kp.group_m = cfg.group_m;

@@ -2,15 +2,17 @@
 per-shape tuned configuration caches, ``cuda_matmul`` (the reference's ``triton_matmul``),
 ``matmul_splitk`` and the ``matmul`` dispatcher — the surface of tritonix/ops/matmul.py:30-293.
 
-Search space = the CUDA kernels' template and launch parameters:
-  tile_n     columns of B per tile (64 / 128 / 256)
-  tile_k     K elements per pipeline stage (64 / 128)
-  stages     depth of the TMA -> shared-memory ring
-  cta_group  1 = one SM per 128 x tile_n tile, 2 = a CTA pair shares a 256 x tile_n tile
-  group_m    band height of the grouped tile order
-  split_k    K slices per tile (split-K kernel only)
-"out of resources" means stages x stage bytes (+ epilogue staging) exceeds the 227 KiB of shared
-memory of an SM, or the accumulators exceed its 512 TMEM columns.
+Search space = the CUDA kernels' template and launch parameters, under the reference's key
+names (tritonix/ops/matmul.py:33-39) so that launchers written against it keep working:
+  block_m     rows of C per tile: 128 = one SM per tile, 256 = a CTA pair (tcgen05 cta_group::2)
+  block_n     columns of B per tile (64 / 128 / 256)
+  block_k     K elements per pipeline stage (64 / 128)
+  num_stages  depth of the TMA -> shared-memory ring
+  group_m     band height of the grouped tile order
+  split_k     K slices per tile (split-K kernel only)
+The C ABI's own names (tile_m, tile_n, tile_k, stages, cta_group, ...) are accepted as well.
+"out of resources" means num_stages x stage bytes (+ epilogue staging) exceeds the 227 KiB of
+shared memory of an SM, or the accumulators exceed its 512 TMEM columns.
 """
 from __future__ import annotations
 
@@ -23,17 +25,19 @@ from tritonix_b200.autotune import Choice, PowerOfTwo, Range, tunable
 from tritonix_b200.dispatcher import dynamic_dispatch
 from tritonix_b200.ops._kernel_handle import CudaKernel
 
-_MEMORY = {"tile_n", "tile_k", "stages", "cta_group"}
-_RANK = {"cta_group": lambda g: -g}  # a CTA pair needs less shared memory per CTA than one CTA
+_MEMORY = {"block_m", "block_n", "block_k", "num_stages"}
+# A 256-row tile is shared by two CTAs, each loading half of the B columns: less shared memory
+# per CTA than a 128-row tile, so this axis is ranked by descending value.
+_RANK = {"block_m": lambda rows: -rows}
 
 matmul_kernel = tunable(
     keys=["m", "n", "k"],
     space={
-        "tile_n": PowerOfTwo(64, 256),
-        "tile_k": PowerOfTwo(64, 128),
-        "stages": Range(2, 8),
-        "cta_group": Choice([1, 2]),
+        "block_m": PowerOfTwo(128, 256),
+        "block_n": PowerOfTwo(64, 256),
+        "block_k": PowerOfTwo(64, 128),
         "group_m": Choice([4, 8, 16]),
+        "num_stages": Range(2, 8),
     },
     memory_params=_MEMORY,
     memory_rank=_RANK,
@@ -43,12 +47,12 @@ matmul_kernel = tunable(
 gemm_splitk_kernel = tunable(
     keys=["m", "n", "k"],
     space={
-        "tile_n": PowerOfTwo(64, 256),
-        "tile_k": PowerOfTwo(64, 128),
-        "stages": Range(3, 8),
-        "cta_group": Choice([1]),
+        "block_m": Choice([128]),
+        "block_n": PowerOfTwo(64, 256),
+        "block_k": PowerOfTwo(64, 128),
         "group_m": Choice([8]),
         "split_k": Choice([1, 2, 4, 8, 16]),
+        "num_stages": Range(3, 8),
     },
     memory_params=_MEMORY,
     memory_rank=_RANK,
@@ -97,14 +101,14 @@ def default_config(m: int, n: int, k: int, split_k: int | None = None) -> dict:
     """Configuration used when tuning is disabled (``TRITONIX_B200_TUNE=0``): the shapes that
     measured best on a B200 for large, skinny and small problems."""
     if split_k is not None:
-        return {"tile_n": 128 if n >= 1024 else 64, "tile_k": 128, "stages": 3, "cta_group": 1,
-                "group_m": 8, "split_k": int(split_k)}
+        return {"block_m": 128, "block_n": 128 if n >= 1024 else 64, "block_k": 128, "group_m": 8,
+                "split_k": int(split_k), "num_stages": 4 if m <= 64 else 3}
     if m > 128 and n >= 256:
-        return {"tile_n": 256, "tile_k": 128, "stages": 3, "cta_group": 2, "group_m": 16}
+        return {"block_m": 256, "block_n": 256, "block_k": 128, "group_m": 16, "num_stages": 3}
     if n >= 256:
-        return {"tile_n": 256, "tile_k": 64, "stages": 4, "cta_group": 1, "group_m": 8}
-    return {"tile_n": 128 if n > 64 else 64, "tile_k": 64, "stages": 6, "cta_group": 1,
-            "group_m": 8}
+        return {"block_m": 128, "block_n": 256, "block_k": 64, "group_m": 8, "num_stages": 4}
+    return {"block_m": 128, "block_n": 128 if n > 64 else 64, "block_k": 64, "group_m": 8,
+            "num_stages": 6}
 
 
 def _tuning_enabled() -> bool:
@@ -114,9 +118,9 @@ def _tuning_enabled() -> bool:
 def _plausible(m: int, n: int):
     """Drops configurations that cannot win for the shape, to keep the first call short."""
     def keep(cfg):
-        if cfg.get("cta_group", 1) == 2 and m <= 128:
+        if cfg.get("block_m", 128) == 256 and m <= 128:
             return False
-        if cfg["tile_n"] > 64 and cfg["tile_n"] >= 2 * max(n, 64):
+        if cfg["block_n"] > 64 and cfg["block_n"] >= 2 * max(n, 64):
             return False
         return True
     return keep

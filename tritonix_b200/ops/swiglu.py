@@ -33,14 +33,14 @@ _mm = _sys.modules["tritonix_b200.ops.matmul"]  # the module (ops.matmul is also
 glu_kernel = tunable(
     keys=["m", "n", "k"],
     space={
-        "tile_n": PowerOfTwo(128, 256),
-        "tile_k": PowerOfTwo(64, 128),
-        "stages": Range(2, 8),
-        "cta_group": Choice([1, 2]),
+        "block_m": PowerOfTwo(128, 256),
+        "block_n": PowerOfTwo(128, 256),
+        "block_k": PowerOfTwo(64, 128),
         "group_m": Choice([4, 8, 16]),
+        "num_stages": Range(2, 8),
     },
-    memory_params={"tile_n", "tile_k", "stages", "cta_group"},
-    memory_rank={"cta_group": lambda g: -g},
+    memory_params={"block_m", "block_n", "block_k", "num_stages"},
+    memory_rank={"block_m": lambda rows: -rows},
 )(CudaKernel("glu_kernel", glu=True,
              doc="Z = act(X.W1) * (X.W2) over interleaved W12; n counts W12's columns (2F)."))
 
@@ -63,8 +63,8 @@ class _SwigluMlpKernel(CudaKernel):
 swiglu_kernel = tunable(
     keys=["m", "n", "k"],
     space=dict(glu_kernel.space),
-    memory_params={"tile_n", "tile_k", "stages", "cta_group"},
-    memory_rank={"cta_group": lambda g: -g},
+    memory_params={"block_m", "block_n", "block_k", "num_stages"},
+    memory_rank={"block_m": lambda rows: -rows},
 )(_SwigluMlpKernel("swiglu_kernel",
                    doc="Z[M, f] = (silu(X.W1) * (X.W2)) . W3, W12 interleaved, W3 is (n/2, f)."))
 
@@ -78,9 +78,9 @@ def interleave_weights(w1: torch.Tensor, w2: torch.Tensor) -> torch.Tensor:
 
 def default_glu_config(m: int, n: int, k: int) -> dict:
     if m > 128:
-        return {"tile_n": 256, "tile_k": 128, "stages": 3, "cta_group": 2, "group_m": 16}
-    return {"tile_n": 256 if n >= 256 else 128, "tile_k": 64, "stages": 4, "cta_group": 1,
-            "group_m": 8}
+        return {"block_m": 256, "block_n": 256, "block_k": 128, "group_m": 16, "num_stages": 3}
+    return {"block_m": 128, "block_n": 256 if n >= 256 else 128, "block_k": 64, "group_m": 8,
+            "num_stages": 4}
 
 
 def _launch_glu(x: torch.Tensor, w12: torch.Tensor, cfg: dict, activation: str,
