@@ -188,7 +188,7 @@ def setup_contraction(workload, rank, world, dev):
     return step, e2e_step, work
 
 
-def setup_mlp(rank, world, dev, chunks=0):
+def setup_mlp(rank, world, dev, chunks=0, comm_sms=0):
     """SwiGLU MLP, tensor parallel: column-parallel fused gate/up, row-parallel down, one
     all-reduce.  Global weights come from fixed seeds and are sliced, so every world size
     computes the same function."""
@@ -208,9 +208,8 @@ def setup_mlp(rank, world, dev, chunks=0):
     sw = sys.modules["tritonix_b200.ops.swiglu"]
     mm = sys.modules["tritonix_b200.ops.matmul"]
     mlp = TensorParallelSwiGLU(
-        w12, wd, chunks=chunks if chunks > 0 else (1 if world == 1 else 4),
-        gate_up_fn=lambda xx, ww: sw._launch_glu(xx, ww, GLU_CFG, "silu"),
-        down_fn=lambda h, ww, out: mm._launch_matmul(h, ww, GEMM_CFG, out))
+        w12, wd, chunks=chunks if chunks > 0 else (1 if world == 1 else 4), comm_sms=comm_sms,
+        gate_up_cfg=GLU_CFG, down_cfg=GEMM_CFG)
     state = {}
 
     def step():
@@ -229,7 +228,7 @@ def setup_mlp(rank, world, dev, chunks=0):
     nchunks = len(mlp.chunk_bounds(m))
     work = dict(flops=flops, bytes=None, units=float(m), launches=2 * nchunks, h2d=x_host.numel() * 2,
                 d2h=y_host.numel() * 2, copies=1, cfg={"gate_up": GLU_CFG, "down": GEMM_CFG},
-                out=None, check=None)
+                out=None, check=None, chunks=nchunks)
     return step, e2e_step, work
 
 
@@ -346,6 +345,8 @@ def main():
     ap.add_argument("--chunks", type=int, default=0,
                     help="mlp: row chunks whose all-reduce overlaps the next chunk's GEMMs "
                          "(default: 1 on one GPU, 4 otherwise)")
+    ap.add_argument("--comm-sms", type=int, default=0,
+                    help="mlp on >1 GPU: SMs the GEMM grids leave free for the all-reduce kernel")
     ap.add_argument("--no-e2e", action="store_true",
                     help="skip the host-buffer leg (used for profiler captures of the kernel)")
     args = ap.parse_args()
@@ -364,7 +365,14 @@ def main():
     torch.cuda.set_device(dev)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=dev)
+        pg_options = None
+        if args.workload == "mlp" and args.comm_sms > 0:
+            try:  # keep the all-reduce inside the SMs that the GEMM grids leave free
+                pg_options = dist.ProcessGroupNCCL.Options()
+                pg_options.config.max_ctas = args.comm_sms
+            except Exception:
+                pg_options = None
+        dist.init_process_group("nccl", device_id=dev, pg_options=pg_options)
 
     def barrier():
         if world > 1:
@@ -383,7 +391,7 @@ def main():
         for base in (GEMM_CFG, SPLITK_CFG, GLU_CFG):
             base.update(override)
     if args.workload == "mlp":
-        step, e2e_step, work = setup_mlp(rank, world, dev, args.chunks)
+        step, e2e_step, work = setup_mlp(rank, world, dev, args.chunks, args.comm_sms)
     else:
         step, e2e_step, work = setup_contraction(args.workload, rank, world, dev)
 
@@ -432,6 +440,8 @@ def main():
         "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": WORKLOADS[args.workload]["dtype"],
         "data": "synthetic",
         "config": {"workload": WORKLOADS[args.workload]["name"], "kernel_config": work["cfg"],
+                   **({"allreduce_chunks": work["chunks"], "comm_sms": args.comm_sms}
+                      if args.workload == "mlp" and world > 1 else {}),
                    "parallelism": ("tp%d" % world) if strong else ("rows_sharded_x%d" % world),
                    "l2": ("operands rotate through %d copies (> 3x L2)" % work["copies"]) if work["copies"] > 1
                    else "operands exceed the 126 MB L2"},

@@ -65,24 +65,63 @@ class TensorParallelSwiGLU:
     ``gate_up_fn(x, w12) -> h`` and ``down_fn(h, w_down, out=y_rows)`` (writes the partial
     output into ``out``) default to this package's CUDA kernels; they are parameters so that the partitioning and the chunked
     all-reduce schedule can be exercised by CPU (gloo) ranks in tests.
+
+    ``comm_sms``: the GEMM kernels are persistent (one CTA per SM, nearly all of its shared
+    memory), so a collective's kernel cannot slip in beside them; it only gets SMs as GEMM CTAs
+    retire.  ``comm_sms > 0`` makes the default kernels leave that many SMs free (grid capped at
+    SM count - comm_sms) so that NCCL's all-reduce of chunk i runs while chunk i+1 is computed.
+    It pays off only when communication is a large share of the step (measured on 8 B200:
+    8 chunks with 32 SMs left free beat 4 chunks with none by 4-7 %; at 2 GPUs it loses).
+    ``gate_up_cfg`` / ``down_cfg`` override the kernel configurations of the default kernels.
     """
 
     def __init__(self, w12_shard: torch.Tensor, w_down_shard: torch.Tensor,
                  group: Optional[dist.ProcessGroup] = None, chunks: int = 4,
-                 gate_up_fn: Optional[Callable] = None, down_fn: Optional[Callable] = None):
+                 gate_up_fn: Optional[Callable] = None, down_fn: Optional[Callable] = None,
+                 comm_sms: int = 0, gate_up_cfg: Optional[dict] = None,
+                 down_cfg: Optional[dict] = None):
         if w12_shard.shape[1] != 2 * w_down_shard.shape[0]:
             raise ValueError("w12 shard must have twice as many columns as w_down shard has rows")
         self.w12 = w12_shard
         self.w_down = w_down_shard
         self.group = group
         self.chunks = max(1, int(chunks))
+        self.comm_sms = max(0, int(comm_sms))
         if gate_up_fn is None or down_fn is None:
-            from tritonix_b200.ops import cuda_matmul, swiglu
-            gate_up_fn = gate_up_fn or swiglu
-            down_fn = down_fn or cuda_matmul
+            default_gate_up, default_down = self._default_kernels(gate_up_cfg, down_cfg)
+            gate_up_fn = gate_up_fn or default_gate_up
+            down_fn = down_fn or default_down
         self.gate_up_fn = gate_up_fn
         self.down_fn = down_fn
         self._comm_stream = None
+
+    def _default_kernels(self, gate_up_cfg, down_cfg):
+        """This package's fused gate/up and down-projection launches, with the grid cap that
+        leaves SMs to the collective when there is one."""
+        import sys
+
+        import tritonix_b200.ops  # noqa: F401
+        from tritonix_b200 import _cabi
+        mm = sys.modules["tritonix_b200.ops.matmul"]
+        sw = sys.modules["tritonix_b200.ops.swiglu"]
+        cap = {}
+        if self.world_size > 1 and self.comm_sms > 0 and self.w12.is_cuda:
+            with torch.cuda.device(self.w12.device):
+                sms = _cabi.lib.tnx_sm_count()
+            if sms > self.comm_sms + 2:
+                cap = {"max_ctas": (sms - self.comm_sms) // 2 * 2}
+        d, two_f = self.w12.shape
+        d_out = self.w_down.shape[1]
+
+        def gate_up(x, w12):
+            cfg = gate_up_cfg or sw.default_glu_config(x.shape[0], two_f, d)
+            return sw._launch_glu(x, w12, {**cfg, **cap}, "silu")
+
+        def down(h, w_down, out):
+            cfg = down_cfg or mm.default_config(h.shape[0], d_out, two_f // 2)
+            return mm._launch_matmul(h, w_down, {**cfg, **cap}, out)
+
+        return gate_up, down
 
     @property
     def world_size(self) -> int:
@@ -100,7 +139,8 @@ class TensorParallelSwiGLU:
         world = self.world_size
         on_gpu = x.is_cuda
         if on_gpu and world > 1 and self._comm_stream is None:
-            self._comm_stream = torch.cuda.Stream(device=x.device)
+            # high priority: the collective's blocks are placed as soon as SMs are free
+            self._comm_stream = torch.cuda.Stream(device=x.device, priority=-1)
         pending = []
         for lo, hi in self.chunk_bounds(m):
             h = self.gate_up_fn(x[lo:hi], self.w12)
