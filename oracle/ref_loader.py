@@ -17,8 +17,9 @@ import sys
 import types
 
 
-def load_reference(root: str = "/root/reference", interpret: bool = True):
-    """Returns (matmul_module, swiglu_module) of the reference tree at ``root``."""
+def load_reference(root: str, interpret: bool = True):
+    """Returns (matmul_module, swiglu_module) of the reference source tree at ``root`` (the
+    directory that contains its ``tritonix`` package)."""
     if interpret:
         os.environ.setdefault("TRITON_INTERPRET", "1")
     if not os.path.isdir(os.path.join(root, "tritonix")):

@@ -2,7 +2,7 @@
 (matmul_kernel, gemm_splitk_kernel, glu_kernel of ayghri/tritonix) on CPU under Triton's
 interpreter, on seeded inputs.  Run once where the reference tree is mounted:
 
-    TRITON_INTERPRET=1 python tests/golden/make_golden.py [/root/reference]
+    TRITON_INTERPRET=1 python tests/golden/make_golden.py <path to the reference source tree>
 
 Inputs are regenerated from the recorded seeds by tests (torch CPU generator); for every case
 the file stores the reference output, the inputs' fp64 checksums (to detect generator drift)
@@ -55,7 +55,9 @@ def make_inputs(name, kind, m, n, k, dtype):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: python " + sys.argv[0] + " <path to the reference source tree>")
+    root = sys.argv[1]
     ref_mm, ref_sw = load_reference(root)
     import triton
 

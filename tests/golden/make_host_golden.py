@@ -3,7 +3,7 @@
 helpers, the dispatcher's key functions) on fixed scenarios.  Run where the reference tree is
 mounted:
 
-    python tests/golden/make_host_golden.py [/root/reference]
+    python tests/golden/make_host_golden.py <path to the reference source tree>
 
 The tuner is driven with a deterministic cost model in place of the GPU timer
 (triton.testing.do_bench is replaced for the run), so the recorded visiting order, the
@@ -37,7 +37,9 @@ def cost_model(cfg):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: python " + sys.argv[0] + " <path to the reference source tree>")
+    root = sys.argv[1]
     load_reference(root)
     import triton
     rp = importlib.import_module("tritonix.utils.pruners")
