@@ -108,7 +108,8 @@ def test_split_k_with_glu_epilogue():
 
 
 @pytest.mark.parametrize("m,n,k,split_k,tile_n", [(64, 1024, 2048, 4, 128), (64, 512, 4096, 8, 128), (8, 256, 1024, 2, 256),
-                                                  (128, 256, 2048, 4, 64), (40, 136, 1024, 4, 128), (300, 192, 1536, 2, 64)])
+                                                  (128, 256, 2048, 4, 64), (40, 136, 1024, 4, 128), (300, 192, 1536, 2, 64),
+                                                  (64, 1024, 4096, 8, 256), (48, 512, 2048, 4, 256)])
 def test_cluster_exchange_matches_workspace_path(m, n, k, split_k, tile_n, monkeypatch):
     """2, 4 or 8 slices of a small tile exchange partials through cluster shared memory; the
     result must be bit-identical to the workspace path (same fp32 sum, same order)."""

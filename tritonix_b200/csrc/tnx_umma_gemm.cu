@@ -62,6 +62,7 @@ struct UmmaParams {
                         // partials through distributed shared memory (no workspace)
   int tile_k;
   int b_kmajor;         // 1: B is stored N x K (K contiguous, e.g. a transposed weight view)
+  int staging_bytes;    // epilogue staging region (two 16 KiB store buffers, or one split-K partial)
   int a_rows;           // rows of A that TMA brings in per stage (128, or fewer for a skinny M)
   int stages;
   int acc_stages;
@@ -209,7 +210,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const uint32_t smem_a = base_addr;
   const uint32_t smem_b = smem_a + p.stages * a_stage_bytes;
   const uint32_t smem_out = smem_b + p.stages * b_stage_bytes;  // 2 staging buffers
-  Ctrl* ctrl = reinterpret_cast<Ctrl*>(base_ptr + (smem_out - base_addr) + 2 * kStagingBytes);
+  Ctrl* ctrl = reinterpret_cast<Ctrl*>(base_ptr + (smem_out - base_addr) + p.staging_bytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -893,7 +894,19 @@ inline int a_box_rows(const tnx_problem& p, const tnx_config& cfg) {
 static bool use_cluster_split(const tnx_problem& p, const tnx_config& cfg, int split) {
   if (cfg.cta_group != 1 || (split != 2 && split != 4 && split != 8)) return false;
   if (getenv("TNX_NO_CLUSTER_SPLITK") != nullptr) return false;
-  return static_cast<long long>(a_box_rows(p, cfg)) * cfg.tile_n * 4 <= 2 * kStagingBytes;
+  const int rows = a_box_rows(p, cfg);
+  const long long partial = static_cast<long long>(rows) * cfg.tile_n * 4;
+  // Fits the regular staging area, or (skinny M only) a staging area grown to 64 KiB.
+  return partial <= 2 * kStagingBytes || (rows <= 64 && partial <= 4 * kStagingBytes);
+}
+
+// Bytes of shared memory set aside for the epilogue.
+static int staging_bytes_for(const tnx_problem& p, const tnx_config& cfg, int split) {
+  if (split > 1 && use_cluster_split(p, cfg, split)) {
+    const int partial = a_box_rows(p, cfg) * cfg.tile_n * 4;
+    if (partial > 2 * kStagingBytes) return (partial + 1023) / 1024 * 1024;
+  }
+  return 2 * kStagingBytes;
 }
 
 bool umma_eligible(const tnx_problem& p, const char** why) {
@@ -955,9 +968,17 @@ int umma_query(const tnx_problem& p, tnx_config* cfg, tnx_resources* out) {
     return TNX_ERR_INVALID;
   }
 
+  const int tile_rows = kRowsPerCta * cfg->cta_group;
+  const int tiles_m = cdiv(p.m, tile_rows);
+  const int tiles_n = cdiv(p.n, cfg->tile_n);
+  const int num_kb = cdiv(p.k, cfg->tile_k);
+  int split = cfg->split_k > num_kb ? num_kb : cfg->split_k;
+  const int kb_per = cdiv(num_kb, split);
+  split = cdiv(num_kb, kb_per);  // no empty slice
+
   const int load_n = cfg->tile_n / cfg->cta_group;
   const int stage_bytes = (a_box_rows(p, *cfg) + load_n) * cfg->tile_k * 2;
-  const int fixed = 2 * kStagingBytes + kCtrlBytes + kAlignSlack;
+  const int fixed = staging_bytes_for(p, *cfg, split) + kCtrlBytes + kAlignSlack;
   if (cfg->stages == 0) {
     int s = (kMaxDynamicSmem - fixed) / stage_bytes;
     cfg->stages = s > 8 ? 8 : s;
@@ -969,14 +990,6 @@ int umma_query(const tnx_problem& p, tnx_config* cfg, tnx_resources* out) {
   const long long smem = static_cast<long long>(cfg->stages) * stage_bytes + fixed;
   int tmem = 32;
   while (tmem < cfg->acc_stages * cfg->tile_n) tmem <<= 1;
-
-  const int tile_rows = kRowsPerCta * cfg->cta_group;
-  const int tiles_m = cdiv(p.m, tile_rows);
-  const int tiles_n = cdiv(p.n, cfg->tile_n);
-  const int num_kb = cdiv(p.k, cfg->tile_k);
-  int split = cfg->split_k > num_kb ? num_kb : cfg->split_k;
-  const int kb_per = cdiv(num_kb, split);
-  split = cdiv(num_kb, kb_per);  // no empty slice
 
   out->kernel = TNX_KERNEL_TCGEN05;
   out->smem_bytes = static_cast<int32_t>(smem > 0x7fffffff ? 0x7fffffff : smem);
@@ -1062,6 +1075,7 @@ int umma_launch(const tnx_problem& p, const tnx_config& cfg, const tnx_resources
   kp.kb_per_slice = cdiv(kp.num_kb, res.split_k);
   kp.tile_k = cfg.tile_k;
   kp.a_rows = a_rows;
+  kp.staging_bytes = staging_bytes_for(p, cfg, res.split_k);
   kp.b_kmajor = b_kmajor ? 1 : 0;
   kp.stages = cfg.stages;
   kp.acc_stages = cfg.acc_stages;
