@@ -252,7 +252,7 @@ _plans: dict = {}
 
 def _plan(m, n, k, dtype, strides, cfg, epilogue):
     """(problem, config, resources) for a launch signature; validated once, then reused."""
-    key = (m, n, k, dtype, strides, epilogue, tuple(sorted(cfg.items())) if cfg else ())
+    key = (m, n, k, dtype, strides, epilogue, tuple(cfg.items()) if cfg else ())
     plan = _plans.get(key)
     if plan is None:
         problem = make_problem(m, n, k, dtype, strides, epilogue)
@@ -272,8 +272,7 @@ def launch_raw(device: torch.device, dtype: torch.dtype, a_ptr: int, b_ptr: int,
     stream of ``device``.  With ``tile_order="hilbert"`` the tile table is generated here;
     ``tile_order="table"`` takes it from ``tile_table`` (int32 CUDA tensor, one packed
     ``(row << 16) | col`` word per tile)."""
-    problem, config, res = _plan(int(m), int(n), int(k), dtype, tuple(int(s) for s in strides),
-                                 cfg, int(epilogue))
+    problem, config, res = _plan(m, n, k, dtype, tuple(strides), cfg, epilogue)
     idx = device.index if device.index is not None else torch.cuda.current_device()
     switch = idx != torch.cuda.current_device()
     if switch:

@@ -775,8 +775,46 @@ EncodeTiledFn get_encode_fn() {
 
 // 2-D row-major tensor of 16-bit elements: `cols` contiguous elements per row, `rows` rows,
 // `pitch_elems` elements between rows; box = box_cols x box_rows with the 128-byte swizzle.
+// Small cache of encoded tensor maps: serving loops call with the same buffers over and over,
+// and the driver call that encodes a map costs more than the lookup.
+struct TmapKey {
+  const void* ptr;
+  int64_t cols, rows, pitch;
+  int32_t dtype, box_cols, box_rows, is_operand;
+  bool operator==(const TmapKey& o) const {
+    return ptr == o.ptr && cols == o.cols && rows == o.rows && pitch == o.pitch &&
+           dtype == o.dtype && box_cols == o.box_cols && box_rows == o.box_rows &&
+           is_operand == o.is_operand;
+  }
+};
+struct TmapSlot {
+  TmapKey key;
+  CUtensorMap map;
+  bool valid;
+};
+constexpr int kTmapSlots = 256;
+std::mutex g_tmap_mu;
+TmapSlot g_tmap_cache[kTmapSlots];
+
+inline unsigned tmap_hash(const TmapKey& k) {
+  uint64_t h = reinterpret_cast<uint64_t>(k.ptr) * 0x9E3779B97F4A7C15ull;
+  h ^= static_cast<uint64_t>(k.cols) * 0xC2B2AE3D27D4EB4Full + static_cast<uint64_t>(k.rows) * 0x165667B19E3779F9ull;
+  h ^= static_cast<uint64_t>(k.pitch) << 17 ^ static_cast<uint64_t>(k.box_rows) << 7 ^ static_cast<uint64_t>(k.box_cols);
+  h ^= h >> 29;
+  return static_cast<unsigned>(h) % kTmapSlots;
+}
+
 int make_tmap(CUtensorMap* out, const void* ptr, int dtype, int64_t cols, int64_t rows,
               int64_t pitch_elems, int box_cols, int box_rows, bool is_operand) {
+  const TmapKey key{ptr, cols, rows, pitch_elems, dtype, box_cols, box_rows, is_operand ? 1 : 0};
+  const unsigned slot = tmap_hash(key);
+  {
+    std::lock_guard<std::mutex> lock(g_tmap_mu);
+    if (g_tmap_cache[slot].valid && g_tmap_cache[slot].key == key) {
+      *out = g_tmap_cache[slot].map;
+      return TNX_OK;
+    }
+  }
   EncodeTiledFn encode = get_encode_fn();
   if (encode == nullptr) {
     set_error("cuTensorMapEncodeTiled is not available from the CUDA driver");
@@ -797,6 +835,12 @@ int make_tmap(CUtensorMap* out, const void* ptr, int dtype, int64_t cols, int64_
               static_cast<int>(r), ptr, static_cast<long long>(rows), static_cast<long long>(cols),
               static_cast<long long>(pitch_elems));
     return TNX_ERR_CUDA;
+  }
+  {
+    std::lock_guard<std::mutex> lock(g_tmap_mu);
+    g_tmap_cache[slot].key = key;
+    g_tmap_cache[slot].map = *out;
+    g_tmap_cache[slot].valid = true;
   }
   return TNX_OK;
 }
@@ -853,6 +897,38 @@ cudaError_t allow_full_smem(KernelFn fn) {
   return e;
 }
 
+// cudaOccupancyMaxActiveClusters, remembered per (kernel, device, shared memory, cluster size).
+cudaError_t max_active_clusters(KernelFn fn, const cudaLaunchConfig_t& lc, int* out) {
+  struct Entry {
+    KernelFn fn;
+    int dev;
+    size_t smem;
+    unsigned cluster;
+    int fit;
+  };
+  static std::mutex mu;
+  static std::vector<Entry> seen;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  const unsigned cluster = lc.attrs[0].val.clusterDim.x;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    for (const Entry& en : seen)
+      if (en.fn == fn && en.dev == dev && en.smem == lc.dynamicSmemBytes && en.cluster == cluster) {
+        *out = en.fit;
+        return cudaSuccess;
+      }
+  }
+  int fit = 0;
+  e = cudaOccupancyMaxActiveClusters(&fit, reinterpret_cast<const void*>(fn), &lc);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> lock(mu);
+  seen.push_back({fn, dev, lc.dynamicSmemBytes, cluster, fit});
+  *out = fit;
+  return cudaSuccess;
+}
+
 int device_sm_count() {
   static int sms = -1;
   if (sms < 0) {
@@ -893,7 +969,7 @@ inline int a_box_rows(const tnx_problem& p, const tnx_config& cfg) {
 // staging area.  Then no workspace is needed at all.
 static bool use_cluster_split(const tnx_problem& p, const tnx_config& cfg, int split) {
   if (cfg.cta_group != 1 || (split != 2 && split != 4 && split != 8)) return false;
-  if (getenv("TNX_NO_CLUSTER_SPLITK") != nullptr) return false;
+  if (getenv("TNX_NO_CLUSTER_SPLITK") != nullptr) return false;  // read every time: tests flip it
   const int rows = a_box_rows(p, cfg);
   const long long partial = static_cast<long long>(rows) * cfg.tile_n * 4;
   // Fits the regular staging area, or (skinny M only) a staging area grown to 64 KiB.
@@ -1119,7 +1195,7 @@ int umma_launch(const tnx_problem& p, const tnx_config& cfg, const tnx_resources
   if (xchg) {
     // Clusters of split_k CTAs do not always tile the GPU evenly: ask how many fit at once.
     int fit = 0;
-    e = cudaOccupancyMaxActiveClusters(&fit, reinterpret_cast<const void*>(fn), &lc);
+    e = max_active_clusters(fn, lc, &fit);
     if (e != cudaSuccess || fit < 1) {
       set_error("clusters of %d CTAs cannot be scheduled for the split-K exchange: %s", res.split_k,
                 e != cudaSuccess ? cudaGetErrorString(e) : "none fit");
