@@ -233,12 +233,32 @@ def setup_mlp(rank, world, dev, chunks=0, comm_sms=0):
 
 
 # ---------------------------------------------------------------------------------------------
-def time_steps(fn, steps, warmup, barrier):
+def time_steps(fn, steps, warmup, barrier, graph=False):
+    """Device time of exactly `steps` calls of fn.  With graph=True the `steps` launches are
+    captured once into a CUDA graph (the way a decode loop issues a short, launch-latency-bound
+    kernel) and the timed region is one replay of that graph."""
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
-    barrier()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                for _ in range(steps):
+                    fn()
+            g.replay()  # warm-up replay
+            torch.cuda.synchronize()
+            barrier()
+            start.record(side)
+            g.replay()
+            end.record(side)
+        torch.cuda.synchronize()
+        barrier()
+        return start.elapsed_time(end)
+    barrier()
     start.record()
     for _ in range(steps):
         fn()
@@ -347,6 +367,9 @@ def main():
                          "(default: 1 on one GPU, 4 otherwise)")
     ap.add_argument("--comm-sms", type=int, default=0,
                     help="mlp on >1 GPU: SMs the GEMM grids leave free for the all-reduce kernel")
+    ap.add_argument("--launch", choices=["auto", "eager", "graph"], default="auto",
+                    help="how the timed steps are issued: one by one, or as one CUDA graph of "
+                         "`steps` launches (auto: graph for the launch-latency-bound splitk workload)")
     ap.add_argument("--no-e2e", action="store_true",
                     help="skip the host-buffer leg (used for profiler captures of the kernel)")
     args = ap.parse_args()
@@ -396,8 +419,9 @@ def main():
         step, e2e_step, work = setup_contraction(args.workload, rank, world, dev)
 
     # ---- device-timed value (operands resident in HBM)
+    use_graph = args.launch == "graph" or (args.launch == "auto" and args.workload == "splitk")
     with ClockSampler(local_rank) as clocks:
-        ms_total = time_steps(step, args.steps, args.warmup, barrier)
+        ms_total = time_steps(step, args.steps, args.warmup, barrier, graph=use_graph)
     tnx.check_status(dev)
     ms_total = max_over_ranks(ms_total)
     ms_step = ms_total / args.steps
@@ -443,6 +467,7 @@ def main():
                    **({"allreduce_chunks": work["chunks"], "comm_sms": args.comm_sms}
                       if args.workload == "mlp" and world > 1 else {}),
                    "parallelism": ("tp%d" % world) if strong else ("rows_sharded_x%d" % world),
+                   "launch": "cuda_graph_of_%d_steps" % args.steps if use_graph else "eager",
                    "l2": ("operands rotate through %d copies (> 3x L2)" % work["copies"]) if work["copies"] > 1
                    else "operands exceed the 126 MB L2"},
         "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": work["h2d"],

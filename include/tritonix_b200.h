@@ -193,6 +193,14 @@ int tnx_gemm_splitk_static(const tnx_problem* problem, const tnx_config* config,
  */
 int tnx_read_status(int32_t* status_word, int32_t* code_out, void* stream);
 
+/*
+ * Self-test of the failure path (no counterpart in the reference): enqueues a one-warp kernel
+ * that waits, with the same bounded wait the GEMM kernels use, on a barrier nothing signals.
+ * After `limit_ms` (1..5000) the wait gives up, the kernel writes code 0x1ff to *status_word and
+ * returns normally; tnx_read_status() then reports TNX_ERR_DEVICE.  Nothing traps or faults.
+ */
+int tnx_selftest_bounded_wait(int32_t* status_word, uint32_t limit_ms, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -196,6 +196,24 @@ def test_do_bench_returns_positive_ms():
     assert 0 < ms < 5 and 0 < med < 5
 
 
+def test_expired_wait_is_reported_not_fatal():
+    """A device wait that nothing satisfies gives up after its limit, the kernel returns, the
+    status word carries a code, Python raises DeviceStatusError, and the context keeps working."""
+    dev = torch.device(DEV, torch.cuda.current_device())
+    word = _cabi.status_word(dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    assert _cabi.lib.tnx_selftest_bounded_wait(word.data_ptr(), 50, stream) == _cabi.OK
+    with pytest.raises(tnx.DeviceStatusError, match="0x1ff"):
+        tnx.check_status(dev)
+    tnx.check_status(dev)  # the word was reset; nothing else is wrong
+    a, b = seeded(128, 128, 128, f16)
+    c = torch.empty(128, 128, device=DEV, dtype=f16)
+    _cabi.launch(a.to(DEV), b.to(DEV), c, None)
+    tnx.check_status(dev)
+    assert_close(c.cpu(), O.matmul_oracle(a, b), f16)
+    assert _cabi.lib.tnx_selftest_bounded_wait(None, 50, stream) == _cabi.ERR_INVALID
+
+
 def test_status_word_reports_clean_after_all_launches():
     tnx.check_status()
     w = _cabi.status_word(torch.device(DEV, torch.cuda.current_device()))

@@ -70,7 +70,7 @@ class Resources(ctypes.Structure):
 
 
 EXPORTS = ("tnx_version", "tnx_last_error", "tnx_sm_count", "tnx_gemm_query", "tnx_gemm",
-           "tnx_glu", "tnx_read_status", "tnx_gemm_splitk_static")
+           "tnx_glu", "tnx_read_status", "tnx_gemm_splitk_static", "tnx_selftest_bounded_wait")
 STATIC_SCRATCH_BYTES = 16 * 1024 * 1024 + 65536
 
 
@@ -102,6 +102,8 @@ def _load() -> ctypes.CDLL:
     lib.tnx_gemm_splitk_static.argtypes = [ctypes.POINTER(Problem), ctypes.POINTER(Config),
                                            ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                            ctypes.c_void_p, ctypes.c_void_p]
+    lib.tnx_selftest_bounded_wait.restype = ctypes.c_int
+    lib.tnx_selftest_bounded_wait.argtypes = [ctypes.c_void_p, ctypes.c_uint32, ctypes.c_void_p]
     lib.tnx_read_status.restype = ctypes.c_int
     lib.tnx_read_status.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32),
                                     ctypes.c_void_p]

@@ -1310,3 +1310,41 @@ extern "C" int tnx_gemm_splitk_static(const tnx_problem* problem, const tnx_conf
   }
   return tnx::umma_launch(*problem, cfg, res, a, b, c, scratch, nullptr, status_word, s);
 }
+
+// ---------------------------------------------------------------------------------------------
+// Self-test of the bounded-wait machinery
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+// One warp waits on an mbarrier that nothing ever arrives on, through the same ptx::mbar_wait the
+// GEMM kernels use.  The wait must give up after `limit_ns`, record a code and let the kernel
+// return normally: no trap, no fault, the context stays usable.
+__global__ void bounded_wait_selftest_kernel(int* status, unsigned long long limit_ns) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    tnx::ptx::mbar_init(tnx::ptx::smem_u32(&bar), 1);
+    abort_flag = 0;
+    tnx::ptx::fence_mbar_init();
+  }
+  __syncthreads();
+  const bool ok = tnx::ptx::mbar_wait(tnx::ptx::smem_u32(&bar), 0, &abort_flag, limit_ns);
+  if (!ok && threadIdx.x == 0 && status != nullptr) atomicCAS(status, 0, 0x1ff);
+}
+
+}  // namespace
+
+extern "C" int tnx_selftest_bounded_wait(int32_t* status_word, uint32_t limit_ms, void* stream) {
+  if (status_word == nullptr || limit_ms == 0 || limit_ms > 5000) {
+    tnx::set_error("tnx_selftest_bounded_wait needs a status word and a limit of 1..5000 ms");
+    return TNX_ERR_INVALID;
+  }
+  bounded_wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      status_word, static_cast<unsigned long long>(limit_ms) * 1000000ull);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    tnx::set_error("self-test launch failed: %s", cudaGetErrorString(e));
+    return TNX_ERR_CUDA;
+  }
+  return TNX_OK;
+}
