@@ -188,7 +188,8 @@ def setup_contraction(workload, rank, world, dev):
     return step, e2e_step, work
 
 
-def setup_mlp(rank, world, dev, chunks=0, comm_sms=0):
+def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1):
+    comm_sms = (32 if world >= 8 else 0) if comm_sms < 0 else comm_sms
     """SwiGLU MLP, tensor parallel: column-parallel fused gate/up, row-parallel down, one
     all-reduce.  Global weights come from fixed seeds and are sliced, so every world size
     computes the same function."""
@@ -228,7 +229,7 @@ def setup_mlp(rank, world, dev, chunks=0, comm_sms=0):
     nchunks = len(mlp.chunk_bounds(m))
     work = dict(flops=flops, bytes=None, units=float(m), launches=2 * nchunks, h2d=x_host.numel() * 2,
                 d2h=y_host.numel() * 2, copies=1, cfg={"gate_up": GLU_CFG, "down": GEMM_CFG},
-                out=None, check=None, chunks=nchunks)
+                out=None, check=None, chunks=nchunks, comm_sms=comm_sms)
     return step, e2e_step, work
 
 
@@ -365,8 +366,9 @@ def main():
     ap.add_argument("--chunks", type=int, default=0,
                     help="mlp: row chunks whose all-reduce overlaps the next chunk's GEMMs "
                          "(default: 1 on one GPU, 4 otherwise)")
-    ap.add_argument("--comm-sms", type=int, default=0,
-                    help="mlp on >1 GPU: SMs the GEMM grids leave free for the all-reduce kernel")
+    ap.add_argument("--comm-sms", type=int, default=-1,
+                    help="mlp on >1 GPU: SMs the GEMM grids leave free for the all-reduce kernel "
+                         "(-1: 32 on 8 or more GPUs, else 0)")
     ap.add_argument("--launch", choices=["auto", "eager", "graph"], default="auto",
                     help="how the timed steps are issued: one by one, or as one CUDA graph of "
                          "`steps` launches (auto: graph for the launch-latency-bound splitk workload)")
@@ -389,10 +391,11 @@ def main():
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         pg_options = None
-        if args.workload == "mlp" and args.comm_sms > 0:
+        reserve = (32 if world >= 8 else 0) if args.comm_sms < 0 else args.comm_sms
+        if args.workload == "mlp" and reserve > 0:
             try:  # keep the all-reduce inside the SMs that the GEMM grids leave free
                 pg_options = dist.ProcessGroupNCCL.Options()
-                pg_options.config.max_ctas = args.comm_sms
+                pg_options.config.max_ctas = reserve
             except Exception:
                 pg_options = None
         dist.init_process_group("nccl", device_id=dev, pg_options=pg_options)
@@ -464,7 +467,7 @@ def main():
         "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": WORKLOADS[args.workload]["dtype"],
         "data": "synthetic",
         "config": {"workload": WORKLOADS[args.workload]["name"], "kernel_config": work["cfg"],
-                   **({"allreduce_chunks": work["chunks"], "comm_sms": args.comm_sms}
+                   **({"allreduce_chunks": work["chunks"], "comm_sms": work["comm_sms"]}
                       if args.workload == "mlp" and world > 1 else {}),
                    "parallelism": ("tp%d" % world) if strong else ("rows_sharded_x%d" % world),
                    "launch": "cuda_graph_of_%d_steps" % args.steps if use_graph else "eager",

@@ -70,15 +70,17 @@ class TensorParallelSwiGLU:
     memory), so a collective's kernel cannot slip in beside them; it only gets SMs as GEMM CTAs
     retire.  ``comm_sms > 0`` makes the default kernels leave that many SMs free (grid capped at
     SM count - comm_sms) so that NCCL's all-reduce of chunk i runs while chunk i+1 is computed.
-    It pays off only when communication is a large share of the step (measured on 8 B200:
-    8 chunks with 32 SMs left free beat 4 chunks with none by 4-7 %; at 2 GPUs it loses).
+    It pays off only when communication is a large share of the step: on 8 B200, 4 chunks with
+    32 SMs left free take 1.48-1.54 ms per 32768-token step against 1.65-1.86 ms with none; with
+    16 or 24 SMs NCCL loses bandwidth, and on 2 GPUs the slower GEMMs cost more than is hidden.
+    ``None`` (default) picks 32 on 8 or more ranks and 0 otherwise.
     ``gate_up_cfg`` / ``down_cfg`` override the kernel configurations of the default kernels.
     """
 
     def __init__(self, w12_shard: torch.Tensor, w_down_shard: torch.Tensor,
                  group: Optional[dist.ProcessGroup] = None, chunks: int = 4,
                  gate_up_fn: Optional[Callable] = None, down_fn: Optional[Callable] = None,
-                 comm_sms: int = 0, gate_up_cfg: Optional[dict] = None,
+                 comm_sms: Optional[int] = None, gate_up_cfg: Optional[dict] = None,
                  down_cfg: Optional[dict] = None):
         if w12_shard.shape[1] != 2 * w_down_shard.shape[0]:
             raise ValueError("w12 shard must have twice as many columns as w_down shard has rows")
@@ -86,6 +88,8 @@ class TensorParallelSwiGLU:
         self.w_down = w_down_shard
         self.group = group
         self.chunks = max(1, int(chunks))
+        if comm_sms is None:  # measured on 8 B200: 32 SMs left to NCCL; not worth it on fewer ranks
+            comm_sms = 32 if self.world_size >= 8 else 0
         self.comm_sms = max(0, int(comm_sms))
         if gate_up_fn is None or down_fn is None:
             default_gate_up, default_down = self._default_kernels(gate_up_cfg, down_cfg)
