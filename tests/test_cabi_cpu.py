@@ -82,8 +82,12 @@ def test_invalid_and_unbuilt_configs_are_value_errors():
         _cabi.make_config({"tile_q": 3})
     with pytest.raises(ValueError, match="unsupported dtype"):
         _cabi.make_problem(1, 1, 1, torch.int8, (1, 1, 1, 1, 1, 1))
-    with pytest.raises(ValueError, match="unit inner strides"):
-        q(512, 512, 512, {"kernel": "tcgen05"}, strides=(1, 512, 512, 1, 512, 1))
+    with pytest.raises(ValueError, match="unit stride"):
+        q(512, 512, 512, {"kernel": "tcgen05"}, strides=(2, 1024, 512, 1, 512, 1))
+    with pytest.raises(ValueError, match="unit stride"):
+        q(512, 512, 512, {"kernel": "tcgen05"}, strides=(512, 1, 512, 1, 1, 512))   # column-major C
+    # a transposed A (stored K x M) is a legal tcgen05 operand
+    assert q(512, 512, 512, {"kernel": "tcgen05"}, strides=(1, 512, 512, 1, 512, 1)).kernel == _cabi.KERNEL_TCGEN05
     # a transposed B (stored N x K) is a legal tcgen05 operand
     assert q(512, 512, 512, {"kernel": "tcgen05"}, strides=(512, 1, 1, 512, 512, 1)).kernel == _cabi.KERNEL_TCGEN05
 

@@ -107,6 +107,27 @@ def test_transposed_b_operand(m, n, k, dtype, cfg, epi):
     assert_close(c.cpu(), ref, dtype)
 
 
+@pytest.mark.parametrize("m,n,k,dtype,cfg,b_transposed", [
+    (256, 384, 512, bf16, {"tile_n": 128}, False),
+    (1000, 520, 264, f16, {"tile_n": 256, "tile_k": 128, "stages": 2}, False),
+    (2048, 1024, 1024, bf16, {"tile_n": 256, "cta_group": 2, "tile_k": 128, "stages": 3}, True),
+    (64, 1024, 2048, f16, {"tile_n": 128, "split_k": 4}, False),
+    (200, 256, 320, bf16, {"tile_n": 64, "split_k": 2}, True),
+])
+def test_transposed_a_operand(m, n, k, dtype, cfg, b_transposed):
+    """A given as the transpose of a (K, M) row-major tensor (as in a weight-gradient product
+    X^T . dY) runs on the tcgen05 kernel as an M-major operand, without a copy."""
+    a, b = seeded(m, k, n, dtype, seed=m + 3)
+    a_view = a.t().contiguous().to(DEV).t()            # logical (M, K), strides (1, M)
+    assert a_view.stride() == (1, m)
+    b_dev = b.t().contiguous().to(DEV).t() if b_transposed else b.to(DEV)
+    c = torch.full((m, n), float("nan"), device=DEV, dtype=dtype)
+    res = _cabi.launch(a_view, b_dev, c, {**T, **cfg})
+    _cabi.check_status(c.device)
+    assert res.kernel == _cabi.KERNEL_TCGEN05
+    assert_close(c.cpu(), O.matmul_oracle(a, b), dtype)
+
+
 def test_output_tails_are_not_overwritten():
     """Canary rows/columns around C: the TMA store clips at the tensor bounds."""
     a, b = seeded(200, 72, 136, f16, seed=5)

@@ -180,9 +180,13 @@ def require_cuda(*tensors: torch.Tensor) -> None:
 def umma_eligible_tensors(a: torch.Tensor, b: torch.Tensor) -> bool:
     """True when (a, b) can run on the TMA/tcgen05 kernels (the only ones worth tuning)."""
     if not (a.dtype in (torch.float16, torch.bfloat16) and a.dtype == b.dtype
-            and a.dim() == 2 and b.dim() == 2 and a.stride(1) == 1 and a.stride(0) % 8 == 0
+            and a.dim() == 2 and b.dim() == 2
             and a.shape[1] % 8 == 0 and b.shape[1] % 8 == 0
             and a.data_ptr() % 16 == 0 and b.data_ptr() % 16 == 0):
+        return False
+    row_major_a = a.stride(1) == 1 and a.stride(0) % 8 == 0
+    transposed_a = a.stride(0) == 1 and a.stride(1) % 8 == 0 and a.shape[0] % 8 == 0
+    if not (row_major_a or transposed_a):
         return False
     row_major_b = b.stride(1) == 1 and b.stride(0) % 8 == 0
     transposed_b = b.stride(0) == 1 and b.stride(1) % 8 == 0   # e.g. weight.t()

@@ -62,6 +62,7 @@ struct UmmaParams {
                         // partials through distributed shared memory (no workspace)
   int tile_k;
   int b_kmajor;         // 1: B is stored N x K (K contiguous, e.g. a transposed weight view)
+  int a_mmajor;         // 1: A is stored K x M (M contiguous, e.g. a transposed activation view)
   int staging_bytes;    // epilogue staging region (two 16 KiB store buffers, or one split-K partial)
   int a_rows;           // rows of A that TMA brings in per stage (128, or fewer for a skinny M)
   int stages;
@@ -293,10 +294,17 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const int k0 = kb * TILE_K;
           if (CTA_GROUP == 1) {
             ptx::mbar_arrive_expect_tx(full_bar, stage_tx);
+            if (p.a_mmajor) {  // two 64-row atoms of tile_k x 128 B, like a row-major B
 #pragma unroll
-            for (int ka = 0; ka < TILE_K / kAtomElems; ++ka)
-              ptx::tma_load_2d(a_dst + ka * a_atom_bytes, &tmap_a,
-                               k0 + ka * kAtomElems, row0, full_bar);
+              for (int ma = 0; ma < kRowsPerCta / kAtomElems; ++ma)
+                ptx::tma_load_2d(a_dst + ma * (TILE_K * kAtomBytes), &tmap_a, row0 + ma * kAtomElems,
+                                 k0, full_bar);
+            } else {
+#pragma unroll
+              for (int ka = 0; ka < TILE_K / kAtomElems; ++ka)
+                ptx::tma_load_2d(a_dst + ka * a_atom_bytes, &tmap_a, k0 + ka * kAtomElems, row0,
+                                 full_bar);
+            }
             if (p.b_kmajor) {
 #pragma unroll
               for (int ka = 0; ka < TILE_K / kAtomElems; ++ka)
@@ -312,10 +320,17 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             // Both CTAs' loads complete on the leader's barrier; the leader announces the bytes.
             const uint32_t leader_bar = ptx::mapa(full_bar, 0);
             if (leader) ptx::mbar_arrive_expect_tx(full_bar, stage_tx);
+            if (p.a_mmajor) {
 #pragma unroll
-            for (int ka = 0; ka < TILE_K / kAtomElems; ++ka)
-              ptx::tma_load_2d_pair(a_dst + ka * a_atom_bytes, &tmap_a,
-                                    k0 + ka * kAtomElems, row0, leader_bar);
+              for (int ma = 0; ma < kRowsPerCta / kAtomElems; ++ma)
+                ptx::tma_load_2d_pair(a_dst + ma * (TILE_K * kAtomBytes), &tmap_a,
+                                      row0 + ma * kAtomElems, k0, leader_bar);
+            } else {
+#pragma unroll
+              for (int ka = 0; ka < TILE_K / kAtomElems; ++ka)
+                ptx::tma_load_2d_pair(a_dst + ka * a_atom_bytes, &tmap_a, k0 + ka * kAtomElems,
+                                      row0, leader_bar);
+            }
             if (p.b_kmajor) {
 #pragma unroll
               for (int ka = 0; ka < TILE_K / kAtomElems; ++ka)
@@ -343,13 +358,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     if (leader && lane == 0) {
       // Instruction descriptor: fp32 accumulate, A K-major, B MN-major, M x N = (128*CTA_GROUP) x TILE_N.
       const uint32_t fmt = BF16 ? 1u : 0u;
-      const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (0u << 15) |
+      const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((p.a_mmajor ? 1u : 0u) << 15) |
                              ((p.b_kmajor ? 0u : 1u) << 16) |
                              (static_cast<uint32_t>(TILE_N >> 3) << 17) |
                              (static_cast<uint32_t>((kRowsPerCta * CTA_GROUP) >> 4) << 24);
       // A: rows of 128 B, 8-row groups 1024 B apart.  B: 64-column atoms of tile_k rows x 128 B;
       // LBO = bytes between atoms along N, SBO = bytes between 8-row groups along K.
-      const uint64_t a_desc_hi = ptx::make_smem_desc(0, 0, 1024);
+      // An A stored K x M is an MN-major operand: 64-row atoms of tile_k x 128 B, LBO to the next atom.
+      const uint64_t a_desc_hi =
+          p.a_mmajor ? ptx::make_smem_desc(0, TILE_K * kAtomBytes, 1024) : ptx::make_smem_desc(0, 0, 1024);
       // A K-major B (stored N x K) is laid out like A: rows of 128 B, one slab per 64 K elements.
       const uint64_t b_desc_hi =
           p.b_kmajor ? ptx::make_smem_desc(0, 0, 1024) : ptx::make_smem_desc(0, TILE_K * kAtomBytes, 1024);
@@ -382,7 +399,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const uint32_t b_src = smem_b + stage * b_stage_bytes;
 #pragma unroll
           for (int k16 = 0; k16 < TILE_K / 16; ++k16) {
-            const uint32_t a_addr = a_src + (k16 >> 2) * a_atom_bytes + (k16 & 3) * 32;
+            const uint32_t a_addr = p.a_mmajor ? a_src + k16 * (16 * kAtomBytes)
+                                               : a_src + (k16 >> 2) * a_atom_bytes + (k16 & 3) * 32;
             const uint32_t b_addr = p.b_kmajor
                                         ? b_src + (k16 >> 2) * (LOAD_N * kAtomBytes) + (k16 & 3) * 32
                                         : b_src + k16 * (16 * kAtomBytes);
@@ -958,7 +976,7 @@ inline int cdiv(int a, int b) { return (a + b - 1) / b; }
 // Rows of A fetched per stage: a single-CTA tile over a problem with fewer than 128 rows only
 // needs (and only pays shared memory for) M rounded up to the 8-row swizzle group.
 inline int a_box_rows(const tnx_problem& p, const tnx_config& cfg) {
-  if (cfg.cta_group == 1 && p.m < kRowsPerCta) return ((p.m + 7) / 8) * 8;
+  if (cfg.cta_group == 1 && p.m < kRowsPerCta && p.stride_ak == 1) return ((p.m + 7) / 8) * 8;
   return kRowsPerCta;
 }
 
@@ -989,17 +1007,21 @@ bool umma_eligible(const tnx_problem& p, const char** why) {
   const char* w = nullptr;
   if (p.dtype != TNX_F16 && p.dtype != TNX_BF16)
     w = "tcgen05 path takes fp16 or bf16 operands";
-  else if (p.stride_ak != 1 || p.stride_cn != 1 || (p.stride_bn != 1 && p.stride_bk != 1))
-    w = "tcgen05 path needs unit inner strides (row-major A and C; B row-major or its transpose)";
-  else if ((p.stride_am % 8) != 0 || (p.stride_cm % 8) != 0 ||
+  else if (p.stride_cn != 1 || (p.stride_ak != 1 && p.stride_am != 1) ||
+           (p.stride_bn != 1 && p.stride_bk != 1))
+    w = "tcgen05 path needs a unit stride in A, in B (either dimension) and along the rows of C";
+  else if (((p.stride_ak == 1 ? p.stride_am : p.stride_ak) % 8) != 0 || (p.stride_cm % 8) != 0 ||
            ((p.stride_bn == 1 ? p.stride_bk : p.stride_bn) % 8) != 0)
     w = "tcgen05 path needs row pitches that are multiples of 16 bytes";
+  else if (p.stride_ak != 1 && (p.m % 8) != 0)
+    w = "tcgen05 path needs M to be a multiple of 8 when A is stored K x M";
   else if (p.k < 1 || p.m < 1 || p.n < 1)
     w = "empty problem";
   else if ((p.k % 8) != 0 || (p.n % 8) != 0 || (p.epilogue != TNX_EPI_NONE && (p.n % 16) != 0))
     // TMA clips and zero-fills in 16-byte units along the contiguous dimension
     w = "tcgen05 path needs K, N (and N/2 for a GLU epilogue) to be multiples of 8 elements";
-  else if (p.stride_am < p.k || (p.stride_bn == 1 ? p.stride_bk < p.n : p.stride_bn < p.k))
+  else if ((p.stride_ak == 1 ? p.stride_am < p.k : p.stride_ak < p.m) ||
+           (p.stride_bn == 1 ? p.stride_bk < p.n : p.stride_bn < p.k))
     w = "row pitch smaller than the row length";
   if (why) *why = w;
   return w == nullptr;
@@ -1124,7 +1146,9 @@ int umma_launch(const tnx_problem& p, const tnx_config& cfg, const tnx_resources
   const int n_out = glu ? p.n / 2 : p.n;
   CUtensorMap ta, tb, tc;
   const int a_rows = a_box_rows(p, cfg);
-  int rc = make_tmap(&ta, a, p.dtype, p.k, p.m, p.stride_am, kAtomElems, a_rows, true);
+  const bool a_mmajor = p.stride_ak != 1;
+  int rc = a_mmajor ? make_tmap(&ta, a, p.dtype, p.m, p.k, p.stride_ak, kAtomElems, cfg.tile_k, true)
+                    : make_tmap(&ta, a, p.dtype, p.k, p.m, p.stride_am, kAtomElems, a_rows, true);
   if (rc != TNX_OK) return rc;
   // B row-major (K x N): boxes of 64 columns x tile_k rows.  B stored N x K (a transposed view):
   // boxes of 64 K elements x the CTA's B columns, like A.
@@ -1153,6 +1177,7 @@ int umma_launch(const tnx_problem& p, const tnx_config& cfg, const tnx_resources
   kp.a_rows = a_rows;
   kp.staging_bytes = staging_bytes_for(p, cfg, res.split_k);
   kp.b_kmajor = b_kmajor ? 1 : 0;
+  kp.a_mmajor = a_mmajor ? 1 : 0;
   kp.stages = cfg.stages;
   kp.acc_stages = cfg.acc_stages;
   kp.group_m = cfg.group_m;
