@@ -39,7 +39,7 @@ def draw_case(rng: random.Random):
     return m, n, k, dtype, epi, cfg
 
 
-@pytest.mark.parametrize("seed", range(60))
+@pytest.mark.parametrize("seed", range(120))
 def test_random_problem(seed):
     rng = random.Random(1000 + seed)
     m, n, k, dtype, epi, cfg = draw_case(rng)
