@@ -166,21 +166,29 @@ def setup_contraction(workload, rank, world, dev):
     mm = sys.modules["tritonix_b200.ops.matmul"]
     sw = sys.modules["tritonix_b200.ops.swiglu"]
     mm._matmul_cfg[(m, n, k)] = {x: v for x, v in GEMM_CFG.items()}
+    mm._matmul_cfg[(1024, n, k)] = dict(GEMM_CFG)   # row chunks of the host pipeline
+    sw._glu_cfg[(1024, n, k)] = dict(GLU_CFG)
     mm._splitk_cfg[(m, n, k, SPLITK_CFG["split_k"])] = dict(SPLITK_CFG)
     sw._glu_cfg[(m, n, k)] = dict(GLU_CFG)
     if workload == "gemm":
         tnx.matmul.cache[(m, k, str(dt), k, n, str(dt))] = "cuda"  # skip the first-call timing
 
+    rows = 1024
+    pipe = tnx.HostRowPipeline(dev, k, n_out, dt, rows_per_chunk=rows) if workload == "glu" else None
+
     def e2e_step():
-        a_in.copy_(a_host, non_blocking=True)
-        b_in.copy_(b_host, non_blocking=True)
+        # every step uploads A and B from pinned host memory and downloads the result; for the
+        # two large workloads the rows of A / C are pipelined against the kernel (public helpers)
         if workload == "gemm":
-            out = tnx.matmul(a_in, b_in)
-        elif workload == "splitk":
-            out = tnx.matmul_splitk(a_in, b_in, split_k=SPLITK_CFG["split_k"])
+            tnx.matmul_from_host(a_host, b_host, c_host, rows_per_chunk=rows, b_device=b_in)
+        elif workload == "glu":
+            pipe.run(lambda xd, od: tnx.swiglu(xd, b_in, out=od), a_host, c_host,
+                     before=lambda: b_in.copy_(b_host, non_blocking=True))
         else:
-            out = tnx.swiglu(a_in, b_in)
-        c_host.copy_(out, non_blocking=True)
+            a_in.copy_(a_host, non_blocking=True)
+            b_in.copy_(b_host, non_blocking=True)
+            out = tnx.matmul_splitk(a_in, b_in, split_k=SPLITK_CFG["split_k"])
+            c_host.copy_(out, non_blocking=True)
 
     work = dict(flops=2.0 * m * n * k, bytes=float(algo_bytes), units=None, launches=1,
                 h2d=a_host.numel() * 2 + b_host.numel() * 2, d2h=c_host.numel() * 2, copies=copies,
@@ -218,12 +226,14 @@ def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1):
 
     x_host = x.cpu().pin_memory()
     y_host = torch.empty((m, d), dtype=dt).pin_memory()
-    x_in = torch.empty_like(x)
+
+    pipe = tnx.HostRowPipeline(dev, d, d, dt, rows_per_chunk=4096)
+    chunk_mlp = TensorParallelSwiGLU(w12, wd, chunks=1, comm_sms=comm_sms, gate_up_cfg=GLU_CFG,
+                                     down_cfg=GEMM_CFG)
 
     def e2e_step():
-        x_in.copy_(x_host, non_blocking=True)
-        y = mlp(x_in)
-        y_host.copy_(y, non_blocking=True)
+        # rows of x stream in, rows of y stream out, 4096 rows (one all-reduce) at a time
+        pipe.run(lambda xd, yd: chunk_mlp(xd, out=yd), x_host, y_host)
 
     flops = 2.0 * m * d * (2 * ff) + 2.0 * m * ff * d
     nchunks = len(mlp.chunk_bounds(m))

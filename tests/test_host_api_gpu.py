@@ -239,3 +239,21 @@ def test_tuned_configuration_is_persisted(tmp_path, monkeypatch):
     monkeypatch.setattr(tnx.TunableKernel, "tune", no_tuning)
     out2 = tnx.triton_matmul(a, b)
     assert torch.equal(out1, out2) and mm._matmul_cfg[(384, 640, 512)] == cfg
+
+
+def test_matmul_from_host_pipelines_rows(monkeypatch):
+    """A and the result in pinned host memory, B uploaded once: rows are pipelined through
+    upload / compute / download streams and the result equals the one-shot product."""
+    monkeypatch.setenv("TRITONIX_B200_TUNE", "0")
+    a, b = seeded(1000, 512, 384, bf16, seed=8)
+    a_host, b_host = a.pin_memory(), b.pin_memory()
+    out_host = torch.full((1000, 384), float("nan"), dtype=bf16).pin_memory()
+    tnx.matmul_from_host(a_host, b_host, out_host, rows_per_chunk=256)   # 3 full chunks + 232 rows
+    torch.cuda.synchronize()
+    tnx.check_status()
+    assert_close(out_host, O.matmul_oracle(a, b), bf16)
+    # device-resident B, second call reuses the pipeline's buffers
+    out2 = torch.empty_like(out_host).pin_memory()
+    tnx.matmul_from_host(a_host, b.to(DEV), out2, rows_per_chunk=256)
+    torch.cuda.synchronize()
+    assert torch.equal(out2, out_host)

@@ -13,6 +13,7 @@ from tritonix_b200.dispatcher import DynamicDispatcher, dynamic_dispatch
 from tritonix_b200.ops import (cuda_matmul, gemm_splitk_kernel, glu, glu_kernel,
                                interleave_weights, matmul, matmul_kernel, matmul_splitk, swiglu,
                                swiglu_kernel, swiglu_mlp, triton_matmul)
+from tritonix_b200.host_io import HostRowPipeline, matmul_from_host
 from tritonix_b200.testing import do_bench
 from tritonix_b200.utils.pruners import (CoordinateMonotonicFunction, CoordinateUnimodalFunction,
                                          MonotonicCascadeTrie)
@@ -24,7 +25,8 @@ __all__ = ["matmul", "matmul_splitk", "cuda_matmul", "triton_matmul", "matmul_ke
            "interleave_weights", "tunable", "TunableKernel", "PowerOfTwo", "Range", "Choice",
            "SpaceConfig", "ConfigSpace", "MonotonicCascadeTrie", "CoordinateUnimodalFunction",
            "CoordinateMonotonicFunction", "DynamicDispatcher", "dynamic_dispatch",
-           "OutOfResources", "DeviceStatusError", "check_status", "do_bench", "install_as_tritonix"]
+           "OutOfResources", "DeviceStatusError", "check_status", "do_bench", "install_as_tritonix",
+           "HostRowPipeline", "matmul_from_host"]
 
 
 def install_as_tritonix() -> None:

@@ -137,9 +137,10 @@ class TensorParallelSwiGLU:
         mult = 256 if m % 256 == 0 else 1
         return [shard_bounds(m, i, n, mult) for i in range(n)]
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         m = x.shape[0]
-        y = torch.empty((m, self.w_down.shape[1]), device=x.device, dtype=x.dtype)
+        y = out if out is not None else torch.empty((m, self.w_down.shape[1]), device=x.device,
+                                                    dtype=x.dtype)
         world = self.world_size
         on_gpu = x.is_cuda
         if on_gpu and world > 1 and self._comm_stream is None:
