@@ -133,4 +133,4 @@ def test_shipped_kernel_spaces_are_consistent():
         names, values = tk._memory_axes()
         assert set(names) == {"block_m", "block_n", "block_k", "num_stages"}  # the reference's axes
         assert values[names.index("block_m")][0] == max(tk.space["block_m"].values())
-    assert len(t.matmul_kernel.configs()) == 2 * 3 * 2 * 3 * 7
+    assert len(t.matmul_kernel.configs()) == 2 * 3 * 2 * 3 * 4 * 7

@@ -37,6 +37,7 @@ matmul_kernel = tunable(
         "block_n": PowerOfTwo(64, 256),
         "block_k": PowerOfTwo(64, 128),
         "group_m": Choice([4, 8, 16]),
+        "split_k": Choice([1, 2, 4, 8]),
         "num_stages": Range(2, 8),
     },
     memory_params=_MEMORY,
@@ -103,12 +104,48 @@ def default_config(m: int, n: int, k: int, split_k: int | None = None) -> dict:
     if split_k is not None:
         return {"block_m": 128, "block_n": 128 if n >= 1024 else 64, "block_k": 128, "group_m": 8,
                 "split_k": int(split_k), "num_stages": 4 if m <= 64 else 3}
-    if m > 128 and n >= 256:
-        return {"block_m": 256, "block_n": 256, "block_k": 128, "group_m": 16, "num_stages": 3}
-    if n >= 256:
-        return {"block_m": 128, "block_n": 256, "block_k": 64, "group_m": 8, "num_stages": 4}
-    return {"block_m": 128, "block_n": 128 if n > 64 else 64, "block_k": 64, "group_m": 8,
-            "num_stages": 6}
+    # Large problems: 256 x 256 tiles on CTA pairs.  Problems that cannot give most SMs such a
+    # tile take smaller single-SM tiles, and whatever still leaves SMs idle is split along K.
+    def ctas(bm, bn):
+        return -(-m // bm) * -(-n // bn) * (bm // 128)
+
+    if m > 128 and n >= 256 and ctas(256, 256) >= 100:
+        cfg = {"block_m": 256, "block_n": 256, "block_k": 128, "group_m": 16, "num_stages": 3}
+    elif n > 64 and (m <= 128 or ctas(128, 128) >= 74):
+        cfg = {"block_m": 128, "block_n": 128, "block_k": 128, "group_m": 8, "num_stages": 4}
+    else:
+        cfg = {"block_m": 128, "block_n": 64, "block_k": 128, "group_m": 8, "num_stages": 4}
+    cfg["split_k"] = _auto_split(m, n, k, cfg)
+    # deepest ring that fits next to the 34 KiB of epilogue staging and barriers (at most 6 slots)
+    pair = cfg["block_m"] // 128
+    a_rows = 128 if (m >= 128 or pair == 2) else -(-m // 8) * 8
+    stage_bytes = (a_rows + cfg["block_n"] // pair) * cfg["block_k"] * 2
+    cfg["num_stages"] = max(2, min(6, (232448 - 34304) // stage_bytes))
+    return cfg
+
+
+_SM_COUNT = 148  # B200
+
+
+def _auto_split(m: int, n: int, k: int, cfg: dict) -> int:
+    """K slices for a problem whose tiles cannot fill the GPU: the largest power of two (at most
+    8) that still fits one wave of CTAs and leaves every slice at least 512 elements of K."""
+    tiles = -(-m // cfg["block_m"]) * -(-n // cfg["block_n"]) * (cfg["block_m"] // 128)
+    split = 1
+    while split < 8 and tiles * split * 2 <= _SM_COUNT and k // (split * 2) >= 512:
+        split *= 2
+    return split
+
+
+def _plausible_split(m: int, n: int, k: int):
+    """Split factors worth timing: 1 always, larger ones only while one wave of CTAs holds them."""
+    def keep(cfg):
+        s = cfg.get("split_k", 1)
+        if s == 1:
+            return True
+        tiles = -(-m // cfg["block_m"]) * -(-n // cfg["block_n"]) * (cfg["block_m"] // 128)
+        return tiles * s <= _SM_COUNT and k // s >= 256
+    return keep
 
 
 def _tuning_enabled() -> bool:
@@ -156,7 +193,9 @@ def cuda_matmul(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = Non
     cfg = _matmul_cfg.get(key)
     if cfg is None:
         if _tuning_enabled() and _cabi.umma_eligible_tensors(a, b):
-            cfg = _tuned(matmul_kernel, lambda c: _launch_matmul(a, b, c), key, a, _plausible(m, n))
+            keep_tile, keep_split = _plausible(m, n), _plausible_split(m, n, k)
+            cfg = _tuned(matmul_kernel, lambda c: _launch_matmul(a, b, c), key, a,
+                         lambda c: keep_tile(c) and keep_split(c))
         cfg = cfg or default_config(m, n, k)
         _matmul_cfg[key] = cfg
     return _launch_matmul(a, b, cfg, out)
