@@ -178,6 +178,8 @@ def _tuned(kernel, launcher, shape_key: tuple, a: torch.Tensor, filter_fn):
     cfg = tuning_cache.load(kernel.kernel.__name__, key)
     if cfg is None:
         cfg = kernel.tune(launcher, filter_fn=filter_fn)
+        # tuning has synchronised anyway: make sure no probed configuration gave up a device wait
+        _cabi.check_status(a.device)
         tuning_cache.save(kernel.kernel.__name__, key, cfg)
     return cfg
 
