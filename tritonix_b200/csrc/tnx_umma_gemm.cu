@@ -370,6 +370,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       // A K-major B (stored N x K) is laid out like A: rows of 128 B, one slab per 64 K elements.
       const uint64_t b_desc_hi =
           p.b_kmajor ? ptx::make_smem_desc(0, 0, 1024) : ptx::make_smem_desc(0, TILE_K * kAtomBytes, 1024);
+      // Address steps along K in 16-byte units.  A K-major operand advances 32 B per 16 elements
+      // inside a 64-element slab and one slab (rows x 128 B) per 64; an MN-major operand advances
+      // 16 rows of 128 B per 16 elements, i.e. 2048 B, and 8192 B per 64.
+      const uint32_t a_step16 = (p.a_mmajor ? 2048u : 32u) >> 4;
+      const uint32_t a_slab16 = (p.a_mmajor ? 8192u : static_cast<uint32_t>(a_atom_bytes)) >> 4;
+      const uint32_t b_step16 = (p.b_kmajor ? 32u : 2048u) >> 4;
+      const uint32_t b_slab16 = (p.b_kmajor ? static_cast<uint32_t>(LOAD_N * kAtomBytes) : 8192u) >> 4;
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
@@ -397,15 +404,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (u == cluster_id) TNX_TRACE(128 + (kb - kb0));
           const uint32_t a_src = smem_a + stage * a_stage_bytes;
           const uint32_t b_src = smem_b + stage * b_stage_bytes;
+          const uint32_t a16 = a_src >> 4, b16 = b_src >> 4;  // descriptor addresses count 16 B
 #pragma unroll
           for (int k16 = 0; k16 < TILE_K / 16; ++k16) {
-            const uint32_t a_addr = p.a_mmajor ? a_src + k16 * (16 * kAtomBytes)
-                                               : a_src + (k16 >> 2) * a_atom_bytes + (k16 & 3) * 32;
-            const uint32_t b_addr = p.b_kmajor
-                                        ? b_src + (k16 >> 2) * (LOAD_N * kAtomBytes) + (k16 & 3) * 32
-                                        : b_src + k16 * (16 * kAtomBytes);
-            ptx::umma_f16<CTA_GROUP>(d_tmem, a_desc_hi | ((a_addr >> 4) & 0x3fffu),
-                                     b_desc_hi | ((b_addr >> 4) & 0x3fffu), idesc, accumulate);
+            // K step = (k16 / 4) slabs of 64 elements + (k16 % 4) steps of 16 inside a slab
+            const uint32_t a_off = a16 + (k16 >> 2) * a_slab16 + (k16 & 3) * a_step16;
+            const uint32_t b_off = b16 + (k16 >> 2) * b_slab16 + (k16 & 3) * b_step16;
+            // (in a cluster launch the shared-window address carries the CTA rank above bit 18)
+            ptx::umma_f16<CTA_GROUP>(d_tmem, a_desc_hi | (a_off & 0x3fffu), b_desc_hi | (b_off & 0x3fffu),
+                                     idesc, accumulate);
             accumulate = 1;
           }
           // Frees this ring slot (in both CTAs of a pair) once the MMAs above have read it.
