@@ -201,6 +201,56 @@ int tnx_read_status(int32_t* status_word, int32_t* code_out, void* stream);
  */
 int tnx_selftest_bounded_wait(int32_t* status_word, uint32_t limit_ms, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * 2-D convolution forward as an implicit GEMM (GEMM_M = batch*h_out*w_out, GEMM_N = c_out,
+ * GEMM_K = c_in*filter_h*filter_w).  Replaces a launch of conv2d_forward_kernel[grid](...) as
+ * made by conv2d_forward (tritonix/ops/conv2d/forward.py:8-165 and :202-319): same operands
+ * (input N x C x H x W, weight C_OUT x C x R x S, optional bias of C_OUT values, all of one
+ * dtype), same geometry arguments, fp32 accumulation, output cast to the operand type.
+ * ------------------------------------------------------------------------------------------- */
+#define TNX_LAYOUT_NCHW 0 /* contiguous N x C x H x W (what the reference requires)             */
+#define TNX_LAYOUT_NHWC 1 /* contiguous N x H x W x C (torch.channels_last): no repacking pass */
+
+typedef struct tnx_conv2d_problem {
+  int32_t batch, c_in, h_in, w_in; /* input                                                       */
+  int32_t c_out, filter_h, filter_w;
+  int32_t stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
+  int32_t dtype;         /* TNX_F16 / TNX_BF16 / TNX_F32                                          */
+  int32_t has_bias;      /* 0 or 1                                                                */
+  int32_t input_layout;  /* TNX_LAYOUT_*                                                          */
+  int32_t output_layout; /* TNX_LAYOUT_*                                                          */
+  int32_t reserved0;
+} tnx_conv2d_problem;
+
+typedef struct tnx_conv2d_resources {
+  int32_t kernel;          /* TNX_KERNEL_TCGEN05 (fp16/bf16) or TNX_KERNEL_STRIDED (fp32)        */
+  int32_t h_out, w_out;
+  int32_t tile_w, tile_h;  /* output pixels per 128-row tile: tile_w x tile_h (tcgen05 only)    */
+  int32_t smem_bytes, tmem_columns, grid;
+  int64_t workspace_bytes; /* repacked input, weights and output; 0 for the fp32 kernel         */
+} tnx_conv2d_resources;
+
+/* Output geometry, kernel family, resources and the workspace the caller must provide.
+ * `config` may be NULL; only tile_n, tile_k, stages, cta_group, group_m and max_ctas are used. */
+int tnx_conv2d_query(const tnx_conv2d_problem* problem, const tnx_config* config,
+                     tnx_conv2d_resources* out);
+
+/*
+ * Enqueues output = conv2d(input, weight) + bias on `stream`.  Never allocates.
+ *   fp16/bf16: the input is repacked to N x H x W x C (skipped for TNX_LAYOUT_NHWC with c_in a
+ *   multiple of 8), the weights to C_OUT x (R*S) x C zero-padded to 64 channels, both into
+ *   `workspace`; a tcgen05 kernel then multiplies 128-pixel rectangles of the output by the
+ *   weights, one TMA box load per filter tap and 64-channel block (padding comes from TMA's
+ *   out-of-range zero fill); the result is written N x H x W x C and repacked if NCHW is wanted.
+ *   fp32: a CUDA-core kernel reads and writes the tensors in place (no workspace).
+ * `bias` may be NULL when has_bias == 0.  `workspace` needs workspace_bytes from the query and
+ * 256-byte alignment; its content before and after the call is meaningless.
+ */
+int tnx_conv2d_forward(const tnx_conv2d_problem* problem, const tnx_config* config,
+                       const void* input, const void* weight, const void* bias, void* output,
+                       void* workspace, size_t workspace_bytes, int32_t* status_word,
+                       void* stream);
+
 #ifdef __cplusplus
 }
 #endif

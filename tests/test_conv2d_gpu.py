@@ -1,0 +1,175 @@
+"""GPU parity of the convolution forward (tnx_conv2d_forward through the C ABI) against the
+CPU oracle and against outputs of the reference's own kernel."""
+import pytest
+import torch
+
+from oracle import conv2d as OC
+from tests import conv_cases
+from tritonix_b200 import _cabi
+from tritonix_b200.ops.conv2d import conv2d_forward, conv2d_forward_kernel
+
+pytestmark = pytest.mark.gpu
+TOL = {torch.float16: 2e-3, torch.bfloat16: 8e-3, torch.float32: 1e-5}
+DEV = "cuda"
+
+
+def run_conv(x, w, b, stride, padding, dilation, cfg=None, channels_last=False):
+    """One launch through the C ABI into a NaN-filled output."""
+    xd, wd = x.to(DEV), w.to(DEV)
+    bd = b.to(DEV) if b is not None else None
+    if channels_last:
+        xd = xd.contiguous(memory_format=torch.channels_last)
+    n, c, h, wi = x.shape
+    c_out, _, r, s = w.shape
+    h_out, w_out = OC.conv_output_size(h, wi, r, s, stride, padding, dilation)
+    out = torch.full((n, c_out, h_out, w_out), float("nan"), device=DEV, dtype=x.dtype)
+    if channels_last:
+        out = out.contiguous(memory_format=torch.channels_last)
+    res = conv2d_forward_kernel[(1,)](out, xd, wd, bd, n, c, h, wi, c_out, h_out, w_out, r, s,
+                                      stride[0], stride[1], padding[0], padding[1], dilation[0],
+                                      dilation[1], n * h_out * w_out, c_out, c * r * s,
+                                      **(cfg or {}))
+    _cabi.check_status(out.device)
+    return out.cpu().contiguous(), res
+
+
+def check(out, ref, dtype, scale=1.0):
+    assert out.shape == ref.shape and out.dtype == ref.dtype
+    assert not torch.isnan(out.float()).any(), "output has unwritten / NaN elements"
+    err = OC.rel_err(out, ref)
+    assert err <= TOL[dtype] * scale, f"max|err|/max|ref| = {err:.3e}"
+
+
+def seeded(xshape, wshape, dtype, bias=True, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    n, c, h, w = xshape
+    c_out, r, s = wshape
+    x = torch.randn(n, c, h, w, generator=g).to(dtype)
+    wt = (torch.randn(c_out, c, r, s, generator=g) * (c * r * s) ** -0.5).to(dtype)
+    b = torch.randn(c_out, generator=g).to(dtype) if bias else None
+    return x, wt, b
+
+
+@pytest.fixture(scope="module")
+def conv_golden():
+    return conv_cases.golden()
+
+
+@pytest.mark.parametrize("name", conv_cases.case_ids())
+def test_matches_reference_kernel_output(conv_golden, name):
+    x, w, b, stride, padding, dilation, ref, dtype = conv_cases.load_case(conv_golden, name)
+    out, res = run_conv(x, w, b, stride, padding, dilation)
+    assert res.kernel == (_cabi.KERNEL_STRIDED if dtype == "float32" else _cabi.KERNEL_TCGEN05)
+    check(out, ref, x.dtype)
+    check(out, OC.conv2d_oracle(x, w, b, stride, padding, dilation), x.dtype)
+
+
+GEOMS = [
+    # xshape, (c_out, r, s), stride, padding, dilation
+    ((1, 64, 56, 56), (64, 3, 3), (1, 1), (1, 1), (1, 1)),     # ResNet 3x3
+    ((2, 64, 56, 56), (128, 3, 3), (2, 2), (1, 1), (1, 1)),    # strided 3x3
+    ((2, 256, 14, 14), (512, 1, 1), (1, 1), (0, 0), (1, 1)),   # 1x1, 4 channel blocks
+    ((1, 3, 64, 64), (32, 7, 7), (2, 2), (3, 3), (1, 1)),      # stem: 3 channels, 7x7 / 2
+    ((1, 32, 20, 24), (48, 3, 3), (1, 1), (2, 2), (2, 2)),     # dilated
+    ((3, 96, 7, 7), (160, 3, 3), (1, 1), (1, 1), (1, 1)),      # small image, 49 pixels
+    ((1, 40, 17, 19), (72, 3, 5), (2, 1), (0, 2), (1, 1)),     # ragged everything
+    ((1, 128, 28, 28), (200, 3, 3), (1, 1), (1, 1), (1, 1)),   # c_out not a tile multiple
+    ((2, 16, 9, 9), (8, 3, 3), (3, 3), (0, 0), (1, 1)),        # stride 3, tiny c_out
+    ((1, 8, 5, 300), (16, 1, 3), (1, 1), (0, 1), (1, 1)),      # wide rows
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("geom", GEOMS)
+def test_geometries_against_oracle(geom, dtype):
+    xshape, wshape, stride, padding, dilation = geom
+    x, w, b = seeded(xshape, wshape, dtype, bias=True, seed=xshape[1])
+    out, res = run_conv(x, w, b, stride, padding, dilation)
+    assert res.kernel == _cabi.KERNEL_TCGEN05
+    check(out, OC.conv2d_oracle(x, w, b, stride, padding, dilation), dtype)
+
+
+@pytest.mark.parametrize("cfg", [
+    dict(BLOCK_SIZE_M=128, BLOCK_SIZE_N=64, BLOCK_SIZE_K=64),
+    dict(BLOCK_SIZE_M=128, BLOCK_SIZE_N=128, BLOCK_SIZE_K=128),
+    dict(BLOCK_SIZE_M=128, BLOCK_SIZE_N=256, BLOCK_SIZE_K=64, num_stages=3),
+    dict(BLOCK_SIZE_M=256, BLOCK_SIZE_N=128, BLOCK_SIZE_K=64),
+    dict(BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=128, GROUP_SIZE_M=4),
+    dict(tile_n=128, tile_k=64, cta_group=2, stages=2),
+])
+def test_configurations(cfg):
+    x, w, b = seeded((2, 192, 30, 30), (320, 3, 3), torch.bfloat16, seed=11)
+    out, _ = run_conv(x, w, b, (1, 1), (1, 1), (1, 1), cfg)
+    check(out, OC.conv2d_oracle(x, w, b, (1, 1), (1, 1), (1, 1)), torch.bfloat16)
+
+
+@pytest.mark.parametrize("channels", [(64, 64), (24, 40), (30, 64), (64, 20)])
+def test_channels_last_in_and_out(channels):
+    """torch.channels_last tensors: used in place when the channel counts are multiples of 8,
+    through the padding passes otherwise; same numbers either way."""
+    c_in, c_out = channels
+    x, w, b = seeded((2, c_in, 18, 22), (c_out, 3, 3), torch.float16, seed=5)
+    ref = OC.conv2d_oracle(x, w, b, (1, 1), (1, 1), (1, 1))
+    out_cl, _ = run_conv(x, w, b, (1, 1), (1, 1), (1, 1), channels_last=True)
+    out, _ = run_conv(x, w, b, (1, 1), (1, 1), (1, 1))
+    check(out_cl, ref, torch.float16)
+    assert torch.equal(out_cl, out)
+
+
+@pytest.mark.parametrize("geom", GEOMS[:5])
+def test_fp32_kernel(geom):
+    xshape, wshape, stride, padding, dilation = geom
+    x, w, b = seeded(xshape, wshape, torch.float32, seed=3)
+    out, res = run_conv(x, w, b, stride, padding, dilation)
+    assert res.kernel == _cabi.KERNEL_STRIDED and res.workspace_bytes == 0
+    check(out, OC.conv2d_oracle(x, w, b, stride, padding, dilation), torch.float32)
+    out_cl, _ = run_conv(x, w, b, stride, padding, dilation, channels_last=True)
+    check(out_cl, OC.conv2d_oracle(x, w, b, stride, padding, dilation), torch.float32)
+
+
+def test_public_entry_tunes_and_repeats():
+    x, w, b = seeded((2, 64, 28, 28), (96, 3, 3), torch.bfloat16, seed=9)
+    xd, wd, bd = x.to(DEV), w.to(DEV), b.to(DEV)
+    first = conv2d_forward(xd, wd, bd, stride=1, padding=1)
+    second = conv2d_forward(xd, wd, bd, stride=(1, 1), padding=(1, 1))
+    _cabi.check_status(first.device)
+    assert torch.equal(first, second)
+    check(first.cpu(), OC.conv2d_oracle(x, w, b, (1, 1), (1, 1), (1, 1)), torch.bfloat16)
+    fixed = conv2d_forward(xd, wd, bd, padding=(1, 1),
+                           config=dict(BLOCK_SIZE_M=128, BLOCK_SIZE_N=128, BLOCK_SIZE_K=64))
+    check(fixed.cpu(), OC.conv2d_oracle(x, w, b, (1, 1), (1, 1), (1, 1)), torch.bfloat16)
+    cl = conv2d_forward(xd.contiguous(memory_format=torch.channels_last), wd, bd, padding=1)
+    assert cl.is_contiguous(memory_format=torch.channels_last)
+    check(cl.cpu().contiguous(), OC.conv2d_oracle(x, w, b, (1, 1), (1, 1), (1, 1)), torch.bfloat16)
+
+
+def test_linearity_at_full_size():
+    """conv(x1 + x2) = conv(x1) + conv(x2) for inputs whose sums are exact in bf16, at a size the
+    CPU oracle would take too long on (ResNet-50 layer, batch 32)."""
+    g = torch.Generator().manual_seed(1)
+    x1 = torch.randint(-4, 5, (32, 128, 28, 28), generator=g).to(torch.bfloat16).to(DEV)
+    x2 = torch.randint(-4, 5, (32, 128, 28, 28), generator=g).to(torch.bfloat16).to(DEV)
+    w = torch.randint(-2, 3, (128, 128, 3, 3), generator=g).to(torch.bfloat16).to(DEV)
+    y1 = conv2d_forward(x1, w, None, padding=1, config=dict(BLOCK_SIZE_M=256, BLOCK_SIZE_N=128))
+    y2 = conv2d_forward(x2, w, None, padding=1, config=dict(BLOCK_SIZE_M=256, BLOCK_SIZE_N=128))
+    y12 = conv2d_forward(x1 + x2, w, None, padding=1,
+                         config=dict(BLOCK_SIZE_M=128, BLOCK_SIZE_N=128))
+    _cabi.check_status(y1.device)
+    # small integers: every product and partial sum is exact in fp32, the results in bf16 are
+    # exact whenever they stay below 256 in magnitude; compare in fp32 with the bf16 tolerance
+    err = OC.rel_err(y12.float().cpu(), (y1.float() + y2.float()).cpu())
+    assert err <= 8e-3
+
+
+def test_errors():
+    x = torch.zeros(1, 8, 4, 4, device=DEV, dtype=torch.float16)
+    w = torch.zeros(8, 8, 7, 7, device=DEV, dtype=torch.float16)
+    with pytest.raises(ValueError):
+        conv2d_forward(x, w)  # filter larger than the input
+    with pytest.raises(ValueError):
+        conv2d_forward(x, torch.zeros(8, 4, 3, 3, device=DEV, dtype=torch.float16))
+    with pytest.raises(RuntimeError):
+        conv2d_forward(x.cpu(), w.cpu())
+    with pytest.raises(ValueError):
+        conv2d_forward(x, torch.zeros(8, 8, 3, 3, device=DEV, dtype=torch.float16),
+                       config=dict(BLOCK_SIZE_M=64))

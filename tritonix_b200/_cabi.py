@@ -69,8 +69,24 @@ class Resources(ctypes.Structure):
                 ("workspace_bytes", ctypes.c_int64)]
 
 
+class ConvProblem(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int32) for n in (
+        "batch", "c_in", "h_in", "w_in", "c_out", "filter_h", "filter_w", "stride_h", "stride_w",
+        "pad_h", "pad_w", "dil_h", "dil_w", "dtype", "has_bias", "input_layout", "output_layout",
+        "reserved0")]
+
+
+class ConvResources(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int32) for n in (
+        "kernel", "h_out", "w_out", "tile_w", "tile_h", "smem_bytes", "tmem_columns", "grid")] + \
+        [("workspace_bytes", ctypes.c_int64)]
+
+
+LAYOUT_NCHW, LAYOUT_NHWC = 0, 1
+
 EXPORTS = ("tnx_version", "tnx_last_error", "tnx_sm_count", "tnx_gemm_query", "tnx_gemm",
-           "tnx_glu", "tnx_read_status", "tnx_gemm_splitk_static", "tnx_selftest_bounded_wait")
+           "tnx_glu", "tnx_read_status", "tnx_gemm_splitk_static", "tnx_selftest_bounded_wait",
+           "tnx_conv2d_query", "tnx_conv2d_forward")
 STATIC_SCRATCH_BYTES = 16 * 1024 * 1024 + 65536
 
 
@@ -107,6 +123,14 @@ def _load() -> ctypes.CDLL:
     lib.tnx_read_status.restype = ctypes.c_int
     lib.tnx_read_status.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32),
                                     ctypes.c_void_p]
+    lib.tnx_conv2d_query.restype = ctypes.c_int
+    lib.tnx_conv2d_query.argtypes = [ctypes.POINTER(ConvProblem), ctypes.POINTER(Config),
+                                     ctypes.POINTER(ConvResources)]
+    lib.tnx_conv2d_forward.restype = ctypes.c_int
+    lib.tnx_conv2d_forward.argtypes = [ctypes.POINTER(ConvProblem), ctypes.POINTER(Config),
+                                       ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                       ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t,
+                                       ctypes.c_void_p, ctypes.c_void_p]
     return lib
 
 
@@ -350,3 +374,55 @@ def launch_splitk_static(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor,
                                         b.data_ptr(), c.data_ptr(),
                                         status_word(a.device).data_ptr(), stream)
     raise_for(rc)
+
+
+# ---------------------------------------------------------------------------------------------
+# Convolution
+# ---------------------------------------------------------------------------------------------
+_conv_workspaces: dict = {}
+
+
+def conv_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Scratch for the repacked input, weights and output of a convolution, one per (device,
+    stream), grown on demand.  Not cleared: the library writes every byte it reads."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    key = (idx, torch.cuda.current_stream(idx).cuda_stream)
+    with _scratch_lock:
+        w = _conv_workspaces.get(key)
+        if w is None or w.numel() < nbytes:
+            w = torch.empty(max(nbytes, 256), dtype=torch.uint8, device=torch.device("cuda", idx))
+            _conv_workspaces[key] = w
+        return w
+
+
+def make_conv_problem(batch, c_in, h_in, w_in, c_out, filter_h, filter_w, stride, padding, dilation,
+                      dtype, has_bias, input_layout=LAYOUT_NCHW,
+                      output_layout=LAYOUT_NCHW) -> ConvProblem:
+    if dtype not in DTYPES:
+        raise ValueError(f"unsupported dtype {dtype}")
+    return ConvProblem(batch, c_in, h_in, w_in, c_out, filter_h, filter_w, stride[0], stride[1],
+                       padding[0], padding[1], dilation[0], dilation[1], DTYPES[dtype],
+                       1 if has_bias else 0, input_layout, output_layout, 0)
+
+
+def conv_query(problem: ConvProblem, config: Config | None = None) -> ConvResources:
+    res = ConvResources()
+    raise_for(lib.tnx_conv2d_query(ctypes.byref(problem),
+                                   ctypes.byref(config) if config is not None else None,
+                                   ctypes.byref(res)))
+    return res
+
+
+def conv_launch(problem: ConvProblem, config: Config | None, res: ConvResources,
+                x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None,
+                y: torch.Tensor) -> None:
+    """Enqueues tnx_conv2d_forward on torch's current stream of x's device."""
+    require_cuda(x, w, y)
+    ws = conv_workspace(x.device, res.workspace_bytes) if res.workspace_bytes else None
+    with torch.cuda.device(x.device):
+        raise_for(lib.tnx_conv2d_forward(
+            ctypes.byref(problem), ctypes.byref(config) if config is not None else None,
+            x.data_ptr(), w.data_ptr(), bias.data_ptr() if bias is not None else None,
+            y.data_ptr(), ws.data_ptr() if ws is not None else None,
+            ws.numel() if ws is not None else 0, status_word(x.device).data_ptr(),
+            torch.cuda.current_stream(x.device).cuda_stream))

@@ -27,6 +27,28 @@ int umma_launch(const tnx_problem& p, const tnx_config& cfg, const tnx_resources
 // 16-byte aligned row pitches).  Pointer alignment is checked at launch.
 bool umma_eligible(const tnx_problem& p, const char** why);
 
+// Convolution on the tcgen05 kernel.  The plan fixes the pixel rectangle a CTA tile covers and
+// the layout of the caller's workspace (offsets in bytes, each a multiple of 256).
+struct ConvPlan {
+  int h_out, w_out;
+  int tile_w, tile_h;        // output pixels per CTA tile
+  int tiles_w, tiles_h;      // CTA tiles per image
+  int row_tiles;             // batch * tiles_h * tiles_w
+  int c_pitch;               // channels per pixel of the N x H x W x C input the kernel reads
+  int cblocks;               // 64-channel blocks per filter tap
+  int k_packed;              // taps * cblocks * 64: row length of the packed weights
+  int c_out_pitch;           // channels per pixel of the N x H x W x C output the kernel writes
+  bool repack_input, repack_output;
+  int64_t off_input, off_weight, off_output, workspace_bytes;
+};
+int umma_conv_query(const tnx_conv2d_problem& p, tnx_config* cfg, tnx_conv2d_resources* out,
+                    ConvPlan* plan);
+// x: N x H x W x c_pitch, w: c_out x k_packed, y: N x h_out x w_out x c_out_pitch.
+int umma_conv_launch(const tnx_conv2d_problem& p, const tnx_config& cfg,
+                     const tnx_conv2d_resources& res, const ConvPlan& plan, const void* x,
+                     const void* w, const void* bias, void* y, int32_t* status_word,
+                     cudaStream_t stream);
+
 int strided_query(const tnx_problem& p, tnx_config* cfg, tnx_resources* out);
 int strided_launch(const tnx_problem& p, const void* a, const void* b, void* c,
                    cudaStream_t stream);

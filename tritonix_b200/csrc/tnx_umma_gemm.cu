@@ -77,6 +77,17 @@ struct UmmaParams {
   int* counters;        // split-K: one arrival counter per 128-row output tile
   int* status;
   unsigned long long timeout_ns;
+  // Convolution (implicit GEMM): the rows of a CTA's tile are a cv_tw x cv_th rectangle of output
+  // pixels of one image, A comes from an N x H x W x C tensor through a 4-D tensor map, and K
+  // runs over (filter tap, 64-channel block).
+  int conv;
+  int cv_tw, cv_th;            // output pixels per CTA tile (cv_tw * cv_th = a_rows)
+  int cv_tiles_w, cv_tiles_h;  // CTA tiles per image
+  int cv_row_tiles;            // batch * cv_tiles_h * cv_tiles_w
+  int cv_cblocks;              // 64-channel blocks per filter tap
+  int cv_taps, cv_fw;          // filter_h * filter_w, filter_w
+  int cv_sh, cv_sw, cv_ph, cv_pw, cv_dh, cv_dw;
+  const void* bias;            // one value per output column, of the operand type, or nullptr
 #ifdef TNX_DEV_TRACE
   unsigned long long* trace;  // development builds only: 256 timestamp slots per CTA
 #endif
@@ -148,6 +159,12 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     __half2 v = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
   }
+}
+
+template <bool BF16>
+__device__ __forceinline__ float unpack1(uint16_t bits) {
+  if (BF16) return __uint_as_float(static_cast<uint32_t>(bits) << 16);
+  return __half2float(__ushort_as_half(bits));
 }
 
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c,
@@ -282,6 +299,18 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int col0 = tn * TILE_N + static_cast<int>(cta_rank) * LOAD_N;
         const int kb0 = slice * p.kb_per_slice;
         const int kb1 = min(kb0 + p.kb_per_slice, p.num_kb);
+        // Convolution: image and first input column / row (before the tap's offset) of this
+        // CTA's pixel rectangle.  A pair's missing last tile gets image = batch: all zero fill.
+        int cv_n = 0, cv_x = 0, cv_y = 0;
+        if (p.conv) {
+          const int row_tile = tm * CTA_GROUP + static_cast<int>(cta_rank);
+          const int per_image = p.cv_tiles_h * p.cv_tiles_w;
+          cv_n = row_tile / per_image;
+          const int rem = row_tile - cv_n * per_image;
+          const int hb = rem / p.cv_tiles_w;
+          cv_y = hb * p.cv_th * p.cv_sh - p.cv_ph;
+          cv_x = (rem - hb * p.cv_tiles_w) * p.cv_tw * p.cv_sw - p.cv_pw;
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           const uint32_t empty_bar = ptx::smem_u32(&ctrl->empty[stage]);
           if (!ptx::mbar_wait(empty_bar, phase ^ 1u, abort_flag, p.timeout_ns)) {
@@ -294,7 +323,20 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const int k0 = kb * TILE_K;
           if (CTA_GROUP == 1) {
             ptx::mbar_arrive_expect_tx(full_bar, stage_tx);
-            if (p.a_mmajor) {  // two 64-row atoms of tile_k x 128 B, like a row-major B
+            if (p.conv) {  // one box of pixels x 64 channels per (tap, channel block)
+#pragma unroll
+              for (int ka = 0; ka < TILE_K / kAtomElems; ++ka) {
+                const int g = kb * (TILE_K / kAtomElems) + ka;
+                const int tap = g / p.cv_cblocks;
+                const int fr = tap / p.cv_fw;
+                // past the last tap: a channel coordinate beyond C reads zeros
+                const int ch = tap < p.cv_taps ? (g - tap * p.cv_cblocks) * kAtomElems
+                                               : p.cv_cblocks * kAtomElems;
+                ptx::tma_load_4d(a_dst + ka * a_atom_bytes, &tmap_a, ch,
+                                 cv_x + (tap - fr * p.cv_fw) * p.cv_dw, cv_y + fr * p.cv_dh, cv_n,
+                                 full_bar);
+              }
+            } else if (p.a_mmajor) {  // two 64-row atoms of tile_k x 128 B, like a row-major B
 #pragma unroll
               for (int ma = 0; ma < kRowsPerCta / kAtomElems; ++ma)
                 ptx::tma_load_2d(a_dst + ma * (TILE_K * kAtomBytes), &tmap_a, row0 + ma * kAtomElems,
@@ -320,7 +362,19 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             // Both CTAs' loads complete on the leader's barrier; the leader announces the bytes.
             const uint32_t leader_bar = ptx::mapa(full_bar, 0);
             if (leader) ptx::mbar_arrive_expect_tx(full_bar, stage_tx);
-            if (p.a_mmajor) {
+            if (p.conv) {
+#pragma unroll
+              for (int ka = 0; ka < TILE_K / kAtomElems; ++ka) {
+                const int g = kb * (TILE_K / kAtomElems) + ka;
+                const int tap = g / p.cv_cblocks;
+                const int fr = tap / p.cv_fw;
+                const int ch = tap < p.cv_taps ? (g - tap * p.cv_cblocks) * kAtomElems
+                                               : p.cv_cblocks * kAtomElems;
+                ptx::tma_load_4d_pair(a_dst + ka * a_atom_bytes, &tmap_a, ch,
+                                      cv_x + (tap - fr * p.cv_fw) * p.cv_dw, cv_y + fr * p.cv_dh,
+                                      cv_n, leader_bar);
+              }
+            } else if (p.a_mmajor) {
 #pragma unroll
               for (int ma = 0; ma < kRowsPerCta / kAtomElems; ++ma)
                 ptx::tma_load_2d_pair(a_dst + ma * (TILE_K * kAtomBytes), &tmap_a,
@@ -714,6 +768,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                            o[piece * 4 + 2], o[piece * 4 + 3]);
             }
           } else {
+            if (p.bias != nullptr) {
+              const uint16_t* bias16 = reinterpret_cast<const uint16_t*>(p.bias);
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const int bc = acc_col0 + col + j;
+                if (bc < p.n) v[j] += unpack1<BF16>(__ldg(bias16 + bc));
+              }
+            }
             uint32_t o[16];
 #pragma unroll
             for (int j = 0; j < 16; ++j) o[j] = pack2<BF16>(v[2 * j], v[2 * j + 1]);
@@ -728,7 +790,16 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         ptx::fence_proxy_async_smem();
         ptx::named_barrier_sync(kEpiBarrier, kEpiThreads);
         if (epi_tid == 0) {
-          ptx::tma_store_2d(&tmap_c, out_col, row0, buf);
+          if (!p.conv) {
+            ptx::tma_store_2d(&tmap_c, out_col, row0, buf);
+          } else if (row_tile < p.cv_row_tiles) {  // rows are a rectangle of pixels of one image
+            const int per_image = p.cv_tiles_h * p.cv_tiles_w;
+            const int img = row_tile / per_image;
+            const int rem = row_tile - img * per_image;
+            const int hb = rem / p.cv_tiles_w;
+            ptx::tma_store_4d(&tmap_c, out_col, (rem - hb * p.cv_tiles_w) * p.cv_tw, hb * p.cv_th,
+                              img, buf);
+          }
           ptx::tma_store_commit();
         }
         ++stores;
@@ -1168,7 +1239,7 @@ int umma_launch(const tnx_problem& p, const tnx_config& cfg, const tnx_resources
   rc = make_tmap(&tc, c, p.dtype, n_out, p.m, p.stride_cm, kAtomElems, kRowsPerCta, false);
   if (rc != TNX_OK) return rc;
 
-  UmmaParams kp;
+  UmmaParams kp = {};
   kp.m = p.m;
   kp.n = p.n;
   kp.k = p.k;
@@ -1240,6 +1311,275 @@ int umma_launch(const tnx_problem& p, const tnx_config& cfg, const tnx_resources
   e = cudaLaunchKernelEx(&lc, fn, ta, tb, tc, kp);
   if (e != cudaSuccess) {
     set_error("kernel launch failed: %s", cudaGetErrorString(e));
+    (void)cudaGetLastError();
+    return TNX_ERR_CUDA;
+  }
+  return TNX_OK;
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// Convolution forward on the same kernel
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+inline int64_t align256(int64_t v) { return (v + 255) / 256 * 256; }
+
+// 4-D tensor map over an N x H x W x C tensor of 16-bit elements (dimension order C, W, H, N).
+// A box is 64 channels x box_w x box_h pixels of one image, walked with the given pixel steps.
+int make_tmap_nhwc(CUtensorMap* out, const void* ptr, int dtype, int64_t c, int64_t w, int64_t h,
+                   int64_t n, int box_w, int box_h, int step_w, int step_h, bool is_operand) {
+  EncodeTiledFn encode = get_encode_fn();
+  if (encode == nullptr) {
+    set_error("cuTensorMapEncodeTiled is not available from the CUDA driver");
+    return TNX_ERR_CUDA;
+  }
+  const cuuint64_t dims[4] = {static_cast<cuuint64_t>(c), static_cast<cuuint64_t>(w),
+                              static_cast<cuuint64_t>(h), static_cast<cuuint64_t>(n)};
+  const cuuint64_t strides[3] = {static_cast<cuuint64_t>(c) * 2, static_cast<cuuint64_t>(w * c) * 2,
+                                 static_cast<cuuint64_t>(h * w * c) * 2};
+  const cuuint32_t box[4] = {static_cast<cuuint32_t>(kAtomElems), static_cast<cuuint32_t>(box_w),
+                             static_cast<cuuint32_t>(box_h), 1};
+  const cuuint32_t estr[4] = {1, static_cast<cuuint32_t>(step_w), static_cast<cuuint32_t>(step_h), 1};
+  const CUtensorMapDataType dt =
+      dtype == TNX_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = encode(out, dt, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                      is_operand ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled (4-D) failed with CUresult %d (ptr %p, %lld x %lld x %lld x %lld, "
+              "box %d x %d, steps %d x %d)",
+              static_cast<int>(r), ptr, static_cast<long long>(n), static_cast<long long>(h),
+              static_cast<long long>(w), static_cast<long long>(c), box_w, box_h, step_w, step_h);
+    return TNX_ERR_CUDA;
+  }
+  return TNX_OK;
+}
+
+// Picks the rectangle of output pixels one CTA tile covers: at most 128 pixels, a multiple of 8
+// (whole swizzle groups), fewest tiles per image first, then most pixels per tile, then widest.
+void pick_pixel_tile(int h_out, int w_out, int step_h, int step_w, int* tile_w, int* tile_h) {
+  long long best_tiles = -1;
+  int best_w = 8, best_h = 1, best_px = 0;
+  for (int tw = 1; tw <= kRowsPerCta; ++tw) {
+    if ((tw - 1) * step_w + 1 > 256) break;
+    if (tw > w_out && tw > 8) break;
+    for (int th = 1; tw * th <= kRowsPerCta; ++th) {
+      if ((th - 1) * step_h + 1 > 256) break;
+      const int px = tw * th;
+      if (px % 8 != 0) continue;
+      const long long tiles = static_cast<long long>(cdiv(w_out, tw)) * cdiv(h_out, th);
+      const bool better = best_tiles < 0 || tiles < best_tiles ||
+                          (tiles == best_tiles && (px < best_px || (px == best_px && tw > best_w)));
+      if (better) {
+        best_tiles = tiles;
+        best_w = tw;
+        best_h = th;
+        best_px = px;
+      }
+    }
+  }
+  *tile_w = best_w;
+  *tile_h = best_h;
+}
+
+}  // namespace
+
+int umma_conv_query(const tnx_conv2d_problem& p, tnx_config* cfg, tnx_conv2d_resources* out,
+                    ConvPlan* plan) {
+  const int h_out = (p.h_in + 2 * p.pad_h - p.dil_h * (p.filter_h - 1) - 1) / p.stride_h + 1;
+  const int w_out = (p.w_in + 2 * p.pad_w - p.dil_w * (p.filter_w - 1) - 1) / p.stride_w + 1;
+  plan->h_out = h_out;
+  plan->w_out = w_out;
+  if (p.stride_h > 8 || p.stride_w > 8) {  // a tensor map walks a box in steps of at most 8
+    set_error("convolution strides above 8 are not supported for fp16/bf16 (got %d x %d)",
+              p.stride_h, p.stride_w);
+    return TNX_ERR_INVALID;
+  }
+  pick_pixel_tile(h_out, w_out, p.stride_h, p.stride_w, &plan->tile_w, &plan->tile_h);
+  plan->tiles_w = cdiv(w_out, plan->tile_w);
+  plan->tiles_h = cdiv(h_out, plan->tile_h);
+  const long long row_tiles = static_cast<long long>(p.batch) * plan->tiles_w * plan->tiles_h;
+  if (row_tiles > 0x7fffffLL) {
+    set_error("convolution output has too many pixel tiles (%lld)", row_tiles);
+    return TNX_ERR_INVALID;
+  }
+  plan->row_tiles = static_cast<int>(row_tiles);
+  const int a_rows = plan->tile_w * plan->tile_h;
+
+  // Workspace: the kernel reads N x H x W x C with C a multiple of 8 and writes the same way.
+  plan->repack_input = !(p.input_layout == TNX_LAYOUT_NHWC && p.c_in % 8 == 0);
+  plan->repack_output = !(p.output_layout == TNX_LAYOUT_NHWC && p.c_out % 8 == 0);
+  plan->c_pitch = (p.c_in + 7) / 8 * 8;
+  plan->c_out_pitch = (p.c_out + 7) / 8 * 8;
+  plan->cblocks = cdiv(p.c_in, kAtomElems);
+  plan->k_packed = p.filter_h * p.filter_w * plan->cblocks * kAtomElems;
+  int64_t off = 0;
+  plan->off_input = off;
+  if (plan->repack_input)
+    off += align256(static_cast<int64_t>(p.batch) * p.h_in * p.w_in * plan->c_pitch * 2);
+  plan->off_weight = off;
+  off += align256(static_cast<int64_t>(p.c_out) * plan->k_packed * 2);
+  plan->off_output = off;
+  if (plan->repack_output)
+    off += align256(static_cast<int64_t>(p.batch) * h_out * w_out * plan->c_out_pitch * 2);
+  plan->workspace_bytes = off;
+
+  if (cfg->cta_group == 0) {
+    if (cfg->tile_m != 0)
+      cfg->cta_group = cfg->tile_m == 2 * kRowsPerCta ? 2 : 1;  // 256 rows = a CTA pair
+    else
+      cfg->cta_group = (row_tiles >= 2 && p.c_out > 64) ? 2 : 1;
+  }
+  if (cfg->tile_m != 0 && cfg->tile_m != kRowsPerCta * cfg->cta_group) {
+    set_error("tile_m=%d is not built: cta_group=%d tiles have %d rows", cfg->tile_m,
+              cfg->cta_group, kRowsPerCta * cfg->cta_group);
+    return TNX_ERR_NOT_BUILT;
+  }
+  if (cfg->cta_group != 1 && cfg->cta_group != 2) {
+    set_error("cta_group must be 1 or 2, got %d", cfg->cta_group);
+    return TNX_ERR_INVALID;
+  }
+  if (cfg->tile_n == 0) cfg->tile_n = p.c_out > 128 ? 256 : (p.c_out > 64 || cfg->cta_group == 2 ? 128 : 64);
+  if (cfg->tile_k == 0) cfg->tile_k = (plan->k_packed % 128 == 0) ? 128 : 64;
+  if (cfg->group_m == 0) cfg->group_m = 8;
+  cfg->acc_stages = 2;
+  cfg->split_k = 1;
+  cfg->tile_m = kRowsPerCta * cfg->cta_group;
+  if (cfg->tile_k != 64 && cfg->tile_k != 128) {
+    set_error("tile_k=%d is not built (64 or 128)", cfg->tile_k);
+    return TNX_ERR_NOT_BUILT;
+  }
+  if (pick_kernel(cfg->tile_n, cfg->tile_k, cfg->cta_group, false, p.dtype) == nullptr) {
+    set_error("no kernel built for tile_n=%d cta_group=%d", cfg->tile_n, cfg->cta_group);
+    return TNX_ERR_NOT_BUILT;
+  }
+  const int load_n = cfg->tile_n / cfg->cta_group;
+  const int stage_bytes = (a_rows + load_n) * cfg->tile_k * 2;
+  const int fixed = 2 * kStagingBytes + kCtrlBytes + kAlignSlack;
+  if (cfg->stages == 0) {
+    int s = (kMaxDynamicSmem - fixed) / stage_bytes;
+    cfg->stages = s > 8 ? 8 : s;
+  }
+  if (cfg->stages < 2 || cfg->stages > kMaxStages) {
+    set_error("stages must be in [2, %d], got %d", kMaxStages, cfg->stages);
+    return TNX_ERR_INVALID;
+  }
+  const long long smem = static_cast<long long>(cfg->stages) * stage_bytes + fixed;
+  const int tiles_m = cdiv(plan->row_tiles, cfg->cta_group);
+  const int tiles_n = cdiv(p.c_out, cfg->tile_n);
+  int max_clusters = device_sm_count() / cfg->cta_group;
+  if (cfg->max_ctas > 0 && cfg->max_ctas / cfg->cta_group < max_clusters)
+    max_clusters = cfg->max_ctas / cfg->cta_group;
+  if (max_clusters < 1) max_clusters = 1;
+  const long long units = static_cast<long long>(tiles_m) * tiles_n;
+  out->kernel = TNX_KERNEL_TCGEN05;
+  out->h_out = h_out;
+  out->w_out = w_out;
+  out->tile_w = plan->tile_w;
+  out->tile_h = plan->tile_h;
+  out->smem_bytes = static_cast<int32_t>(smem > 0x7fffffff ? 0x7fffffff : smem);
+  out->tmem_columns = 2 * cfg->tile_n < 32 ? 32 : 2 * cfg->tile_n;
+  out->grid = static_cast<int32_t>((units < max_clusters ? units : max_clusters) * cfg->cta_group);
+  out->workspace_bytes = plan->workspace_bytes;
+  if (smem > kMaxDynamicSmem) {
+    set_error("shared memory budget exceeded: %lld B needed (%d stages x %d B + %d B), %d B per SM",
+              smem, cfg->stages, stage_bytes, fixed, kMaxDynamicSmem);
+    return TNX_ERR_RESOURCES;
+  }
+  if (tiles_n > 0xffff) {
+    set_error("too many output-channel tiles (%d)", tiles_n);
+    return TNX_ERR_INVALID;
+  }
+  return TNX_OK;
+}
+
+int umma_conv_launch(const tnx_conv2d_problem& p, const tnx_config& cfg,
+                     const tnx_conv2d_resources& res, const ConvPlan& plan, const void* x,
+                     const void* w, const void* bias, void* y, int32_t* status_word,
+                     cudaStream_t stream) {
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) |
+       reinterpret_cast<uintptr_t>(y)) & 15u) {
+    set_error("tcgen05 convolution needs 16-byte aligned input, weight and output buffers");
+    return TNX_ERR_INVALID;
+  }
+  KernelFn fn = pick_kernel(cfg.tile_n, cfg.tile_k, cfg.cta_group, false, p.dtype);
+  if (fn == nullptr) return TNX_ERR_NOT_BUILT;
+  const int a_rows = plan.tile_w * plan.tile_h;
+  CUtensorMap ta, tb, tc;
+  int rc = make_tmap_nhwc(&ta, x, p.dtype, plan.c_pitch, p.w_in, p.h_in, p.batch,
+                          (plan.tile_w - 1) * p.stride_w + 1, (plan.tile_h - 1) * p.stride_h + 1,
+                          p.stride_w, p.stride_h, true);
+  if (rc != TNX_OK) return rc;
+  rc = make_tmap(&tb, w, p.dtype, plan.k_packed, p.c_out, plan.k_packed, kAtomElems,
+                 cfg.tile_n / cfg.cta_group, true);
+  if (rc != TNX_OK) return rc;
+  rc = make_tmap_nhwc(&tc, y, p.dtype, plan.c_out_pitch, plan.w_out, plan.h_out, p.batch,
+                      plan.tile_w, plan.tile_h, 1, 1, false);
+  if (rc != TNX_OK) return rc;
+
+  UmmaParams kp = {};
+  kp.m = plan.row_tiles * kRowsPerCta;
+  kp.n = p.c_out;
+  kp.k = plan.k_packed;
+  kp.n_out = plan.c_out_pitch;
+  kp.tiles_m = cdiv(plan.row_tiles, cfg.cta_group);
+  kp.tiles_n = cdiv(p.c_out, cfg.tile_n);
+  kp.num_kb = cdiv(plan.k_packed, cfg.tile_k);
+  kp.split_k = 1;
+  kp.cluster_split = 0;
+  kp.kb_per_slice = kp.num_kb;
+  kp.tile_k = cfg.tile_k;
+  kp.a_rows = a_rows;
+  kp.staging_bytes = 2 * kStagingBytes;
+  kp.b_kmajor = 1;
+  kp.a_mmajor = 0;
+  kp.stages = cfg.stages;
+  kp.acc_stages = 2;
+  kp.group_m = cfg.group_m;
+  kp.tile_order = TNX_ORDER_GROUPED;
+  kp.epilogue = TNX_EPI_NONE;
+  kp.status = status_word;
+  kp.timeout_ns = wait_limit_ns();
+  kp.conv = 1;
+  kp.cv_tw = plan.tile_w;
+  kp.cv_th = plan.tile_h;
+  kp.cv_tiles_w = plan.tiles_w;
+  kp.cv_tiles_h = plan.tiles_h;
+  kp.cv_row_tiles = plan.row_tiles;
+  kp.cv_cblocks = plan.cblocks;
+  kp.cv_taps = p.filter_h * p.filter_w;
+  kp.cv_fw = p.filter_w;
+  kp.cv_sh = p.stride_h;
+  kp.cv_sw = p.stride_w;
+  kp.cv_ph = p.pad_h;
+  kp.cv_pw = p.pad_w;
+  kp.cv_dh = p.dil_h;
+  kp.cv_dw = p.dil_w;
+  kp.bias = p.has_bias ? bias : nullptr;
+
+  cudaError_t e = allow_full_smem(fn);
+  if (e != cudaSuccess) {
+    set_error("cudaFuncSetAttribute(%d B dynamic smem): %s", kMaxDynamicSmem, cudaGetErrorString(e));
+    (void)cudaGetLastError();
+    return TNX_ERR_CUDA;
+  }
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = dim3(res.grid, 1, 1);
+  lc.blockDim = dim3(kThreads, 1, 1);
+  lc.dynamicSmemBytes = res.smem_bytes;
+  lc.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cfg.cta_group;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  lc.attrs = attr;
+  lc.numAttrs = 1;
+  e = cudaLaunchKernelEx(&lc, fn, ta, tb, tc, kp);
+  if (e != cudaSuccess) {
+    set_error("convolution kernel launch failed: %s", cudaGetErrorString(e));
     (void)cudaGetLastError();
     return TNX_ERR_CUDA;
   }

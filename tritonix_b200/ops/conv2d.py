@@ -1,0 +1,209 @@
+"""2-D convolution forward: ``conv2d_forward`` and the ``conv2d_forward_kernel`` handle — the
+surface of tritonix/ops/conv2d/forward.py:8-319 (forward only; the reference's backward and
+channel-sparse kernels are not part of this package).
+
+The convolution is an implicit GEMM, GEMM_M = N*H_OUT*W_OUT, GEMM_N = C_OUT, GEMM_K = C_IN*R*S.
+For fp16/bf16 it runs on the tcgen05 kernel: a tile's 128 rows are a rectangle of output pixels,
+each filter tap is one TMA box load from the N x H x W x C input (zero fill outside the image is
+the padding), the weights are a K-major operand.  NCHW tensors are repacked on the way in and
+out; ``torch.channels_last`` tensors with channel counts that are multiples of 8 are used in
+place.  fp32 runs on a CUDA-core kernel.
+
+Search space, under the reference's key names (forward.py:8-18):
+  BLOCK_SIZE_M  output pixels per tile: 128 = one SM per tile, 256 = a CTA pair
+  BLOCK_SIZE_N  output channels per tile (64 / 128 / 256)
+  BLOCK_SIZE_K  K elements per pipeline stage (64 / 128)
+  GROUP_SIZE_M  band height of the grouped tile order
+  num_stages    depth of the TMA -> shared-memory ring
+"""
+from __future__ import annotations
+
+import torch
+
+from tritonix_b200 import _cabi
+from tritonix_b200.autotune import Choice, PowerOfTwo, Range, tunable
+
+_CONV_ALIASES = {"BLOCK_SIZE_M": "tile_m", "BLOCK_SIZE_N": "tile_n", "BLOCK_SIZE_K": "tile_k",
+                 "GROUP_SIZE_M": "group_m"}
+_CONV_IGNORED = {"OUT_DTYPE", "USE_TF32"}
+
+
+def _pair(v):
+    if isinstance(v, int):
+        return (v, v)
+    v = tuple(int(x) for x in v)
+    if len(v) != 2:
+        raise ValueError(f"expected an int or a pair, got {v}")
+    return v
+
+
+def _conv_config(cfg: dict | None) -> _cabi.Config | None:
+    """Reference config keys (forward.py:302-305) -> the C ABI's."""
+    if not cfg:
+        return None
+    out = {}
+    for key, value in cfg.items():
+        if key in _CONV_IGNORED:
+            continue
+        out[_CONV_ALIASES.get(key, key)] = value
+    return _cabi.make_config(out)
+
+
+def _layout(t: torch.Tensor) -> int:
+    if t.is_contiguous():
+        return _cabi.LAYOUT_NCHW
+    if t.is_contiguous(memory_format=torch.channels_last):
+        return _cabi.LAYOUT_NHWC
+    raise ValueError("tensor must be contiguous NCHW or torch.channels_last")
+
+
+class _Conv2dKernel:
+    """Handle with the reference's launch syntax (forward.py:277-290):
+
+        conv2d_forward_kernel[grid](out, input, weight, bias, N, C_IN, H_IN, W_IN, C_OUT, H_OUT,
+                                    W_OUT, R, S, str_h, str_w, pad_h, pad_w, dil_h, dil_w,
+                                    GEMM_M, GEMM_N, GEMM_K, BLOCK_SIZE_M=..., ...)
+
+    ``grid`` is accepted and ignored (the kernel is persistent and sizes its own grid)."""
+
+    __name__ = "conv2d_forward_kernel"
+
+    def __getitem__(self, grid):
+        def launch(*args, **kwargs):
+            return self.run(*args, **kwargs)
+        return launch
+
+    def run(self, out, input, weight, bias, batch, c_in, h_in, w_in, c_out, h_out, w_out,
+            filter_h, filter_w, stride_h, stride_w, pad_h, pad_w, dil_h, dil_w, gemm_m=None,
+            gemm_n=None, gemm_k=None, **cfg):
+        _cabi.require_cuda(out, input, weight)
+        if not (input.dtype == weight.dtype == out.dtype):
+            raise ValueError(f"dtype mismatch {input.dtype}/{weight.dtype}/{out.dtype}")
+        if bias is not None and (bias.dtype != input.dtype or not bias.is_cuda):
+            raise ValueError("bias must be a CUDA tensor of the input's dtype")
+        problem = _cabi.make_conv_problem(
+            batch, c_in, h_in, w_in, c_out, filter_h, filter_w, (stride_h, stride_w),
+            (pad_h, pad_w), (dil_h, dil_w), input.dtype, bias is not None, _layout(input),
+            _layout(out))
+        config = _conv_config(cfg)
+        res = _cabi.conv_query(problem, config)
+        if (res.h_out, res.w_out) != (h_out, w_out):
+            raise ValueError(f"H_OUT x W_OUT = {h_out} x {w_out} does not match the geometry "
+                             f"({res.h_out} x {res.w_out})")
+        _cabi.conv_launch(problem, config, res, input, weight, bias, out)
+        return res
+
+    def __repr__(self):
+        return "<tritonix_b200 CUDA kernel conv2d_forward_kernel>"
+
+
+conv2d_forward_kernel = tunable(
+    keys=["GEMM_M", "GEMM_N", "GEMM_K"],
+    space={
+        "BLOCK_SIZE_M": PowerOfTwo(128, 256),
+        "BLOCK_SIZE_N": PowerOfTwo(64, 256),
+        "BLOCK_SIZE_K": PowerOfTwo(64, 128),
+        "GROUP_SIZE_M": Choice([4, 8, 16]),
+        "num_stages": Range(2, 8),
+    },
+    memory_params={"BLOCK_SIZE_M", "BLOCK_SIZE_N", "BLOCK_SIZE_K", "num_stages"},
+    memory_rank={"BLOCK_SIZE_M": lambda rows: -rows},
+)(_Conv2dKernel())
+
+# Tuned configuration per problem, as the reference keeps one (forward.py:171, 244-300).
+_CONV_FWD_CONFIG_CACHE: dict[tuple, dict] = {}
+# (BLOCK_SIZE_M, BLOCK_SIZE_N, BLOCK_SIZE_K, GROUP_SIZE_M) tried on the first call for a problem.
+_CANDIDATE_CONFIGS = [
+    (256, 256, 64, 8),
+    (256, 256, 128, 8),
+    (256, 128, 64, 8),
+    (128, 256, 64, 8),
+    (128, 128, 64, 8),
+    (128, 128, 128, 8),
+    (128, 64, 64, 8),
+]
+
+
+def _time_kernel(fn, iters=6, warmup=2):
+    for _ in range(warmup):
+        fn()
+    start = torch.cuda.Event(enable_timing=True)
+    end = torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(iters):
+        fn()
+    end.record()
+    end.synchronize()
+    return start.elapsed_time(end) / iters
+
+
+def conv2d_forward(input: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
+                   stride=(1, 1), padding=(0, 0), dilation=(1, 1), use_tf32: bool = True,
+                   config: dict | None = None) -> torch.Tensor:
+    """Forward of ``torch.nn.functional.conv2d`` (groups = 1), the reference's
+    ``conv2d_forward`` (forward.py:202-319): input N x C x H x W, weight C_OUT x C x R x S,
+    optional bias, fp32 accumulation, output N x C_OUT x H_OUT x W_OUT of the input's dtype.
+
+    A ``torch.channels_last`` input gives a ``channels_last`` output and skips the repacking
+    passes.  ``config`` fixes the kernel configuration (reference keys ``BLOCK_SIZE_M/N/K``,
+    ``GROUP_SIZE_M``, or this package's ``tile_n``/``tile_k``/``stages``/``cta_group``);
+    without it the first call for a problem times a handful of candidates and remembers the
+    best.  ``use_tf32`` is accepted for compatibility: fp32 inputs are computed in full fp32.
+    """
+    _cabi.require_cuda(input, weight)
+    if input.dim() != 4 or weight.dim() != 4:
+        raise ValueError("input must be N x C x H x W and weight C_OUT x C x R x S")
+    if input.shape[1] != weight.shape[1]:
+        raise ValueError(f"channel mismatch: input has {input.shape[1]}, weight {weight.shape[1]}")
+    if weight.dtype != input.dtype or (bias is not None and bias.dtype != input.dtype):
+        raise ValueError("input, weight and bias must share one dtype")
+    stride, padding, dilation = _pair(stride), _pair(padding), _pair(dilation)
+    channels_last = (not input.is_contiguous()
+                     and input.is_contiguous(memory_format=torch.channels_last))
+    if not channels_last and not input.is_contiguous():
+        raise ValueError("input must be contiguous NCHW or torch.channels_last")
+    weight = weight.contiguous()
+    if bias is not None:
+        bias = bias.contiguous()
+    n, c_in, h_in, w_in = input.shape
+    c_out, _, r, s = weight.shape
+    h_out = (h_in + 2 * padding[0] - dilation[0] * (r - 1) - 1) // stride[0] + 1
+    w_out = (w_in + 2 * padding[1] - dilation[1] * (s - 1) - 1) // stride[1] + 1
+    if h_out < 1 or w_out < 1:
+        raise ValueError("the dilated filter is larger than the padded input")
+    out = torch.empty((n, c_out, h_out, w_out), device=input.device, dtype=input.dtype,
+                      memory_format=torch.channels_last if channels_last
+                      else torch.contiguous_format)
+    args = (out, input, weight, bias, n, c_in, h_in, w_in, c_out, h_out, w_out, r, s,
+            stride[0], stride[1], padding[0], padding[1], dilation[0], dilation[1],
+            n * h_out * w_out, c_out, c_in * r * s)
+    launch = conv2d_forward_kernel.run
+
+    if config is None and input.dtype != torch.float32:
+        key = (n, c_in, h_in, w_in, c_out, r, s, stride, padding, dilation, input.dtype,
+               channels_last)
+        config = _CONV_FWD_CONFIG_CACHE.get(key)
+        if config is None:
+            best_time, best = float("inf"), None
+            for bm, bn, bk, g in _CANDIDATE_CONFIGS:
+                cand = dict(BLOCK_SIZE_M=bm, BLOCK_SIZE_N=bn, BLOCK_SIZE_K=bk, GROUP_SIZE_M=g)
+                if bn > 64 and bn // 2 >= c_out:
+                    continue  # half of the tile's columns would be padding
+                try:
+                    t = _time_kernel(lambda: launch(*args, **cand))
+                except (ValueError, _cabi.OutOfResources):
+                    continue
+                if t < best_time:
+                    best_time, best = t, cand
+            config = best or {}
+            _cabi.check_status(input.device)
+            _CONV_FWD_CONFIG_CACHE[key] = config
+    launch(*args, **(config or {}))
+    return out
+
+
+def torch_conv2d_forward(input, weight, bias=None, stride=(1, 1), padding=(0, 0),
+                         dilation=(1, 1)):
+    """PyTorch's own convolution, for comparisons only (forward.py:322-331); never used as a
+    fallback by this package."""
+    return torch.nn.functional.conv2d(input, weight, bias, stride, padding, dilation)
