@@ -211,6 +211,9 @@ int tnx_selftest_bounded_wait(int32_t* status_word, uint32_t limit_ms, void* str
 #define TNX_LAYOUT_NCHW 0 /* contiguous N x C x H x W (what the reference requires)             */
 #define TNX_LAYOUT_NHWC 1 /* contiguous N x H x W x C (torch.channels_last): no repacking pass */
 
+#define TNX_WEIGHT_KCRS 0   /* C_OUT x C x R x S, contiguous (what the reference passes)        */
+#define TNX_WEIGHT_PACKED 1 /* the buffer tnx_conv2d_pack_weights() filled (fp16/bf16 only)     */
+
 typedef struct tnx_conv2d_problem {
   int32_t batch, c_in, h_in, w_in; /* input                                                       */
   int32_t c_out, filter_h, filter_w;
@@ -219,13 +222,14 @@ typedef struct tnx_conv2d_problem {
   int32_t has_bias;      /* 0 or 1                                                                */
   int32_t input_layout;  /* TNX_LAYOUT_*                                                          */
   int32_t output_layout; /* TNX_LAYOUT_*                                                          */
-  int32_t reserved0;
+  int32_t weight_layout; /* TNX_WEIGHT_*                                                          */
 } tnx_conv2d_problem;
 
 typedef struct tnx_conv2d_resources {
   int32_t kernel;          /* TNX_KERNEL_TCGEN05 (fp16/bf16) or TNX_KERNEL_STRIDED (fp32)        */
   int32_t h_out, w_out;
-  int32_t tile_w, tile_h;  /* output pixels per 128-row tile: tile_w x tile_h (tcgen05 only)    */
+  int32_t tile_w, tile_h;  /* tcgen05 only: the rows of a tile are tile_w x tile_h output pixels;
+                              128 x 1 = 128 consecutive pixels in (image, row, column) order    */
   int32_t smem_bytes, tmem_columns, grid;
   int64_t workspace_bytes; /* repacked input, weights and output; 0 for the fp32 kernel         */
 } tnx_conv2d_resources;
@@ -236,12 +240,26 @@ int tnx_conv2d_query(const tnx_conv2d_problem* problem, const tnx_config* config
                      tnx_conv2d_resources* out);
 
 /*
+ * Weights that do not change between calls (inference) can be repacked once instead of on
+ * every call: tnx_conv2d_packed_weight_bytes() gives the size of the packed buffer (0 for
+ * fp32, which has no packed form), tnx_conv2d_pack_weights() fills it from C_OUT x C x R x S
+ * weights on `stream`; pass it as `weight` with problem->weight_layout = TNX_WEIGHT_PACKED.
+ * The packed form depends only on c_in, c_out, filter_h, filter_w and dtype.
+ */
+int64_t tnx_conv2d_packed_weight_bytes(const tnx_conv2d_problem* problem);
+int tnx_conv2d_pack_weights(const tnx_conv2d_problem* problem, const void* weight, void* packed,
+                            void* stream);
+
+/*
  * Enqueues output = conv2d(input, weight) + bias on `stream`.  Never allocates.
  *   fp16/bf16: the input is repacked to N x H x W x C (skipped for TNX_LAYOUT_NHWC with c_in a
  *   multiple of 8), the weights to C_OUT x (R*S) x C zero-padded to 64 channels, both into
- *   `workspace`; a tcgen05 kernel then multiplies 128-pixel rectangles of the output by the
- *   weights, one TMA box load per filter tap and 64-channel block (padding comes from TMA's
- *   out-of-range zero fill); the result is written N x H x W x C and repacked if NCHW is wanted.
+ *   `workspace`; a tcgen05 kernel then multiplies tiles of 128 output pixels by the weights,
+ *   one TMA box load per filter tap and 64-channel block (im2col-mode boxes of 128 consecutive
+ *   pixels; rectangles of pixels fetched with tiled boxes when the padding or the dilated
+ *   filter exceeds what an im2col box can express, or when TNX_CONV_TILED is set in the
+ *   environment); padding comes from TMA's out-of-range zero fill; the result is written
+ *   N x H x W x C and repacked if NCHW is wanted.
  *   fp32: a CUDA-core kernel reads and writes the tensors in place (no workspace).
  * `bias` may be NULL when has_bias == 0.  `workspace` needs workspace_bytes from the query and
  * 256-byte alignment; its content before and after the call is meaningless.

@@ -79,9 +79,19 @@ GEOMS = [
 ]
 
 
+@pytest.fixture(params=["im2col", "tiled"])
+def box_mode(request, monkeypatch):
+    """Both ways of fetching the pixels of a tile: im2col-mode boxes (default) and rectangles."""
+    if request.param == "tiled":
+        monkeypatch.setenv("TNX_CONV_TILED", "1")
+    else:
+        monkeypatch.delenv("TNX_CONV_TILED", raising=False)
+    return request.param
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("geom", GEOMS)
-def test_geometries_against_oracle(geom, dtype):
+def test_geometries_against_oracle(geom, dtype, box_mode):
     xshape, wshape, stride, padding, dilation = geom
     x, w, b = seeded(xshape, wshape, dtype, bias=True, seed=xshape[1])
     out, res = run_conv(x, w, b, stride, padding, dilation)
@@ -97,14 +107,15 @@ def test_geometries_against_oracle(geom, dtype):
     dict(BLOCK_SIZE_M=256, BLOCK_SIZE_N=256, BLOCK_SIZE_K=128, GROUP_SIZE_M=4),
     dict(tile_n=128, tile_k=64, cta_group=2, stages=2),
 ])
-def test_configurations(cfg):
+def test_configurations(cfg, box_mode):
     x, w, b = seeded((2, 192, 30, 30), (320, 3, 3), torch.bfloat16, seed=11)
-    out, _ = run_conv(x, w, b, (1, 1), (1, 1), (1, 1), cfg)
+    out, res = run_conv(x, w, b, (1, 1), (1, 1), (1, 1), cfg)
+    assert (res.tile_w, res.tile_h) == ((128, 1) if box_mode == "im2col" else (30, 4))
     check(out, OC.conv2d_oracle(x, w, b, (1, 1), (1, 1), (1, 1)), torch.bfloat16)
 
 
 @pytest.mark.parametrize("channels", [(64, 64), (24, 40), (30, 64), (64, 20)])
-def test_channels_last_in_and_out(channels):
+def test_channels_last_in_and_out(channels, box_mode):
     """torch.channels_last tensors: used in place when the channel counts are multiples of 8,
     through the padding passes otherwise; same numbers either way."""
     c_in, c_out = channels
@@ -159,6 +170,39 @@ def test_linearity_at_full_size():
     # exact whenever they stay below 256 in magnitude; compare in fp32 with the bf16 tolerance
     err = OC.rel_err(y12.float().cpu(), (y1.float() + y2.float()).cpu())
     assert err <= 8e-3
+
+
+def test_wide_padding_uses_rectangles():
+    """Padding beyond what an im2col box can express (128) falls back to rectangles of pixels."""
+    x, w, b = seeded((1, 16, 6, 6), (16, 3, 3), torch.float16, seed=2)
+    out, res = run_conv(x, w, b, (1, 1), (130, 2), (1, 1))
+    assert (res.tile_w, res.tile_h) != (128, 1)
+    check(out, OC.conv2d_oracle(x, w, b, (1, 1), (130, 2), (1, 1)), torch.float16)
+
+
+def test_packed_weights_match_and_follow_updates():
+    """Weights packed once (tnx_conv2d_pack_weights) give the same bits as weights packed inside
+    the call, and the public entry repacks after an in-place update of the weight tensor."""
+    x, w, b = seeded((2, 48, 16, 16), (40, 3, 3), torch.float16, seed=4)
+    ref, _ = run_conv(x, w, b, (1, 1), (1, 1), (1, 1))
+    xd, wd, bd = x.to(DEV), w.to(DEV), b.to(DEV)
+    problem = _cabi.make_conv_problem(2, 48, 16, 16, 40, 3, 3, (1, 1), (1, 1), (1, 1),
+                                      torch.float16, True)
+    packed = _cabi.conv_pack_weights(problem, wd)
+    out = torch.full((2, 40, 16, 16), float("nan"), device=DEV, dtype=torch.float16)
+    conv2d_forward_kernel[(1,)](out, xd, packed, bd, 2, 48, 16, 16, 40, 16, 16, 3, 3, 1, 1, 1, 1,
+                                1, 1, weights_packed=True)
+    _cabi.check_status(out.device)
+    assert torch.equal(out.cpu(), ref)
+
+    y1 = conv2d_forward(xd, wd, bd, padding=1)
+    y1_again = conv2d_forward(xd, wd, bd, padding=1)       # served from the packed-weight cache
+    assert torch.equal(y1, y1_again)
+    wd.mul_(2.0)                                           # in place: same storage, new version
+    y2 = conv2d_forward(xd, wd, bd, padding=1)
+    _cabi.check_status(y2.device)
+    check(y2.cpu(), OC.conv2d_oracle(x, w * 2.0, b, (1, 1), (1, 1), (1, 1)), torch.float16)
+    assert not torch.equal(y1, y2)
 
 
 def test_errors():

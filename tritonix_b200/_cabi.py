@@ -73,7 +73,7 @@ class ConvProblem(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int32) for n in (
         "batch", "c_in", "h_in", "w_in", "c_out", "filter_h", "filter_w", "stride_h", "stride_w",
         "pad_h", "pad_w", "dil_h", "dil_w", "dtype", "has_bias", "input_layout", "output_layout",
-        "reserved0")]
+        "weight_layout")]
 
 
 class ConvResources(ctypes.Structure):
@@ -83,10 +83,12 @@ class ConvResources(ctypes.Structure):
 
 
 LAYOUT_NCHW, LAYOUT_NHWC = 0, 1
+WEIGHT_KCRS, WEIGHT_PACKED = 0, 1
 
 EXPORTS = ("tnx_version", "tnx_last_error", "tnx_sm_count", "tnx_gemm_query", "tnx_gemm",
            "tnx_glu", "tnx_read_status", "tnx_gemm_splitk_static", "tnx_selftest_bounded_wait",
-           "tnx_conv2d_query", "tnx_conv2d_forward")
+           "tnx_conv2d_query", "tnx_conv2d_forward", "tnx_conv2d_packed_weight_bytes",
+           "tnx_conv2d_pack_weights")
 STATIC_SCRATCH_BYTES = 16 * 1024 * 1024 + 65536
 
 
@@ -126,6 +128,11 @@ def _load() -> ctypes.CDLL:
     lib.tnx_conv2d_query.restype = ctypes.c_int
     lib.tnx_conv2d_query.argtypes = [ctypes.POINTER(ConvProblem), ctypes.POINTER(Config),
                                      ctypes.POINTER(ConvResources)]
+    lib.tnx_conv2d_packed_weight_bytes.restype = ctypes.c_int64
+    lib.tnx_conv2d_packed_weight_bytes.argtypes = [ctypes.POINTER(ConvProblem)]
+    lib.tnx_conv2d_pack_weights.restype = ctypes.c_int
+    lib.tnx_conv2d_pack_weights.argtypes = [ctypes.POINTER(ConvProblem), ctypes.c_void_p,
+                                            ctypes.c_void_p, ctypes.c_void_p]
     lib.tnx_conv2d_forward.restype = ctypes.c_int
     lib.tnx_conv2d_forward.argtypes = [ctypes.POINTER(ConvProblem), ctypes.POINTER(Config),
                                        ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
@@ -397,12 +404,12 @@ def conv_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
 
 def make_conv_problem(batch, c_in, h_in, w_in, c_out, filter_h, filter_w, stride, padding, dilation,
                       dtype, has_bias, input_layout=LAYOUT_NCHW,
-                      output_layout=LAYOUT_NCHW) -> ConvProblem:
+                      output_layout=LAYOUT_NCHW, weight_layout=WEIGHT_KCRS) -> ConvProblem:
     if dtype not in DTYPES:
         raise ValueError(f"unsupported dtype {dtype}")
     return ConvProblem(batch, c_in, h_in, w_in, c_out, filter_h, filter_w, stride[0], stride[1],
                        padding[0], padding[1], dilation[0], dilation[1], DTYPES[dtype],
-                       1 if has_bias else 0, input_layout, output_layout, 0)
+                       1 if has_bias else 0, input_layout, output_layout, weight_layout)
 
 
 def conv_query(problem: ConvProblem, config: Config | None = None) -> ConvResources:
@@ -426,3 +433,18 @@ def conv_launch(problem: ConvProblem, config: Config | None, res: ConvResources,
             y.data_ptr(), ws.data_ptr() if ws is not None else None,
             ws.numel() if ws is not None else 0, status_word(x.device).data_ptr(),
             torch.cuda.current_stream(x.device).cuda_stream))
+
+
+def conv_pack_weights(problem: ConvProblem, weight: torch.Tensor) -> torch.Tensor:
+    """The weights in the layout the tcgen05 kernel reads (tnx_conv2d_pack_weights), as a new
+    uint8 tensor; enqueued on torch's current stream."""
+    require_cuda(weight)
+    nbytes = lib.tnx_conv2d_packed_weight_bytes(ctypes.byref(problem))
+    if nbytes <= 0:
+        raise ValueError("these weights have no packed form (fp32, or an invalid problem)")
+    packed = torch.empty(nbytes, dtype=torch.uint8, device=weight.device)
+    with torch.cuda.device(weight.device):
+        raise_for(lib.tnx_conv2d_pack_weights(ctypes.byref(problem), weight.data_ptr(),
+                                              packed.data_ptr(),
+                                              torch.cuda.current_stream(weight.device).cuda_stream))
+    return packed

@@ -89,16 +89,28 @@ __global__ void unpad_channels16_kernel(const uint16_t* __restrict__ src, uint16
 
 // Weights C_OUT x C x R x S -> C_OUT x (R*S) x (cblocks*64), zero beyond C: the K order of the
 // implicit GEMM (tap-major, channels contiguous) with every tap starting on a 128-byte boundary.
+// One thread writes 8 channels (16 bytes) of one (output channel, tap).
 __global__ void pack_weights16_kernel(const uint16_t* __restrict__ w, uint16_t* __restrict__ out,
                                       int c_out, int c, int taps, int c_padded) {
-  const long long total = static_cast<long long>(c_out) * taps * c_padded;
+  const int groups = c_padded / 8;
+  const long long total = static_cast<long long>(c_out) * taps * groups;
   for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int ch = static_cast<int>(i % c_padded);
-    const long long rest = i / c_padded;
+    const int grp = static_cast<int>(i % groups);
+    const long long rest = i / groups;
     const int tap = static_cast<int>(rest % taps);
     const long long co = rest / taps;
-    out[i] = ch < c ? w[(co * c + ch) * taps + tap] : static_cast<uint16_t>(0);
+    const uint16_t* src = w + (co * c + grp * 8) * taps + tap;
+    uint16_t v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      v[j] = grp * 8 + j < c ? src[static_cast<long long>(j) * taps] : static_cast<uint16_t>(0);
+    uint4 q;
+    q.x = v[0] | (static_cast<uint32_t>(v[1]) << 16);
+    q.y = v[2] | (static_cast<uint32_t>(v[3]) << 16);
+    q.z = v[4] | (static_cast<uint32_t>(v[5]) << 16);
+    q.w = v[6] | (static_cast<uint32_t>(v[7]) << 16);
+    *reinterpret_cast<uint4*>(out + i * 8) = q;
   }
 }
 
@@ -211,6 +223,11 @@ int validate_conv(const tnx_conv2d_problem* p) {
     set_error("the dilated filter is larger than the padded input");
     return TNX_ERR_INVALID;
   }
+  if (p->weight_layout != TNX_WEIGHT_KCRS &&
+      !(p->weight_layout == TNX_WEIGHT_PACKED && p->dtype != TNX_F32)) {
+    set_error("weight_layout must be TNX_WEIGHT_KCRS, or TNX_WEIGHT_PACKED for fp16/bf16");
+    return TNX_ERR_INVALID;
+  }
   if (p->has_bias != 0 && p->has_bias != 1) {
     set_error("has_bias must be 0 or 1");
     return TNX_ERR_INVALID;
@@ -250,6 +267,38 @@ extern "C" int tnx_conv2d_query(const tnx_conv2d_problem* problem, const tnx_con
   tnx_config cfg = config ? *config : tnx_config{};
   tnx::ConvPlan plan;
   return tnx::umma_conv_query(*problem, &cfg, out, &plan);
+}
+
+extern "C" int64_t tnx_conv2d_packed_weight_bytes(const tnx_conv2d_problem* problem) {
+  if (tnx::validate_conv(problem) != TNX_OK || problem->dtype == TNX_F32) return 0;
+  const int64_t c_padded = (problem->c_in + 63) / 64 * 64;
+  return static_cast<int64_t>(problem->c_out) * problem->filter_h * problem->filter_w * c_padded * 2;
+}
+
+extern "C" int tnx_conv2d_pack_weights(const tnx_conv2d_problem* problem, const void* weight,
+                                       void* packed, void* stream_ptr) {
+  int rc = tnx::validate_conv(problem);
+  if (rc != TNX_OK) return rc;
+  if (problem->dtype == TNX_F32) {
+    tnx::set_error("fp32 weights have no packed form");
+    return TNX_ERR_INVALID;
+  }
+  if (weight == nullptr || packed == nullptr || (reinterpret_cast<uintptr_t>(packed) & 15u)) {
+    tnx::set_error("weight and packed must not be NULL and packed must be 16-byte aligned");
+    return TNX_ERR_INVALID;
+  }
+  const int taps = problem->filter_h * problem->filter_w;
+  const int c_padded = (problem->c_in + 63) / 64 * 64;
+  const long long groups = static_cast<long long>(problem->c_out) * taps * (c_padded / 8);
+  tnx::pack_weights16_kernel<<<tnx::grid_for(groups), 256, 0, static_cast<cudaStream_t>(stream_ptr)>>>(
+      static_cast<const uint16_t*>(weight), static_cast<uint16_t*>(packed), problem->c_out,
+      problem->c_in, taps, c_padded);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    tnx::set_error("weight packing kernel launch failed: %s", cudaGetErrorString(e));
+    return TNX_ERR_CUDA;
+  }
+  return TNX_OK;
 }
 
 extern "C" int tnx_conv2d_forward(const tnx_conv2d_problem* problem, const tnx_config* config,
@@ -336,13 +385,15 @@ extern "C" int tnx_conv2d_forward(const tnx_conv2d_problem* problem, const tnx_c
     x = dst;
   }
   // 2. weights as C_OUT x (R*S) x padded channels
-  {
+  const void* w_packed = weight;
+  if (p.weight_layout != TNX_WEIGHT_PACKED) {
     const int taps = p.filter_h * p.filter_w;
     const int c_padded = plan.k_packed / taps;
-    tnx::pack_weights16_kernel<<<tnx::grid_for(static_cast<long long>(p.c_out) * plan.k_packed), 256, 0,
-                                 stream>>>(static_cast<const uint16_t*>(weight),
-                                           reinterpret_cast<uint16_t*>(ws + plan.off_weight), p.c_out,
-                                           p.c_in, taps, c_padded);
+    tnx::pack_weights16_kernel<<<tnx::grid_for(static_cast<long long>(p.c_out) * plan.k_packed / 8),
+                                 256, 0, stream>>>(static_cast<const uint16_t*>(weight),
+                                                   reinterpret_cast<uint16_t*>(ws + plan.off_weight),
+                                                   p.c_out, p.c_in, taps, c_padded);
+    w_packed = ws + plan.off_weight;
   }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
@@ -351,7 +402,7 @@ extern "C" int tnx_conv2d_forward(const tnx_conv2d_problem* problem, const tnx_c
   }
   // 3. the implicit GEMM
   void* y = plan.repack_output ? static_cast<void*>(ws + plan.off_output) : output;
-  rc = tnx::umma_conv_launch(p, cfg, res, plan, x, ws + plan.off_weight, bias, y, status_word, stream);
+  rc = tnx::umma_conv_launch(p, cfg, res, plan, x, w_packed, bias, y, status_word, stream);
   if (rc != TNX_OK) return rc;
   // 4. output in the layout the caller wants
   if (plan.repack_output) {

@@ -39,6 +39,7 @@ struct ConvPlan {
   int k_packed;              // taps * cblocks * 64: row length of the packed weights
   int c_out_pitch;           // channels per pixel of the N x H x W x C output the kernel writes
   bool repack_input, repack_output;
+  bool im2col;               // tiles are 128 consecutive pixels fetched with im2col-mode boxes
   int64_t off_input, off_weight, off_output, workspace_bytes;
 };
 int umma_conv_query(const tnx_conv2d_problem& p, tnx_config* cfg, tnx_conv2d_resources* out,

@@ -157,6 +157,32 @@ __device__ __forceinline__ void tma_load_4d_pair(uint32_t dst_smem, const void* 
         "r"(leader_bar)
       : "memory");
 }
+// 4-D im2col loads: 128 consecutive output pixels (in image, row, column order) x 64 channels.
+// (c1, c2, c3) is the first pixel's filter-window origin in input coordinates, (off_w, off_h)
+// the filter tap's offset inside the window; pixels outside the image read zero.
+__device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst_smem, const void* tmap, int32_t c0,
+                                                   int32_t c1, int32_t c2, int32_t c3,
+                                                   uint16_t off_w, uint16_t off_h, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3, %4, %5}], [%6], {%7, %8};"
+      :
+      : "r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(c2), "r"(c3),
+        "r"(bar), "h"(off_w), "h"(off_h)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_im2col_4d_pair(uint32_t dst_smem, const void* tmap,
+                                                        int32_t c0, int32_t c1, int32_t c2,
+                                                        int32_t c3, uint16_t off_w, uint16_t off_h,
+                                                        uint32_t leader_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.im2col.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3, %4, %5}], [%6], {%7, %8};"
+      :
+      : "r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(c2), "r"(c3),
+        "r"(leader_bar), "h"(off_w), "h"(off_h)
+      : "memory");
+}
 __device__ __forceinline__ void tma_store_4d(const void* tmap, int32_t c0, int32_t c1, int32_t c2,
                                              int32_t c3, uint32_t src_smem) {
   asm volatile(

@@ -80,7 +80,8 @@ struct UmmaParams {
   // Convolution (implicit GEMM): the rows of a CTA's tile are a cv_tw x cv_th rectangle of output
   // pixels of one image, A comes from an N x H x W x C tensor through a 4-D tensor map, and K
   // runs over (filter tap, 64-channel block).
-  int conv;
+  int conv;                    // 1: rectangles of pixels (tiled boxes); 2: 128 consecutive pixels (im2col boxes)
+  int cv_wout, cv_hout;        // output image size
   int cv_tw, cv_th;            // output pixels per CTA tile (cv_tw * cv_th = a_rows)
   int cv_tiles_w, cv_tiles_h;  // CTA tiles per image
   int cv_row_tiles;            // batch * cv_tiles_h * cv_tiles_w
@@ -302,7 +303,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         // Convolution: image and first input column / row (before the tap's offset) of this
         // CTA's pixel rectangle.  A pair's missing last tile gets image = batch: all zero fill.
         int cv_n = 0, cv_x = 0, cv_y = 0;
-        if (p.conv) {
+        if (p.conv == 1) {
           const int row_tile = tm * CTA_GROUP + static_cast<int>(cta_rank);
           const int per_image = p.cv_tiles_h * p.cv_tiles_w;
           cv_n = row_tile / per_image;
@@ -310,6 +311,18 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const int hb = rem / p.cv_tiles_w;
           cv_y = hb * p.cv_th * p.cv_sh - p.cv_ph;
           cv_x = (rem - hb * p.cv_tiles_w) * p.cv_tw * p.cv_sw - p.cv_pw;
+        } else if (p.conv == 2) {
+          // first of the tile's 128 consecutive pixels (a pair's missing last tile re-reads
+          // tile 0; its rows are never stored)
+          int row_tile = tm * CTA_GROUP + static_cast<int>(cta_rank);
+          if (row_tile >= p.cv_row_tiles) row_tile = 0;
+          const int first = row_tile * kRowsPerCta;
+          const int per_image = p.cv_hout * p.cv_wout;
+          cv_n = first / per_image;
+          const int rem = first - cv_n * per_image;
+          const int ho = rem / p.cv_wout;
+          cv_y = ho * p.cv_sh - p.cv_ph;
+          cv_x = (rem - ho * p.cv_wout) * p.cv_sw - p.cv_pw;
         }
         for (int kb = kb0; kb < kb1; ++kb) {
           const uint32_t empty_bar = ptx::smem_u32(&ctrl->empty[stage]);
@@ -327,14 +340,21 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
               for (int ka = 0; ka < TILE_K / kAtomElems; ++ka) {
                 const int g = kb * (TILE_K / kAtomElems) + ka;
-                const int tap = g / p.cv_cblocks;
+                int tap = g / p.cv_cblocks;
+                const bool past = tap >= p.cv_taps;  // second half of an odd last K block
+                if (past) tap = 0;
                 const int fr = tap / p.cv_fw;
-                // past the last tap: a channel coordinate beyond C reads zeros
-                const int ch = tap < p.cv_taps ? (g - tap * p.cv_cblocks) * kAtomElems
-                                               : p.cv_cblocks * kAtomElems;
-                ptx::tma_load_4d(a_dst + ka * a_atom_bytes, &tmap_a, ch,
-                                 cv_x + (tap - fr * p.cv_fw) * p.cv_dw, cv_y + fr * p.cv_dh, cv_n,
-                                 full_bar);
+                // (past the last tap: a channel coordinate beyond C reads zeros)
+                const int ch = past ? p.cv_cblocks * kAtomElems
+                                    : (g - tap * p.cv_cblocks) * kAtomElems;
+                if (p.conv == 1)
+                  ptx::tma_load_4d(a_dst + ka * a_atom_bytes, &tmap_a, ch,
+                                   cv_x + (tap - fr * p.cv_fw) * p.cv_dw, cv_y + fr * p.cv_dh, cv_n,
+                                   full_bar);
+                else
+                  ptx::tma_load_im2col_4d(a_dst + ka * a_atom_bytes, &tmap_a, ch, cv_x, cv_y, cv_n,
+                                          static_cast<uint16_t>((tap - fr * p.cv_fw) * p.cv_dw),
+                                          static_cast<uint16_t>(fr * p.cv_dh), full_bar);
               }
             } else if (p.a_mmajor) {  // two 64-row atoms of tile_k x 128 B, like a row-major B
 #pragma unroll
@@ -366,13 +386,21 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
               for (int ka = 0; ka < TILE_K / kAtomElems; ++ka) {
                 const int g = kb * (TILE_K / kAtomElems) + ka;
-                const int tap = g / p.cv_cblocks;
+                int tap = g / p.cv_cblocks;
+                const bool past = tap >= p.cv_taps;  // second half of an odd last K block
+                if (past) tap = 0;
                 const int fr = tap / p.cv_fw;
-                const int ch = tap < p.cv_taps ? (g - tap * p.cv_cblocks) * kAtomElems
-                                               : p.cv_cblocks * kAtomElems;
-                ptx::tma_load_4d_pair(a_dst + ka * a_atom_bytes, &tmap_a, ch,
-                                      cv_x + (tap - fr * p.cv_fw) * p.cv_dw, cv_y + fr * p.cv_dh,
-                                      cv_n, leader_bar);
+                const int ch = past ? p.cv_cblocks * kAtomElems
+                                    : (g - tap * p.cv_cblocks) * kAtomElems;
+                if (p.conv == 1)
+                  ptx::tma_load_4d_pair(a_dst + ka * a_atom_bytes, &tmap_a, ch,
+                                        cv_x + (tap - fr * p.cv_fw) * p.cv_dw, cv_y + fr * p.cv_dh,
+                                        cv_n, leader_bar);
+                else
+                  ptx::tma_load_im2col_4d_pair(a_dst + ka * a_atom_bytes, &tmap_a, ch, cv_x, cv_y,
+                                               cv_n,
+                                               static_cast<uint16_t>((tap - fr * p.cv_fw) * p.cv_dw),
+                                               static_cast<uint16_t>(fr * p.cv_dh), leader_bar);
               }
             } else if (p.a_mmajor) {
 #pragma unroll
@@ -790,7 +818,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         ptx::fence_proxy_async_smem();
         ptx::named_barrier_sync(kEpiBarrier, kEpiThreads);
         if (epi_tid == 0) {
-          if (!p.conv) {
+          if (p.conv != 1) {
             ptx::tma_store_2d(&tmap_c, out_col, row0, buf);
           } else if (row_tile < p.cv_row_tiles) {  // rows are a rectangle of pixels of one image
             const int per_image = p.cv_tiles_h * p.cv_tiles_w;
@@ -1357,6 +1385,67 @@ int make_tmap_nhwc(CUtensorMap* out, const void* ptr, int dtype, int64_t c, int6
   return TNX_OK;
 }
 
+using EncodeIm2colFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                    const cuuint64_t*, const cuuint64_t*, const int*, const int*,
+                                    cuuint32_t, cuuint32_t, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                    CUtensorMapFloatOOBfill);
+
+EncodeIm2colFn get_encode_im2col_fn() {
+  static EncodeIm2colFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e =
+        cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &sym, cudaEnableDefault, &qres);
+    if (e == cudaSuccess && qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeIm2colFn>(sym);
+    else
+      (void)cudaGetLastError();
+  });
+  return fn;
+}
+
+// im2col-mode tensor map over an N x H x W x C tensor: a box is 128 consecutive filter-window
+// origins (walking W, then H, then N in steps of the convolution's stride inside the window
+// origins' bounding box) x 64 channels; the load adds the filter tap's offset.
+int make_tmap_im2col(CUtensorMap* out, const void* ptr, const tnx_conv2d_problem& p, int c_pitch) {
+  EncodeIm2colFn encode = get_encode_im2col_fn();
+  if (encode == nullptr) {
+    set_error("cuTensorMapEncodeIm2col is not available from the CUDA driver");
+    return TNX_ERR_CUDA;
+  }
+  const cuuint64_t c = c_pitch, w = p.w_in, h = p.h_in, n = p.batch;
+  const cuuint64_t dims[4] = {c, w, h, n};
+  const cuuint64_t strides[3] = {c * 2, w * c * 2, h * w * c * 2};
+  const int lower[2] = {-p.pad_w, -p.pad_h};
+  const int upper[2] = {p.pad_w - (p.filter_w - 1) * p.dil_w, p.pad_h - (p.filter_h - 1) * p.dil_h};
+  const cuuint32_t estr[4] = {1, static_cast<cuuint32_t>(p.stride_w),
+                              static_cast<cuuint32_t>(p.stride_h), 1};
+  const CUtensorMapDataType dt =
+      p.dtype == TNX_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = encode(out, dt, 4, const_cast<void*>(ptr), dims, strides, lower, upper, kAtomElems,
+                      kRowsPerCta, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeIm2col failed with CUresult %d (ptr %p, %d x %d x %d x %d, corners "
+              "(%d, %d) (%d, %d))",
+              static_cast<int>(r), ptr, p.batch, p.h_in, p.w_in, c_pitch, lower[0], lower[1], upper[0],
+              upper[1]);
+    return TNX_ERR_CUDA;
+  }
+  return TNX_OK;
+}
+
+// im2col-mode boxes keep the window origins' bounding-box corners in 8 bits each.
+bool im2col_usable(const tnx_conv2d_problem& p) {
+  if (getenv("TNX_CONV_TILED") != nullptr) return false;  // read every time: tests flip it
+  const int up_w = p.pad_w - (p.filter_w - 1) * p.dil_w, up_h = p.pad_h - (p.filter_h - 1) * p.dil_h;
+  return p.pad_w <= 128 && p.pad_h <= 128 && up_w >= -128 && up_w <= 127 && up_h >= -128 &&
+         up_h <= 127 && (p.filter_w - 1) * p.dil_w < 65536 && (p.filter_h - 1) * p.dil_h < 65536;
+}
+
 // Picks the rectangle of output pixels one CTA tile covers: at most 128 pixels, a multiple of 8
 // (whole swizzle groups), fewest tiles per image first, then most pixels per tile, then widest.
 void pick_pixel_tile(int h_out, int w_out, int step_h, int step_w, int* tile_w, int* tile_h) {
@@ -1397,10 +1486,19 @@ int umma_conv_query(const tnx_conv2d_problem& p, tnx_config* cfg, tnx_conv2d_res
               p.stride_h, p.stride_w);
     return TNX_ERR_INVALID;
   }
-  pick_pixel_tile(h_out, w_out, p.stride_h, p.stride_w, &plan->tile_w, &plan->tile_h);
-  plan->tiles_w = cdiv(w_out, plan->tile_w);
-  plan->tiles_h = cdiv(h_out, plan->tile_h);
-  const long long row_tiles = static_cast<long long>(p.batch) * plan->tiles_w * plan->tiles_h;
+  plan->im2col = im2col_usable(p);
+  long long row_tiles;
+  if (plan->im2col) {  // a tile = 128 consecutive pixels in (image, row, column) order
+    plan->tile_w = kRowsPerCta;
+    plan->tile_h = 1;
+    plan->tiles_w = plan->tiles_h = 0;
+    row_tiles = (static_cast<long long>(p.batch) * h_out * w_out + kRowsPerCta - 1) / kRowsPerCta;
+  } else {
+    pick_pixel_tile(h_out, w_out, p.stride_h, p.stride_w, &plan->tile_w, &plan->tile_h);
+    plan->tiles_w = cdiv(w_out, plan->tile_w);
+    plan->tiles_h = cdiv(h_out, plan->tile_h);
+    row_tiles = static_cast<long long>(p.batch) * plan->tiles_w * plan->tiles_h;
+  }
   if (row_tiles > 0x7fffffLL) {
     set_error("convolution output has too many pixel tiles (%lld)", row_tiles);
     return TNX_ERR_INVALID;
@@ -1508,19 +1606,24 @@ int umma_conv_launch(const tnx_conv2d_problem& p, const tnx_config& cfg,
   if (fn == nullptr) return TNX_ERR_NOT_BUILT;
   const int a_rows = plan.tile_w * plan.tile_h;
   CUtensorMap ta, tb, tc;
-  int rc = make_tmap_nhwc(&ta, x, p.dtype, plan.c_pitch, p.w_in, p.h_in, p.batch,
-                          (plan.tile_w - 1) * p.stride_w + 1, (plan.tile_h - 1) * p.stride_h + 1,
-                          p.stride_w, p.stride_h, true);
+  int rc = plan.im2col
+               ? make_tmap_im2col(&ta, x, p, plan.c_pitch)
+               : make_tmap_nhwc(&ta, x, p.dtype, plan.c_pitch, p.w_in, p.h_in, p.batch,
+                                (plan.tile_w - 1) * p.stride_w + 1,
+                                (plan.tile_h - 1) * p.stride_h + 1, p.stride_w, p.stride_h, true);
   if (rc != TNX_OK) return rc;
   rc = make_tmap(&tb, w, p.dtype, plan.k_packed, p.c_out, plan.k_packed, kAtomElems,
                  cfg.tile_n / cfg.cta_group, true);
   if (rc != TNX_OK) return rc;
-  rc = make_tmap_nhwc(&tc, y, p.dtype, plan.c_out_pitch, plan.w_out, plan.h_out, p.batch,
-                      plan.tile_w, plan.tile_h, 1, 1, false);
+  const long long pixels = static_cast<long long>(p.batch) * plan.h_out * plan.w_out;
+  rc = plan.im2col ? make_tmap(&tc, y, p.dtype, plan.c_out_pitch, pixels, plan.c_out_pitch,
+                               kAtomElems, kRowsPerCta, false)
+                   : make_tmap_nhwc(&tc, y, p.dtype, plan.c_out_pitch, plan.w_out, plan.h_out,
+                                    p.batch, plan.tile_w, plan.tile_h, 1, 1, false);
   if (rc != TNX_OK) return rc;
 
   UmmaParams kp = {};
-  kp.m = plan.row_tiles * kRowsPerCta;
+  kp.m = plan.im2col ? static_cast<int>(pixels) : plan.row_tiles * kRowsPerCta;
   kp.n = p.c_out;
   kp.k = plan.k_packed;
   kp.n_out = plan.c_out_pitch;
@@ -1542,7 +1645,9 @@ int umma_conv_launch(const tnx_conv2d_problem& p, const tnx_config& cfg,
   kp.epilogue = TNX_EPI_NONE;
   kp.status = status_word;
   kp.timeout_ns = wait_limit_ns();
-  kp.conv = 1;
+  kp.conv = plan.im2col ? 2 : 1;
+  kp.cv_wout = plan.w_out;
+  kp.cv_hout = plan.h_out;
   kp.cv_tw = plan.tile_w;
   kp.cv_th = plan.tile_h;
   kp.cv_tiles_w = plan.tiles_w;

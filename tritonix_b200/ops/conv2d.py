@@ -77,14 +77,16 @@ class _Conv2dKernel:
             filter_h, filter_w, stride_h, stride_w, pad_h, pad_w, dil_h, dil_w, gemm_m=None,
             gemm_n=None, gemm_k=None, **cfg):
         _cabi.require_cuda(out, input, weight)
-        if not (input.dtype == weight.dtype == out.dtype):
+        # weights_packed=True: ``weight`` is the buffer _cabi.conv_pack_weights() returned
+        packed = bool(cfg.pop("weights_packed", False))
+        if not (input.dtype == out.dtype and (packed or weight.dtype == input.dtype)):
             raise ValueError(f"dtype mismatch {input.dtype}/{weight.dtype}/{out.dtype}")
         if bias is not None and (bias.dtype != input.dtype or not bias.is_cuda):
             raise ValueError("bias must be a CUDA tensor of the input's dtype")
         problem = _cabi.make_conv_problem(
             batch, c_in, h_in, w_in, c_out, filter_h, filter_w, (stride_h, stride_w),
             (pad_h, pad_w), (dil_h, dil_w), input.dtype, bias is not None, _layout(input),
-            _layout(out))
+            _layout(out), _cabi.WEIGHT_PACKED if packed else _cabi.WEIGHT_KCRS)
         config = _conv_config(cfg)
         res = _cabi.conv_query(problem, config)
         if (res.h_out, res.w_out) != (h_out, w_out):
@@ -109,6 +111,30 @@ conv2d_forward_kernel = tunable(
     memory_params={"BLOCK_SIZE_M", "BLOCK_SIZE_N", "BLOCK_SIZE_K", "num_stages"},
     memory_rank={"BLOCK_SIZE_M": lambda rows: -rows},
 )(_Conv2dKernel())
+
+# Packed copies of weight tensors seen recently, so that a layer called again with unchanged
+# weights (inference, or several micro-batches per optimiser step) does not repack them.  An
+# entry is valid while the tensor is alive and its version counter (bumped by every in-place
+# write) has not moved.
+_PACKED_WEIGHTS: "dict[tuple, tuple]" = {}
+_PACKED_WEIGHTS_MAX = 64
+
+
+def _packed_weights(weight: torch.Tensor, problem_of) -> torch.Tensor:
+    import weakref
+
+    key = (weight.data_ptr(), tuple(weight.shape), weight.dtype, weight.device)
+    hit = _PACKED_WEIGHTS.get(key)
+    if hit is not None:
+        ref, version, packed = hit
+        if ref() is weight and version == weight._version:
+            return packed
+    packed = _cabi.conv_pack_weights(problem_of(), weight)
+    if len(_PACKED_WEIGHTS) >= _PACKED_WEIGHTS_MAX:
+        _PACKED_WEIGHTS.pop(next(iter(_PACKED_WEIGHTS)))
+    _PACKED_WEIGHTS[key] = (weakref.ref(weight), weight._version, packed)
+    return packed
+
 
 # Tuned configuration per problem, as the reference keeps one (forward.py:171, 244-300).
 _CONV_FWD_CONFIG_CACHE: dict[tuple, dict] = {}
@@ -174,10 +200,18 @@ def conv2d_forward(input: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor
     out = torch.empty((n, c_out, h_out, w_out), device=input.device, dtype=input.dtype,
                       memory_format=torch.channels_last if channels_last
                       else torch.contiguous_format)
+    extra = {}
+    if input.dtype != torch.float32:
+        weight = _packed_weights(weight, lambda: _cabi.make_conv_problem(
+            n, c_in, h_in, w_in, c_out, r, s, stride, padding, dilation, input.dtype,
+            bias is not None))
+        extra["weights_packed"] = True
     args = (out, input, weight, bias, n, c_in, h_in, w_in, c_out, h_out, w_out, r, s,
             stride[0], stride[1], padding[0], padding[1], dilation[0], dilation[1],
             n * h_out * w_out, c_out, c_in * r * s)
-    launch = conv2d_forward_kernel.run
+
+    def launch(*a, **cfg):
+        return conv2d_forward_kernel.run(*a, **cfg, **extra)
 
     if config is None and input.dtype != torch.float32:
         key = (n, c_in, h_in, w_in, c_out, r, s, stride, padding, dilation, input.dtype,
