@@ -426,13 +426,22 @@ def conv_launch(problem: ConvProblem, config: Config | None, res: ConvResources,
     """Enqueues tnx_conv2d_forward on torch's current stream of x's device."""
     require_cuda(x, w, y)
     ws = conv_workspace(x.device, res.workspace_bytes) if res.workspace_bytes else None
-    with torch.cuda.device(x.device):
-        raise_for(lib.tnx_conv2d_forward(
+    idx = x.device.index if x.device.index is not None else torch.cuda.current_device()
+    switch = idx != torch.cuda.current_device()
+    if switch:
+        previous = torch.cuda.current_device()
+        torch.cuda.set_device(idx)
+    try:
+        rc = lib.tnx_conv2d_forward(
             ctypes.byref(problem), ctypes.byref(config) if config is not None else None,
             x.data_ptr(), w.data_ptr(), bias.data_ptr() if bias is not None else None,
             y.data_ptr(), ws.data_ptr() if ws is not None else None,
             ws.numel() if ws is not None else 0, status_word(x.device).data_ptr(),
-            torch.cuda.current_stream(x.device).cuda_stream))
+            torch.cuda.current_stream(idx).cuda_stream)
+    finally:
+        if switch:
+            torch.cuda.set_device(previous)
+    raise_for(rc)
 
 
 def conv_pack_weights(problem: ConvProblem, weight: torch.Tensor) -> torch.Tensor:

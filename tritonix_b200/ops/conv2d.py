@@ -18,6 +18,8 @@ Search space, under the reference's key names (forward.py:8-18):
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from tritonix_b200 import _cabi
@@ -68,6 +70,9 @@ class _Conv2dKernel:
 
     __name__ = "conv2d_forward_kernel"
 
+    def __init__(self):
+        self._plans: dict = {}
+
     def __getitem__(self, grid):
         def launch(*args, **kwargs):
             return self.run(*args, **kwargs)
@@ -83,15 +88,26 @@ class _Conv2dKernel:
             raise ValueError(f"dtype mismatch {input.dtype}/{weight.dtype}/{out.dtype}")
         if bias is not None and (bias.dtype != input.dtype or not bias.is_cuda):
             raise ValueError("bias must be a CUDA tensor of the input's dtype")
-        problem = _cabi.make_conv_problem(
-            batch, c_in, h_in, w_in, c_out, filter_h, filter_w, (stride_h, stride_w),
-            (pad_h, pad_w), (dil_h, dil_w), input.dtype, bias is not None, _layout(input),
-            _layout(out), _cabi.WEIGHT_PACKED if packed else _cabi.WEIGHT_KCRS)
-        config = _conv_config(cfg)
-        res = _cabi.conv_query(problem, config)
-        if (res.h_out, res.w_out) != (h_out, w_out):
-            raise ValueError(f"H_OUT x W_OUT = {h_out} x {w_out} does not match the geometry "
-                             f"({res.h_out} x {res.w_out})")
+        # problem / config / resources are remembered per distinct call signature
+        key = (batch, c_in, h_in, w_in, c_out, filter_h, filter_w, stride_h, stride_w, pad_h,
+               pad_w, dil_h, dil_w, h_out, w_out, input.dtype, bias is not None, _layout(input),
+               _layout(out), packed, tuple(sorted(cfg.items())),
+               os.environ.get("TNX_CONV_TILED"))
+        plan = self._plans.get(key)
+        if plan is None:
+            problem = _cabi.make_conv_problem(
+                batch, c_in, h_in, w_in, c_out, filter_h, filter_w, (stride_h, stride_w),
+                (pad_h, pad_w), (dil_h, dil_w), input.dtype, bias is not None, _layout(input),
+                _layout(out), _cabi.WEIGHT_PACKED if packed else _cabi.WEIGHT_KCRS)
+            config = _conv_config(cfg)
+            res = _cabi.conv_query(problem, config)
+            if (res.h_out, res.w_out) != (h_out, w_out):
+                raise ValueError(f"H_OUT x W_OUT = {h_out} x {w_out} does not match the geometry "
+                                 f"({res.h_out} x {res.w_out})")
+            if len(self._plans) >= 1024:
+                self._plans.clear()
+            plan = self._plans[key] = (problem, config, res)
+        problem, config, res = plan
         _cabi.conv_launch(problem, config, res, input, weight, bias, out)
         return res
 
