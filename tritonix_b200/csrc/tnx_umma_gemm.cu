@@ -303,6 +303,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         // Convolution: image and first input column / row (before the tap's offset) of this
         // CTA's pixel rectangle.  A pair's missing last tile gets image = batch: all zero fill.
         int cv_n = 0, cv_x = 0, cv_y = 0;
+        // (tap row, tap column, channel block) of the next 64-element K slab; K starts at 0 for
+        // every tile of a convolution (no split-K)
+        int cv_fr = 0, cv_fs = 0, cv_cb = 0;
+        const int cv_fh = p.cv_taps / max(p.cv_fw, 1);
         if (p.conv == 1) {
           const int row_tile = tm * CTA_GROUP + static_cast<int>(cta_rank);
           const int per_image = p.cv_tiles_h * p.cv_tiles_w;
@@ -339,22 +343,26 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (p.conv) {  // one box of pixels x 64 channels per (tap, channel block)
 #pragma unroll
               for (int ka = 0; ka < TILE_K / kAtomElems; ++ka) {
-                const int g = kb * (TILE_K / kAtomElems) + ka;
-                int tap = g / p.cv_cblocks;
-                const bool past = tap >= p.cv_taps;  // second half of an odd last K block
-                if (past) tap = 0;
-                const int fr = tap / p.cv_fw;
-                // (past the last tap: a channel coordinate beyond C reads zeros)
-                const int ch = past ? p.cv_cblocks * kAtomElems
-                                    : (g - tap * p.cv_cblocks) * kAtomElems;
+                // (past the last tap, in the second half of an odd last K block, a channel
+                // coordinate beyond C reads zeros)
+                const bool past = cv_fr >= cv_fh;
+                const int ch = past ? p.cv_cblocks * kAtomElems : cv_cb * kAtomElems;
+                const int off_w = past ? 0 : cv_fs * p.cv_dw, off_h = past ? 0 : cv_fr * p.cv_dh;
                 if (p.conv == 1)
-                  ptx::tma_load_4d(a_dst + ka * a_atom_bytes, &tmap_a, ch,
-                                   cv_x + (tap - fr * p.cv_fw) * p.cv_dw, cv_y + fr * p.cv_dh, cv_n,
-                                   full_bar);
+                  ptx::tma_load_4d(a_dst + ka * a_atom_bytes, &tmap_a, ch, cv_x + off_w, cv_y + off_h,
+                                   cv_n, full_bar);
                 else
                   ptx::tma_load_im2col_4d(a_dst + ka * a_atom_bytes, &tmap_a, ch, cv_x, cv_y, cv_n,
-                                          static_cast<uint16_t>((tap - fr * p.cv_fw) * p.cv_dw),
-                                          static_cast<uint16_t>(fr * p.cv_dh), full_bar);
+                                          static_cast<uint16_t>(off_w), static_cast<uint16_t>(off_h),
+                                          full_bar);
+                // next (tap, channel block) without dividing
+                if (++cv_cb == p.cv_cblocks) {
+                  cv_cb = 0;
+                  if (++cv_fs == p.cv_fw) {
+                    cv_fs = 0;
+                    ++cv_fr;
+                  }
+                }
               }
             } else if (p.a_mmajor) {  // two 64-row atoms of tile_k x 128 B, like a row-major B
 #pragma unroll
@@ -385,22 +393,23 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (p.conv) {
 #pragma unroll
               for (int ka = 0; ka < TILE_K / kAtomElems; ++ka) {
-                const int g = kb * (TILE_K / kAtomElems) + ka;
-                int tap = g / p.cv_cblocks;
-                const bool past = tap >= p.cv_taps;  // second half of an odd last K block
-                if (past) tap = 0;
-                const int fr = tap / p.cv_fw;
-                const int ch = past ? p.cv_cblocks * kAtomElems
-                                    : (g - tap * p.cv_cblocks) * kAtomElems;
+                const bool past = cv_fr >= cv_fh;
+                const int ch = past ? p.cv_cblocks * kAtomElems : cv_cb * kAtomElems;
+                const int off_w = past ? 0 : cv_fs * p.cv_dw, off_h = past ? 0 : cv_fr * p.cv_dh;
                 if (p.conv == 1)
-                  ptx::tma_load_4d_pair(a_dst + ka * a_atom_bytes, &tmap_a, ch,
-                                        cv_x + (tap - fr * p.cv_fw) * p.cv_dw, cv_y + fr * p.cv_dh,
-                                        cv_n, leader_bar);
+                  ptx::tma_load_4d_pair(a_dst + ka * a_atom_bytes, &tmap_a, ch, cv_x + off_w,
+                                        cv_y + off_h, cv_n, leader_bar);
                 else
                   ptx::tma_load_im2col_4d_pair(a_dst + ka * a_atom_bytes, &tmap_a, ch, cv_x, cv_y,
-                                               cv_n,
-                                               static_cast<uint16_t>((tap - fr * p.cv_fw) * p.cv_dw),
-                                               static_cast<uint16_t>(fr * p.cv_dh), leader_bar);
+                                               cv_n, static_cast<uint16_t>(off_w),
+                                               static_cast<uint16_t>(off_h), leader_bar);
+                if (++cv_cb == p.cv_cblocks) {
+                  cv_cb = 0;
+                  if (++cv_fs == p.cv_fw) {
+                    cv_fs = 0;
+                    ++cv_fr;
+                  }
+                }
               }
             } else if (p.a_mmajor) {
 #pragma unroll
@@ -554,6 +563,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
       ptx::tc_fence_after_sync();
       if (epi_tid == 0 && u == cluster_id) TNX_TRACE(4);
+#ifdef TNX_DEV_TRACE
+      const int trace_tile = (u - cluster_id) / num_clusters;  // n-th tile of this CTA
+      if (epi_tid == 0 && trace_tile < 40) TNX_TRACE(160 + trace_tile);
+#endif
       const uint32_t t_acc = tmem_base + lane_sel + acc * TILE_N;
 
       if (xchg) {
@@ -834,6 +847,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
 
       // All tcgen05.ld of this accumulator are complete: hand the TMEM buffer back.
+#ifdef TNX_DEV_TRACE
+      if (epi_tid == 0 && trace_tile < 40) TNX_TRACE(200 + trace_tile);
+#endif
       ptx::tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) {
@@ -1663,6 +1679,12 @@ int umma_conv_launch(const tnx_conv2d_problem& p, const tnx_config& cfg,
   kp.cv_dh = p.dil_h;
   kp.cv_dw = p.dil_w;
   kp.bias = p.has_bias ? bias : nullptr;
+#ifdef TNX_DEV_TRACE
+  {
+    const char* t = getenv("TNX_TRACE_PTR");
+    kp.trace = t ? reinterpret_cast<unsigned long long*>(strtoull(t, nullptr, 0)) : nullptr;
+  }
+#endif
 
   cudaError_t e = allow_full_smem(fn);
   if (e != cudaSuccess) {
