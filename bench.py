@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the dense-contraction path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload gemm|splitk|glu|mlp]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload gemm|splitk|glu|mlp|conv]
                     [--impl ours|reference]
 
 Default workload (`gemm`): bf16 C = A.B with M = N = K = 8192, entries N(0,1)/sqrt(K), fp32
@@ -10,7 +10,8 @@ GPUs every rank owns an 8192-row block of a (8192*N) x 8192 A and a replica of B
 no collective): per-GPU work is fixed, so scaling is "weak".
 Other workloads: `splitk` (fp16 64 x 14336 x 4096, HBM-bound), `glu` (bf16 fused SwiGLU
 8192x4096 . 4096x28672), `mlp` (bf16 SwiGLU MLP d=4096, ff=14336, 32768 tokens, tensor parallel
-over the N GPUs with one chunked NCCL all-reduce; strong scaling).
+over the N GPUs with one chunked NCCL all-reduce; strong scaling), `conv` (bf16 conv2d forward,
+64 x 256 x 28 x 28 NCHW with 256 3x3 filters through `conv2d_forward`; batch-sharded, weak).
 
 One JSON line is printed by rank 0.  `value` is device-timed with the operands resident in HBM;
 `e2e` is the same metric through the public API (`tritonix_b200.matmul`, ...) with the operands
@@ -46,6 +47,10 @@ WORKLOADS = {
                 name="swiglu_bf16_x8192x4096_w12_4096x28672_interleaved"),
     "mlp": dict(m=32768, d=4096, ff=14336, dtype="bf16",
                 name="swiglu_mlp_bf16_d4096_ff14336_tokens32768_tensor_parallel"),
+    # a ResNet-50 stage-3 3x3 layer; m, n, k are the implicit GEMM's sizes
+    "conv": dict(batch=64, c_in=256, h=28, w=28, c_out=256, r=3, s=3, stride=1, pad=1,
+                 m=64 * 28 * 28, n=256, k=256 * 9, dtype="bf16",
+                 name="conv2d_fwd_bf16_nchw_64x256x28x28_w256x256x3x3_s1_p1_per_gpu_batch_sharded"),
 }
 
 GEMM_CFG = {"kernel": "tcgen05", "tile_n": 256, "tile_k": 128, "stages": 3, "cta_group": 2, "group_m": 16}
@@ -54,7 +59,8 @@ GLU_CFG = {"kernel": "tcgen05", "tile_n": 256, "tile_k": 128, "stages": 3, "cta_
 
 # DRAM traffic of the dominant kernel per launch, from the ncu captures summarised under
 # profiles/ (None until a capture of that workload exists).
-NCU_TRAFFIC_BYTES = {"gemm": 1_389_138_048, "splitk": 125_974_528, "glu": 885_355_520, "mlp": None}
+NCU_TRAFFIC_BYTES = {"gemm": 1_389_138_048, "splitk": 125_974_528, "glu": 885_355_520, "mlp": None,
+                     "conv": None}
 
 
 def measured_peaks():
@@ -196,6 +202,46 @@ def setup_contraction(workload, rank, world, dev):
     return step, e2e_step, work
 
 
+def setup_conv(rank, world, dev):
+    """conv: conv2d_forward through the public API on NCHW tensors (the reference's layout), so a
+    step is the input repack, the implicit-GEMM kernel and the output repack; the weights are
+    packed once (they do not change between steps)."""
+    import tritonix_b200 as tnx
+    w = WORKLOADS["conv"]
+    dt = torch_dtype(w["dtype"])
+    xshape = (w["batch"], w["c_in"], w["h"], w["w"])
+    wt = randn((w["c_out"], w["c_in"], w["r"], w["s"]), dt, dev, 1, (w["c_in"] * w["r"] * w["s"]) ** -0.5)
+    x_bytes = w["batch"] * w["c_in"] * w["h"] * w["w"] * 2
+    algo_bytes = x_bytes + wt.numel() * 2 + w["m"] * w["n"] * 2
+    copies = -(-3 * L2_BYTES // algo_bytes)
+    xs = [randn(xshape, dt, dev, 1000 * rank + i, 1.0) for i in range(copies)]
+    state = {"i": 0, "out": None}
+    kw = dict(stride=w["stride"], padding=w["pad"])
+
+    def step():
+        i = state["i"] % copies
+        state["i"] += 1
+        state["out"] = tnx.conv2d_forward(xs[i], wt, None, **kw)
+
+    step()  # first call: picks the configuration and packs the weights
+    torch.cuda.synchronize(dev)
+    x_host = xs[0].cpu().pin_memory()
+    y_host = torch.empty(tuple(state["out"].shape), dtype=dt).pin_memory()
+    x_in = torch.empty_like(xs[0])
+
+    def e2e_step():
+        x_in.copy_(x_host, non_blocking=True)
+        y_host.copy_(tnx.conv2d_forward(x_in, wt, None, **kw), non_blocking=True)
+
+    cfg = dict(sys.modules["tritonix_b200.ops.conv2d"]._CONV_FWD_CONFIG_CACHE.popitem()[1])
+    sys.modules["tritonix_b200.ops.conv2d"]._CONV_FWD_CONFIG_CACHE.clear()
+    step()  # re-tune is cheap; keeps the cache consistent after the peek above
+    work = dict(flops=2.0 * w["m"] * w["n"] * w["k"], bytes=float(algo_bytes), units=None, launches=3,
+                h2d=x_host.numel() * 2, d2h=y_host.numel() * 2, copies=copies, cfg=cfg, out=None,
+                check=None)
+    return step, e2e_step, work
+
+
 def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1):
     comm_sms = (32 if world >= 8 else 0) if comm_sms < 0 else comm_sms
     """SwiGLU MLP, tensor parallel: column-parallel fused gate/up, row-parallel down, one
@@ -296,6 +342,15 @@ def cpu_baseline_sample(workload, seconds_target=15.0):
         flops = 2.0 * m_s * d * 2 * ff + 2.0 * m_s * ff * d
         sample = f"{m_s} of {w['m']} tokens, fp32 torch on host"
         units = float(m_s)
+    elif workload == "conv":
+        from oracle import conv2d as OC
+        b_s = 4
+        x = torch.randn(b_s, w["c_in"], w["h"], w["w"], generator=g)
+        wt = torch.randn(w["c_out"], w["c_in"], w["r"], w["s"], generator=g) * 0.02
+        fn = lambda: OC.conv2d_oracle(x, wt, None, (w["stride"],) * 2, (w["pad"],) * 2)  # noqa: E731
+        flops = 2.0 * (w["m"] // w["batch"] * b_s) * w["n"] * w["k"]
+        sample = f"{b_s} of {w['batch']} images, fp32 im2col + torch.matmul on host"
+        units = None
     else:
         m, n, k = w["m"], w["n"], w["k"]
         m_s = min(m, 512 if workload == "glu" else 1024)
@@ -324,6 +379,8 @@ def cpu_baseline_sample(workload, seconds_target=15.0):
 def metric_of(workload):
     if workload == "mlp":
         return "SwiGLU MLP tokens/s", "tokens/s"
+    if workload == "conv":
+        return "conv2d forward TFLOP/s", "TFLOP/s"
     return "GEMM TFLOP/s", "TFLOP/s"
 
 
@@ -428,6 +485,8 @@ def main():
             base.update(override)
     if args.workload == "mlp":
         step, e2e_step, work = setup_mlp(rank, world, dev, args.chunks, args.comm_sms)
+    elif args.workload == "conv":
+        step, e2e_step, work = setup_conv(rank, world, dev)
     else:
         step, e2e_step, work = setup_contraction(args.workload, rank, world, dev)
 
