@@ -1,9 +1,10 @@
 """tritonix_b200 — the dense-contraction path of tritonix (tiled GEMM, split-K GEMM, fused
-GLU/SwiGLU, autotuner, dispatcher) on hand-written CUDA kernels for NVIDIA B200 (sm_100a).
+GLU/SwiGLU, convolution forward, autotuner, dispatcher) on hand-written CUDA kernels for NVIDIA
+B200 (sm_100a).
 
 The public names follow the reference package (tritonix/__init__.py:3-13) for this path:
-``matmul``, ``matmul_splitk``, ``glu_kernel``, ``swiglu_kernel``, ``tunable``,
-``TunableKernel``, ``PowerOfTwo``, ``Range``, ``Choice``.  There is one backend, ``"cuda"``;
+``matmul``, ``matmul_splitk``, ``glu_kernel``, ``swiglu_kernel``, ``conv2d_forward``,
+``torch_conv2d_forward``, ``tunable``, ``TunableKernel``, ``PowerOfTwo``, ``Range``, ``Choice``.  There is one backend, ``"cuda"``;
 nothing falls back to Triton, PyTorch or the CPU.
 """
 from tritonix_b200._cabi import DeviceStatusError, OutOfResources, check_status
