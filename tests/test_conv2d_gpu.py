@@ -76,6 +76,9 @@ GEOMS = [
     ((1, 128, 28, 28), (200, 3, 3), (1, 1), (1, 1), (1, 1)),   # c_out not a tile multiple
     ((2, 16, 9, 9), (8, 3, 3), (3, 3), (0, 0), (1, 1)),        # stride 3, tiny c_out
     ((1, 8, 5, 300), (16, 1, 3), (1, 1), (0, 1), (1, 1)),      # wide rows
+    ((1, 130, 33, 21), (24, 5, 2), (1, 1), (4, 0), (1, 3)),    # 3 channel blocks, 5x2 dilated filter
+    ((2, 64, 12, 126), (32, 3, 3), (1, 1), (1, 1), (1, 1)),    # rows of 126 pixels
+    ((5, 72, 9, 9), (136, 3, 3), (1, 1), (0, 0), (1, 1)),      # no padding, odd tile counts
 ]
 
 
