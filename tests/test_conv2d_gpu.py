@@ -208,6 +208,20 @@ def test_packed_weights_match_and_follow_updates():
     assert not torch.equal(y1, y2)
 
 
+def test_torch_custom_op_and_fake_kernel():
+    import tritonix_b200  # noqa: F401  (registers torch.ops.tritonix.*)
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    x, w, b = seeded((2, 32, 12, 10), (24, 3, 3), torch.float16, seed=6)
+    y = torch.ops.tritonix.conv2d_forward(x.to(DEV), w.to(DEV), b.to(DEV), [2, 1], [1, 1], [1, 1], [])
+    _cabi.check_status(y.device)
+    check(y.cpu(), OC.conv2d_oracle(x, w, b, (2, 1), (1, 1), (1, 1)), torch.float16)
+    with FakeTensorMode():
+        fx = torch.empty(2, 32, 12, 10, device=DEV, dtype=torch.float16)
+        fw = torch.empty(24, 32, 3, 3, device=DEV, dtype=torch.float16)
+        assert torch.ops.tritonix.conv2d_forward(fx, fw, None, [2, 1], [1, 1], [1, 1], []).shape \
+            == (2, 24, 6, 10)
+
+
 def test_errors():
     x = torch.zeros(1, 8, 4, 4, device=DEV, dtype=torch.float16)
     w = torch.zeros(8, 8, 7, 7, device=DEV, dtype=torch.float16)
