@@ -558,7 +558,8 @@ def main():
         "config": {"workload": WORKLOADS[args.workload]["name"], "kernel_config": work["cfg"],
                    **({"allreduce_chunks": work["chunks"], "comm_sms": work["comm_sms"]}
                       if args.workload == "mlp" and world > 1 else {}),
-                   "parallelism": ("tp%d" % world) if strong else ("rows_sharded_x%d" % world),
+                   "parallelism": ("tp%d" % world) if strong else
+                   (("batch_sharded_x%d" if args.workload == "conv" else "rows_sharded_x%d") % world),
                    "launch": "cuda_graph_of_%d_steps" % args.steps if use_graph else "eager",
                    "l2": ("operands rotate through %d copies (> 3x L2)" % work["copies"]) if work["copies"] > 1
                    else "operands exceed the 126 MB L2"},
