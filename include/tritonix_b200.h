@@ -244,7 +244,8 @@ int tnx_conv2d_query(const tnx_conv2d_problem* problem, const tnx_config* config
  * every call: tnx_conv2d_packed_weight_bytes() gives the size of the packed buffer (0 for
  * fp32, which has no packed form), tnx_conv2d_pack_weights() fills it from C_OUT x C x R x S
  * weights on `stream`; pass it as `weight` with problem->weight_layout = TNX_WEIGHT_PACKED.
- * The packed form depends only on c_in, c_out, filter_h, filter_w and dtype.
+ * The packed form depends only on c_in, c_out, filter_h, filter_w and dtype (and on
+ * TNX_CONV_NO_FOLD, which must not change between packing and use).
  */
 int64_t tnx_conv2d_packed_weight_bytes(const tnx_conv2d_problem* problem);
 int tnx_conv2d_pack_weights(const tnx_conv2d_problem* problem, const void* weight, void* packed,
@@ -259,7 +260,10 @@ int tnx_conv2d_pack_weights(const tnx_conv2d_problem* problem, const void* weigh
  *   pixels; rectangles of pixels fetched with tiled boxes when the padding or the dilated
  *   filter exceeds what an im2col box can express, or when TNX_CONV_TILED is set in the
  *   environment); padding comes from TMA's out-of-range zero fill; the result is written
- *   N x H x W x C and repacked if NCHW is wanted.
+ *   N x H x W x C and repacked if NCHW is wanted.  Inputs with c_in <= 16 and
+ *   filter_w * c_in <= 64 are repacked so that the taps of a filter row become channels
+ *   (N x H x W_OUT x filter_w*c_in), which shortens K filter_w-fold; TNX_CONV_NO_FOLD in the
+ *   environment keeps one zero-padded 64-channel block per tap instead.
  *   fp32: a CUDA-core kernel reads and writes the tensors in place (no workspace).
  * `bias` may be NULL when has_bias == 0.  `workspace` needs workspace_bytes from the query and
  * 256-byte alignment; its content before and after the call is meaningless.

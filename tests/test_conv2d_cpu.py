@@ -42,14 +42,40 @@ def test_kernel_family_and_workspace():
     res_cl, _ = query((2, 64, 56, 56), (128, 3, 3), padding=(1, 1),
                       input_layout=_cabi.LAYOUT_NHWC, output_layout=_cabi.LAYOUT_NHWC)
     assert w_bytes <= res_cl.workspace_bytes <= w_bytes + 256
-    # 3 input channels are padded to 8 in the repacked copy, and to 64 in the packed weights
-    res3, p3 = query((1, 3, 32, 32), (16, 3, 3), input_layout=_cabi.LAYOUT_NHWC)
-    assert res3.workspace_bytes >= 32 * 32 * 8 * 2 + 16 * 9 * 64 * 2
-    assert _cabi.lib.tnx_conv2d_packed_weight_bytes(ctypes.byref(p3)) == 16 * 9 * 64 * 2
+    # 24 input channels are padded to 64 in the packed weights (one 64-channel block per tap)
+    res24, p24 = query((1, 24, 32, 32), (16, 3, 3), input_layout=_cabi.LAYOUT_NHWC)
+    assert res24.workspace_bytes >= 16 * 9 * 64 * 2
+    assert _cabi.lib.tnx_conv2d_packed_weight_bytes(ctypes.byref(p24)) == 16 * 9 * 64 * 2
     # fp32: CUDA-core kernel, nothing to repack
     res32, p32 = query((2, 64, 56, 56), (128, 3, 3), padding=(1, 1), dtype=torch.float32)
     assert res32.kernel == _cabi.KERNEL_STRIDED and res32.workspace_bytes == 0
     assert _cabi.lib.tnx_conv2d_packed_weight_bytes(ctypes.byref(p32)) == 0
+
+
+def test_thin_inputs_fold_the_filter_row_into_channels(monkeypatch):
+    """C <= 16 and S*C <= 64: the S taps of a filter row become channels of a repacked input
+    (N x H x W_OUT x S*C, padded to 8), the kernel then sees an R x 1 filter and the horizontal
+    stride disappears (so strides above 8 are fine there)."""
+    res, p = query((2, 3, 64, 64), (32, 7, 7), stride=(2, 2), padding=(3, 3))
+    assert (res.h_out, res.w_out) == (32, 32)
+    folded_in = 2 * 64 * 32 * 24 * 2                 # 7 * 3 = 21 channels -> 24
+    packed = 32 * 7 * 64 * 2                         # one 64-wide K block per filter row
+    y_nhwc = 2 * 32 * 32 * 32 * 2
+    assert folded_in + packed + y_nhwc <= res.workspace_bytes <= folded_in + packed + y_nhwc + 3 * 256
+    assert _cabi.lib.tnx_conv2d_packed_weight_bytes(ctypes.byref(p)) == packed
+    res, _ = query((1, 4, 16, 200), (8, 1, 5), stride=(1, 11))     # stride_w folded away
+    assert res.w_out == (200 - 5) // 11 + 1
+    monkeypatch.setenv("TNX_CONV_NO_FOLD", "1")
+    res, p = query((2, 3, 64, 64), (32, 7, 7), stride=(2, 2), padding=(3, 3))
+    assert _cabi.lib.tnx_conv2d_packed_weight_bytes(ctypes.byref(p)) == 32 * 49 * 64 * 2
+    with pytest.raises(ValueError):
+        query((1, 4, 16, 200), (8, 1, 5), stride=(1, 11))
+    monkeypatch.delenv("TNX_CONV_NO_FOLD")
+    # not for 17+ channels, 1-wide filters or fp32
+    for kw in (dict(xshape=(1, 17, 16, 16), wshape=(8, 3, 3)), dict(xshape=(1, 8, 16, 16), wshape=(8, 3, 1))):
+        _, p = query(**kw)
+        taps = kw["wshape"][1] * kw["wshape"][2]
+        assert _cabi.lib.tnx_conv2d_packed_weight_bytes(ctypes.byref(p)) == 8 * taps * 64 * 2
 
 
 def test_rectangular_tiles_when_im2col_boxes_cannot_be_used(monkeypatch):

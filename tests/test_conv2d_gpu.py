@@ -102,6 +102,33 @@ def test_geometries_against_oracle(geom, dtype, box_mode):
     check(out, OC.conv2d_oracle(x, w, b, stride, padding, dilation), dtype)
 
 
+THIN = [
+    ((2, 3, 64, 64), (32, 7, 7), (2, 2), (3, 3), (1, 1)),      # the classic stem
+    ((1, 3, 33, 47), (24, 3, 3), (1, 1), (1, 1), (1, 1)),
+    ((2, 8, 20, 24), (16, 3, 5), (1, 2), (1, 2), (1, 1)),      # 40 folded channels
+    ((1, 16, 18, 18), (40, 3, 4), (1, 1), (0, 2), (2, 1)),     # exactly 64 folded channels
+    ((1, 4, 9, 120), (8, 1, 5), (1, 11), (0, 0), (1, 1)),      # horizontal stride 11
+    ((3, 1, 28, 28), (8, 5, 5), (1, 1), (2, 2), (1, 2)),       # one channel, dilated columns
+]
+
+
+@pytest.mark.parametrize("fold", [True, False])
+@pytest.mark.parametrize("layout", ["nchw", "channels_last"])
+@pytest.mark.parametrize("geom", THIN)
+def test_thin_inputs(geom, layout, fold, monkeypatch):
+    """Inputs with few channels: the filter row is folded into the channels (default) or every
+    tap gets its own zero-padded 64-channel block (TNX_CONV_NO_FOLD); same numbers either way."""
+    xshape, wshape, stride, padding, dilation = geom
+    if not fold:
+        if stride[1] > 8:
+            pytest.skip("strides above 8 need the folded path")
+        monkeypatch.setenv("TNX_CONV_NO_FOLD", "1")
+    x, w, b = seeded(xshape, wshape, torch.float16, bias=True, seed=wshape[0])
+    out, res = run_conv(x, w, b, stride, padding, dilation, channels_last=(layout == "channels_last"))
+    assert res.kernel == _cabi.KERNEL_TCGEN05
+    check(out, OC.conv2d_oracle(x, w, b, stride, padding, dilation), torch.float16)
+
+
 @pytest.mark.parametrize("cfg", [
     dict(BLOCK_SIZE_M=128, BLOCK_SIZE_N=64, BLOCK_SIZE_K=64),
     dict(BLOCK_SIZE_M=128, BLOCK_SIZE_N=128, BLOCK_SIZE_K=128),

@@ -153,6 +153,83 @@ __global__ void pack_weights16_kernel(const uint16_t* __restrict__ w, uint16_t* 
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Width folding for thin inputs.  With C channels padded to 64 per filter tap, a 3-channel 7x7
+// stem would spend 21 of every 22 multiply-adds on zeros.  Instead the S taps of a filter row
+// become channels: X'[n][h][wo][s*C + c] = X[n][c][h][wo*stride_w - pad_w + s*dil_w] (zero outside
+// the image), and the convolution becomes an R x 1 one over X' with S*C channels, stride_w = 1 and
+// no horizontal padding.  Applies when C <= 16 and S*C <= 64.
+// ---------------------------------------------------------------------------------------------
+__global__ void fold_width16_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ out,
+                                    int batch, int c, int h, int w, int w_out, int fw, int cf,
+                                    int stride_w, int pad_w, int dil_w, long long sn, long long sc,
+                                    long long sh, long long sw) {
+  const long long total = static_cast<long long>(batch) * h * w_out * fw;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int s = static_cast<int>(i % fw);
+    long long rest = i / fw;
+    const int wo = static_cast<int>(rest % w_out);
+    rest /= w_out;
+    const int hh = static_cast<int>(rest % h);
+    const long long n = rest / h;
+    const int wi = wo * stride_w - pad_w + s * dil_w;
+    const bool inside = wi >= 0 && wi < w;
+    uint16_t* dst = out + ((n * h + hh) * w_out + wo) * cf + s * c;
+    const uint16_t* src = x + n * sn + hh * sh + wi * sw;
+    for (int ch = 0; ch < c; ++ch) dst[ch] = inside ? src[ch * sc] : static_cast<uint16_t>(0);
+    if (s == fw - 1)
+      for (int ch = fw * c; ch < cf; ++ch) out[((n * h + hh) * w_out + wo) * cf + ch] = 0;
+  }
+}
+
+// Weights for the folded problem: C_OUT x R x 64 with K index s*C + c inside a filter row.
+__global__ void pack_weights_folded16_kernel(const uint16_t* __restrict__ w,
+                                             uint16_t* __restrict__ out, int c_out, int c, int fh,
+                                             int fw) {
+  const long long total = static_cast<long long>(c_out) * fh * 64;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int k = static_cast<int>(i % 64);
+    const long long rest = i / 64;
+    const int r = static_cast<int>(rest % fh);
+    const long long co = rest / fh;
+    const int s = k / c, ch = k - s * c;
+    out[i] = s < fw ? w[((co * c + ch) * fh + r) * fw + s] : static_cast<uint16_t>(0);
+  }
+}
+
+bool folds_width(const tnx_conv2d_problem& p) {
+  if (getenv("TNX_CONV_NO_FOLD") != nullptr) return false;  // read every time: tests flip it
+  return p.dtype != TNX_F32 && p.filter_w > 1 && p.c_in <= 16 && p.c_in * p.filter_w <= 64;
+}
+
+inline int conv_w_out(const tnx_conv2d_problem& p) {
+  return (p.w_in + 2 * p.pad_w - p.dil_w * (p.filter_w - 1) - 1) / p.stride_w + 1;
+}
+
+// The problem the tcgen05 kernel is given after folding: N x H x W_OUT x (S*C padded to 8)
+// input in the workspace, R x 1 filter, packed weights.
+tnx_conv2d_problem folded_problem(const tnx_conv2d_problem& p) {
+  tnx_conv2d_problem q = p;
+  q.c_in = (p.c_in * p.filter_w + 7) / 8 * 8;
+  q.w_in = conv_w_out(p);
+  q.filter_w = 1;
+  q.stride_w = 1;
+  q.pad_w = 0;
+  q.dil_w = 1;
+  q.input_layout = TNX_LAYOUT_NHWC;
+  q.weight_layout = TNX_WEIGHT_PACKED;
+  return q;
+}
+
+inline long long align256ll(long long v) { return (v + 255) / 256 * 256; }
+
+inline long long folded_input_bytes(const tnx_conv2d_problem& p) {
+  return align256ll(static_cast<long long>(p.batch) * p.h_in * conv_w_out(p) *
+                    ((p.c_in * p.filter_w + 7) / 8 * 8) * 2);
+}
+
 inline int grid_for(long long total) {
   long long blocks = (total + 255) / 256;
   return static_cast<int>(blocks < 1 ? 1 : (blocks > 148 * 16 ? 148 * 16 : blocks));
@@ -305,11 +382,19 @@ extern "C" int tnx_conv2d_query(const tnx_conv2d_problem* problem, const tnx_con
   }
   tnx_config cfg = config ? *config : tnx_config{};
   tnx::ConvPlan plan;
+  if (tnx::folds_width(*problem)) {
+    const tnx_conv2d_problem q = tnx::folded_problem(*problem);
+    rc = tnx::umma_conv_query(q, &cfg, out, &plan);
+    out->workspace_bytes += tnx::folded_input_bytes(*problem);  // the folded input follows the plan's areas
+    return rc;
+  }
   return tnx::umma_conv_query(*problem, &cfg, out, &plan);
 }
 
 extern "C" int64_t tnx_conv2d_packed_weight_bytes(const tnx_conv2d_problem* problem) {
   if (tnx::validate_conv(problem) != TNX_OK || problem->dtype == TNX_F32) return 0;
+  if (tnx::folds_width(*problem))
+    return static_cast<int64_t>(problem->c_out) * problem->filter_h * 64 * 2;
   const int64_t c_padded = (problem->c_in + 63) / 64 * 64;
   return static_cast<int64_t>(problem->c_out) * problem->filter_h * problem->filter_w * c_padded * 2;
 }
@@ -326,12 +411,20 @@ extern "C" int tnx_conv2d_pack_weights(const tnx_conv2d_problem* problem, const 
     tnx::set_error("weight and packed must not be NULL and packed must be 16-byte aligned");
     return TNX_ERR_INVALID;
   }
-  const int taps = problem->filter_h * problem->filter_w;
-  const int c_padded = (problem->c_in + 63) / 64 * 64;
-  const long long groups = static_cast<long long>(problem->c_out) * taps * (c_padded / 8);
-  tnx::pack_weights16_kernel<<<tnx::grid_for(groups), 256, 0, static_cast<cudaStream_t>(stream_ptr)>>>(
-      static_cast<const uint16_t*>(weight), static_cast<uint16_t*>(packed), problem->c_out,
-      problem->c_in, taps, c_padded);
+  if (tnx::folds_width(*problem)) {
+    tnx::pack_weights_folded16_kernel<<<tnx::grid_for(static_cast<long long>(problem->c_out) *
+                                                      problem->filter_h * 64),
+                                        256, 0, static_cast<cudaStream_t>(stream_ptr)>>>(
+        static_cast<const uint16_t*>(weight), static_cast<uint16_t*>(packed), problem->c_out,
+        problem->c_in, problem->filter_h, problem->filter_w);
+  } else {
+    const int taps = problem->filter_h * problem->filter_w;
+    const int c_padded = (problem->c_in + 63) / 64 * 64;
+    const long long groups = static_cast<long long>(problem->c_out) * taps * (c_padded / 8);
+    tnx::pack_weights16_kernel<<<tnx::grid_for(groups), 256, 0, static_cast<cudaStream_t>(stream_ptr)>>>(
+        static_cast<const uint16_t*>(weight), static_cast<uint16_t*>(packed), problem->c_out,
+        problem->c_in, taps, c_padded);
+  }
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     tnx::set_error("weight packing kernel launch failed: %s", cudaGetErrorString(e));
@@ -391,12 +484,14 @@ extern "C" int tnx_conv2d_forward(const tnx_conv2d_problem* problem, const tnx_c
 
   tnx_config cfg = config ? *config : tnx_config{};
   tnx::ConvPlan plan;
-  rc = tnx::umma_conv_query(p, &cfg, &res, &plan);
+  const bool fold = tnx::folds_width(p);
+  const tnx_conv2d_problem folded = fold ? tnx::folded_problem(p) : p;
+  rc = tnx::umma_conv_query(folded, &cfg, &res, &plan);
   if (rc != TNX_OK) return rc;
-  if (plan.workspace_bytes > 0 &&
-      (workspace == nullptr || workspace_bytes < static_cast<size_t>(plan.workspace_bytes))) {
-    tnx::set_error("convolution needs a workspace of %lld bytes (tnx_conv2d_query), got %zu",
-                   static_cast<long long>(plan.workspace_bytes), workspace_bytes);
+  const long long need = plan.workspace_bytes + (fold ? tnx::folded_input_bytes(p) : 0);
+  if (need > 0 && (workspace == nullptr || workspace_bytes < static_cast<size_t>(need))) {
+    tnx::set_error("convolution needs a workspace of %lld bytes (tnx_conv2d_query), got %zu", need,
+                   workspace_bytes);
     return TNX_ERR_INVALID;
   }
   if (reinterpret_cast<uintptr_t>(workspace) & 255u) {
@@ -406,6 +501,57 @@ extern "C" int tnx_conv2d_forward(const tnx_conv2d_problem* problem, const tnx_c
   char* ws = static_cast<char*>(workspace);
   const long long in_pixels = static_cast<long long>(p.h_in) * p.w_in;
   const long long out_pixels = static_cast<long long>(res.h_out) * res.w_out;
+
+  if (fold) {
+    // Thin input: the taps of a filter row become channels (see fold_width16_kernel), then the
+    // same kernel runs an R x 1 convolution over the folded copy.
+    uint16_t* xf = reinterpret_cast<uint16_t*>(ws + plan.workspace_bytes);
+    long long sn, sc, sh, sw;
+    if (p.input_layout == TNX_LAYOUT_NCHW) {
+      sw = 1; sh = p.w_in; sc = in_pixels; sn = in_pixels * p.c_in;
+    } else {
+      sc = 1; sw = p.c_in; sh = static_cast<long long>(p.w_in) * p.c_in; sn = sh * p.h_in;
+    }
+    const long long threads = static_cast<long long>(p.batch) * p.h_in * res.w_out * p.filter_w;
+    tnx::fold_width16_kernel<<<tnx::grid_for(threads), 256, 0, stream>>>(
+        static_cast<const uint16_t*>(input), xf, p.batch, p.c_in, p.h_in, p.w_in, res.w_out,
+        p.filter_w, folded.c_in, p.stride_w, p.pad_w, p.dil_w, sn, sc, sh, sw);
+    const void* w_packed = weight;
+    if (p.weight_layout != TNX_WEIGHT_PACKED) {
+      tnx::pack_weights_folded16_kernel<<<tnx::grid_for(static_cast<long long>(p.c_out) * p.filter_h * 64),
+                                          256, 0, stream>>>(
+          static_cast<const uint16_t*>(weight), reinterpret_cast<uint16_t*>(ws + plan.off_weight),
+          p.c_out, p.c_in, p.filter_h, p.filter_w);
+      w_packed = ws + plan.off_weight;
+    }
+    cudaError_t fe = cudaGetLastError();
+    if (fe != cudaSuccess) {
+      tnx::set_error("folding kernel launch failed: %s", cudaGetErrorString(fe));
+      return TNX_ERR_CUDA;
+    }
+    void* yf = plan.repack_output ? static_cast<void*>(ws + plan.off_output) : output;
+    rc = tnx::umma_conv_launch(folded, cfg, res, plan, xf, w_packed, bias, yf, status_word, stream);
+    if (rc != TNX_OK) return rc;
+    if (plan.repack_output) {
+      if (p.output_layout == TNX_LAYOUT_NCHW) {
+        rc = tnx::launch_transpose16(yf, output, p.batch, static_cast<int>(out_pixels), p.c_out,
+                                     plan.c_out_pitch, out_pixels, out_pixels * plan.c_out_pitch,
+                                     out_pixels * p.c_out, stream);
+        if (rc != TNX_OK) return rc;
+      } else {
+        const long long px = out_pixels * p.batch;
+        tnx::unpad_channels16_kernel<<<tnx::grid_for(px * p.c_out), 256, 0, stream>>>(
+            static_cast<const uint16_t*>(yf), static_cast<uint16_t*>(output), px, p.c_out,
+            plan.c_out_pitch);
+        fe = cudaGetLastError();
+        if (fe != cudaSuccess) {
+          tnx::set_error("repacking kernel launch failed: %s", cudaGetErrorString(fe));
+          return TNX_ERR_CUDA;
+        }
+      }
+    }
+    return TNX_OK;
+  }
 
   // 1. input as N x H x W x c_pitch
   const void* x = input;

@@ -7,7 +7,9 @@ For fp16/bf16 it runs on the tcgen05 kernel: a tile's 128 rows are a rectangle o
 each filter tap is one TMA box load from the N x H x W x C input (zero fill outside the image is
 the padding), the weights are a K-major operand.  NCHW tensors are repacked on the way in and
 out; ``torch.channels_last`` tensors with channel counts that are multiples of 8 are used in
-place.  fp32 runs on a CUDA-core kernel.
+place; inputs with at most 16 channels are repacked so that a filter row's taps become channels
+(a 3-channel 7x7 stem then multiplies 448 instead of 3136 K elements per output).  fp32 runs on
+a CUDA-core kernel.
 
 Search space, under the reference's key names (forward.py:8-18):
   BLOCK_SIZE_M  output pixels per tile: 128 = one SM per tile, 256 = a CTA pair
@@ -92,7 +94,7 @@ class _Conv2dKernel:
         key = (batch, c_in, h_in, w_in, c_out, filter_h, filter_w, stride_h, stride_w, pad_h,
                pad_w, dil_h, dil_w, h_out, w_out, input.dtype, bias is not None, _layout(input),
                _layout(out), packed, tuple(sorted(cfg.items())),
-               os.environ.get("TNX_CONV_TILED"))
+               os.environ.get("TNX_CONV_TILED"), os.environ.get("TNX_CONV_NO_FOLD"))
         plan = self._plans.get(key)
         if plan is None:
             problem = _cabi.make_conv_problem(
@@ -139,7 +141,8 @@ _PACKED_WEIGHTS_MAX = 64
 def _packed_weights(weight: torch.Tensor, problem_of) -> torch.Tensor:
     import weakref
 
-    key = (weight.data_ptr(), tuple(weight.shape), weight.dtype, weight.device)
+    key = (weight.data_ptr(), tuple(weight.shape), weight.dtype, weight.device,
+           os.environ.get("TNX_CONV_NO_FOLD"))
     hit = _PACKED_WEIGHTS.get(key)
     if hit is not None:
         ref, version, packed = hit
