@@ -162,10 +162,13 @@ _CANDIDATE_CONFIGS = [
     (256, 256, 64, 8),
     (256, 256, 128, 8),
     (256, 128, 64, 8),
+    (256, 128, 128, 8),
     (128, 256, 64, 8),
+    (128, 256, 128, 8),
     (128, 128, 64, 8),
     (128, 128, 128, 8),
     (128, 64, 64, 8),
+    (128, 64, 128, 8),
 ]
 
 
