@@ -72,12 +72,49 @@ __global__ void transpose16_pairs_kernel(const uint16_t* __restrict__ src, uint1
   }
 }
 
+// The same transpose with 16-byte accesses and no shared memory: a thread loads an 8 x 8 block
+// (one uint4 from each of 8 rows), transposes it in registers with byte permutes and stores 8
+// uint4.  The 8 threads that share a row of blocks read (and the 8 that share a column write)
+// one whole 128-byte line.  Needs cols, both pitches and both batch strides to be multiples of
+// 8 and 16-byte aligned bases.
+__global__ void __launch_bounds__(64)
+transpose16_vec8_kernel(const uint16_t* __restrict__ src, uint16_t* __restrict__ dst, int rows,
+                        int cols, long long src_pitch, long long dst_pitch, long long src_batch,
+                        long long dst_batch) {
+  const uint16_t* s = src + static_cast<long long>(blockIdx.z) * src_batch;
+  uint16_t* d = dst + static_cast<long long>(blockIdx.z) * dst_batch;
+  const int c = blockIdx.x * 64 + (threadIdx.x & 7) * 8;   // first source column of the block
+  const int r = blockIdx.y * 64 + (threadIdx.x >> 3) * 8;  // first source row of the block
+  if (c >= cols || r >= dst_pitch) return;
+  uint4 in[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    in[i] = r + i < rows ? *reinterpret_cast<const uint4*>(s + (r + i) * src_pitch + c)
+                         : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {  // word column j holds source columns 2j and 2j + 1
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      w[i] = j == 0 ? in[i].x : j == 1 ? in[i].y : j == 2 ? in[i].z : in[i].w;
+    uint4 lo, hi;  // destination rows c + 2j and c + 2j + 1: source rows r .. r + 7
+    lo.x = __byte_perm(w[0], w[1], 0x5410); hi.x = __byte_perm(w[0], w[1], 0x7632);
+    lo.y = __byte_perm(w[2], w[3], 0x5410); hi.y = __byte_perm(w[2], w[3], 0x7632);
+    lo.z = __byte_perm(w[4], w[5], 0x5410); hi.z = __byte_perm(w[4], w[5], 0x7632);
+    lo.w = __byte_perm(w[6], w[7], 0x5410); hi.w = __byte_perm(w[6], w[7], 0x7632);
+    *reinterpret_cast<uint4*>(d + (c + 2 * j) * dst_pitch + r) = lo;
+    *reinterpret_cast<uint4*>(d + (c + 2 * j + 1) * dst_pitch + r) = hi;
+  }
+}
+
 int launch_transpose16(const void* src, void* dst, int batch, int rows, int cols,
                        long long src_pitch, long long dst_pitch, long long src_batch,
                        long long dst_batch, cudaStream_t stream) {
-  const bool pairs = ((cols | src_pitch | dst_pitch | src_batch | dst_batch) & 1) == 0 &&
-                     ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 3u) == 0;
-  const int edge = pairs ? 64 : 32;
+  const long long all = cols | src_pitch | dst_pitch | src_batch | dst_batch;
+  const uintptr_t bases = reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst);
+  const bool vec8 = (all & 7) == 0 && (bases & 15u) == 0;
+  const bool pairs = (all & 1) == 0 && (bases & 3u) == 0;
+  const int edge = (vec8 || pairs) ? 64 : 32;
   // grid.y covers dst_pitch so that the zero padding of the last block of columns is written
   const int row_blocks = static_cast<int>((dst_pitch + edge - 1) / edge);
   const int col_blocks = (cols + edge - 1) / edge;
@@ -86,7 +123,11 @@ int launch_transpose16(const void* src, void* dst, int batch, int rows, int cols
     return TNX_ERR_INVALID;
   }
   dim3 grid(col_blocks, row_blocks, batch), block(32, 8, 1);
-  if (pairs)
+  if (vec8)
+    transpose16_vec8_kernel<<<grid, 64, 0, stream>>>(static_cast<const uint16_t*>(src),
+                                                     static_cast<uint16_t*>(dst), rows, cols,
+                                                     src_pitch, dst_pitch, src_batch, dst_batch);
+  else if (pairs)
     transpose16_pairs_kernel<<<grid, block, 0, stream>>>(static_cast<const uint16_t*>(src),
                                                        static_cast<uint16_t*>(dst), rows, cols,
                                                        src_pitch, dst_pitch, src_batch, dst_batch);
