@@ -78,6 +78,25 @@ def test_thin_inputs_fold_the_filter_row_into_channels(monkeypatch):
         assert _cabi.lib.tnx_conv2d_packed_weight_bytes(ctypes.byref(p)) == 8 * taps * 64 * 2
 
 
+def test_pointwise_nchw_needs_no_workspace(monkeypatch):
+    """1 x 1, stride 1, no padding, NCHW: a batch of GEMMs on the tensors as they are."""
+    res, p = query((4, 64, 28, 28), (256, 1, 1))
+    assert res.kernel == _cabi.KERNEL_TCGEN05 and res.workspace_bytes == 0
+    assert (res.h_out, res.w_out) == (28, 28) and res.grid % 2 == 0      # CTA pairs for 256 channels
+    # anything that breaks the plain-GEMM shape goes through the repacking path
+    for kw in (dict(stride=(2, 2)), dict(padding=(1, 1)), dict(input_layout=_cabi.LAYOUT_NHWC),
+               dict(output_layout=_cabi.LAYOUT_NHWC), dict(weight_layout=_cabi.WEIGHT_PACKED)):
+        res, _ = query((4, 64, 28, 28), (256, 1, 1), **kw)
+        assert res.workspace_bytes > 0
+    res, _ = query((4, 64, 7, 7), (256, 1, 1))        # 49 pixels per image: not a multiple of 8
+    assert res.workspace_bytes > 0
+    res, _ = query((4, 20, 8, 8), (256, 1, 1))        # 20 channels: not a multiple of 8
+    assert res.workspace_bytes > 0
+    monkeypatch.setenv("TNX_CONV_NO_BATCHED_GEMM", "1")
+    res, _ = query((4, 64, 28, 28), (256, 1, 1))
+    assert res.workspace_bytes > 0
+
+
 def test_rectangular_tiles_when_im2col_boxes_cannot_be_used(monkeypatch):
     res, _ = query((1, 64, 56, 56), (64, 3, 3), padding=(1, 1))
     assert (res.tile_w, res.tile_h) == (128, 1)

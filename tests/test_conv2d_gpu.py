@@ -129,6 +129,33 @@ def test_thin_inputs(geom, layout, fold, monkeypatch):
     check(out, OC.conv2d_oracle(x, w, b, stride, padding, dilation), torch.float16)
 
 
+POINTWISE = [
+    ((2, 64, 8, 8), (24, 1, 1)),        # fewer output channels than a tile has rows
+    ((3, 128, 28, 28), (256, 1, 1)),    # CTA pairs by default
+    ((1, 40, 4, 6), (72, 1, 1)),        # 24 pixels: one ragged column tile
+    ((5, 72, 12, 10), (200, 1, 1)),     # ragged rows, columns and K
+]
+
+
+@pytest.mark.parametrize("as_gemm", [True, False])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("geom", POINTWISE)
+def test_pointwise_on_nchw_is_a_batch_of_gemms(geom, dtype, as_gemm, monkeypatch):
+    """1 x 1 / stride 1 / no padding on NCHW tensors: one launch, no workspace, bias per output
+    row; TNX_CONV_NO_BATCHED_GEMM sends the same call through the repacking path."""
+    xshape, wshape = geom
+    if not as_gemm:
+        monkeypatch.setenv("TNX_CONV_NO_BATCHED_GEMM", "1")
+    x, w, b = seeded(xshape, wshape, dtype, bias=True, seed=wshape[0])
+    out, res = run_conv(x, w, b, (1, 1), (0, 0), (1, 1))
+    assert (res.workspace_bytes == 0) == as_gemm
+    check(out, OC.conv2d_oracle(x, w, b, (1, 1), (0, 0), (1, 1)), dtype)
+    xd, wd, bd = x.to(DEV), w.to(DEV), b.to(DEV)
+    via_entry = conv2d_forward(xd, wd, bd)
+    _cabi.check_status(via_entry.device)
+    check(via_entry.cpu(), OC.conv2d_oracle(x, w, b, (1, 1), (0, 0), (1, 1)), dtype)
+
+
 @pytest.mark.parametrize("cfg", [
     dict(BLOCK_SIZE_M=128, BLOCK_SIZE_N=64, BLOCK_SIZE_K=64),
     dict(BLOCK_SIZE_M=128, BLOCK_SIZE_N=128, BLOCK_SIZE_K=128),

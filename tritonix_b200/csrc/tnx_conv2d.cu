@@ -423,6 +423,7 @@ extern "C" int tnx_conv2d_query(const tnx_conv2d_problem* problem, const tnx_con
   }
   tnx_config cfg = config ? *config : tnx_config{};
   tnx::ConvPlan plan;
+  if (tnx::conv_is_batched_gemm(*problem)) return tnx::umma_conv1x1_query(*problem, &cfg, out);
   if (tnx::folds_width(*problem)) {
     const tnx_conv2d_problem q = tnx::folded_problem(*problem);
     rc = tnx::umma_conv_query(q, &cfg, out, &plan);
@@ -525,6 +526,11 @@ extern "C" int tnx_conv2d_forward(const tnx_conv2d_problem* problem, const tnx_c
 
   tnx_config cfg = config ? *config : tnx_config{};
   tnx::ConvPlan plan;
+  if (tnx::conv_is_batched_gemm(p)) {  // 1 x 1 on NCHW tensors: one GEMM per image, nothing to repack
+    rc = tnx::umma_conv1x1_query(p, &cfg, &res);
+    if (rc != TNX_OK) return rc;
+    return tnx::umma_conv1x1_launch(p, cfg, res, input, weight, bias, output, status_word, stream);
+  }
   const bool fold = tnx::folds_width(p);
   const tnx_conv2d_problem folded = fold ? tnx::folded_problem(p) : p;
   rc = tnx::umma_conv_query(folded, &cfg, &res, &plan);

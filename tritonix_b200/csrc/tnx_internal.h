@@ -50,6 +50,15 @@ int umma_conv_launch(const tnx_conv2d_problem& p, const tnx_config& cfg,
                      const void* w, const void* bias, void* y, int32_t* status_word,
                      cudaStream_t stream);
 
+// A 1 x 1, stride-1, unpadded convolution over N x C x H x W tensors is one GEMM per image with
+// no repacking at all: out_n (C_OUT x HW) = W (C_OUT x C) . x_n (C x HW).  The kernel runs the
+// batch in one launch (3-D tensor maps over x and out).
+bool conv_is_batched_gemm(const tnx_conv2d_problem& p);
+int umma_conv1x1_query(const tnx_conv2d_problem& p, tnx_config* cfg, tnx_conv2d_resources* out);
+int umma_conv1x1_launch(const tnx_conv2d_problem& p, const tnx_config& cfg,
+                        const tnx_conv2d_resources& res, const void* x, const void* w,
+                        const void* bias, void* y, int32_t* status_word, cudaStream_t stream);
+
 int strided_query(const tnx_problem& p, tnx_config* cfg, tnx_resources* out);
 int strided_launch(const tnx_problem& p, const void* a, const void* b, void* c,
                    cudaStream_t stream);

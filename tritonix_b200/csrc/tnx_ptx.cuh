@@ -134,6 +134,34 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst_smem, const void* 
       : "memory");
 }
 
+// 3-D tiled loads / stores (column, row, matrix) for a batch of equally shaped matrices.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const void* tmap, int32_t c0,
+                                            int32_t c1, int32_t c2, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3, %4}], [%5];"
+      :
+      : "r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(c2), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst_smem, const void* tmap, int32_t c0,
+                                                 int32_t c1, int32_t c2, uint32_t leader_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3, %4}], [%5];"
+      :
+      : "r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(c2),
+        "r"(leader_bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_3d(const void* tmap, int32_t c0, int32_t c1, int32_t c2,
+                                             uint32_t src_smem) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%1, %2, %3}], [%4];"
+               :
+               : "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(c2), "r"(src_smem)
+               : "memory");
+}
+
 // 4-D tiled loads (channels, x, y, image) for the convolution path: one box of pixels x 64
 // channels per call; coordinates may be negative or past the end (zero fill = the padding).
 __device__ __forceinline__ void tma_load_4d(uint32_t dst_smem, const void* tmap, int32_t c0,

@@ -89,6 +89,11 @@ struct UmmaParams {
   int cv_taps, cv_fw;          // filter_h * filter_w, filter_w
   int cv_sh, cv_sw, cv_ph, cv_pw, cv_dh, cv_dw;
   const void* bias;            // one value per output column, of the operand type, or nullptr
+  // Batched GEMM: `batched` independent problems that share A.  B and C are 3-D tensor maps
+  // (column, row, matrix); tile row index = matrix * bt_tiles_m + row tile inside the matrix.
+  int batched;
+  int bt_tiles_m;              // row tiles (CTA pairs count as one) per matrix
+  int bias_per_row;            // the bias is indexed by the output row instead of the column
 #ifdef TNX_DEV_TRACE
   unsigned long long* trace;  // development builds only: 256 timestamp slots per CTA
 #endif
@@ -296,7 +301,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const int slice = xchg ? static_cast<int>(cluster_rank) : u - t * p.split_k;
         int tm, tn;
         tile_coords(p, t, tm, tn);
-        const int row0 = (tm * CTA_GROUP + static_cast<int>(cta_rank)) * kRowsPerCta;
+        const int bt_img = p.batched ? tm / p.bt_tiles_m : 0;  // which matrix of a batch
+        const int row0 = ((tm - bt_img * p.bt_tiles_m) * CTA_GROUP + static_cast<int>(cta_rank)) * kRowsPerCta;
         const int col0 = tn * TILE_N + static_cast<int>(cta_rank) * LOAD_N;
         const int kb0 = slice * p.kb_per_slice;
         const int kb1 = min(kb0 + p.kb_per_slice, p.num_kb);
@@ -380,6 +386,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               for (int ka = 0; ka < TILE_K / kAtomElems; ++ka)
                 ptx::tma_load_2d(b_dst + ka * (LOAD_N * kAtomBytes), &tmap_b, k0 + ka * kAtomElems,
                                  col0, full_bar);
+            } else if (p.batched) {
+#pragma unroll
+              for (int na = 0; na < LOAD_N / kAtomElems; ++na)
+                ptx::tma_load_3d(b_dst + na * (TILE_K * kAtomBytes), &tmap_b, col0 + na * kAtomElems,
+                                 k0, bt_img, full_bar);
             } else {
 #pragma unroll
               for (int na = 0; na < LOAD_N / kAtomElems; ++na)
@@ -427,6 +438,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               for (int ka = 0; ka < TILE_K / kAtomElems; ++ka)
                 ptx::tma_load_2d_pair(b_dst + ka * (LOAD_N * kAtomBytes), &tmap_b,
                                       k0 + ka * kAtomElems, col0, leader_bar);
+            } else if (p.batched) {
+#pragma unroll
+              for (int na = 0; na < LOAD_N / kAtomElems; ++na)
+                ptx::tma_load_3d_pair(b_dst + na * (TILE_K * kAtomBytes), &tmap_b,
+                                      col0 + na * kAtomElems, k0, bt_img, leader_bar);
             } else {
 #pragma unroll
               for (int na = 0; na < LOAD_N / kAtomElems; ++na)
@@ -547,7 +563,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const int slice = xchg ? static_cast<int>(cluster_rank) : u - t * p.split_k;
       int tm, tn;
       tile_coords(p, t, tm, tn);
-      const int row_tile = tm * CTA_GROUP + static_cast<int>(cta_rank);  // 128-row tile index
+      const int bt_img = p.batched ? tm / p.bt_tiles_m : 0;  // which matrix of a batch
+      // 128-row tile index (inside its matrix for a batch)
+      const int row_tile = (tm - bt_img * p.bt_tiles_m) * CTA_GROUP + static_cast<int>(cta_rank);
       const int row0 = row_tile * kRowsPerCta;
       const int acc_col0 = tn * TILE_N;        // first B column of the tile
       const int out_col0 = tn * OUT_PER_TILE;  // first C column of the tile
@@ -811,10 +829,17 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           } else {
             if (p.bias != nullptr) {
               const uint16_t* bias16 = reinterpret_cast<const uint16_t*>(p.bias);
+              if (p.bias_per_row) {
+                const int br = row0 + row_in_tile;
+                const float bv = br < p.m ? unpack1<BF16>(__ldg(bias16 + br)) : 0.f;
 #pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                const int bc = acc_col0 + col + j;
-                if (bc < p.n) v[j] += unpack1<BF16>(__ldg(bias16 + bc));
+                for (int j = 0; j < 32; ++j) v[j] += bv;
+              } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  const int bc = acc_col0 + col + j;
+                  if (bc < p.n) v[j] += unpack1<BF16>(__ldg(bias16 + bc));
+                }
               }
             }
             uint32_t o[16];
@@ -831,7 +856,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         ptx::fence_proxy_async_smem();
         ptx::named_barrier_sync(kEpiBarrier, kEpiThreads);
         if (epi_tid == 0) {
-          if (p.conv != 1) {
+          if (p.batched) {
+            ptx::tma_store_3d(&tmap_c, out_col, row0, bt_img, buf);
+          } else if (p.conv != 1) {
             ptx::tma_store_2d(&tmap_c, out_col, row0, buf);
           } else if (row_tile < p.cv_row_tiles) {  // rows are a rectangle of pixels of one image
             const int per_image = p.cv_tiles_h * p.cv_tiles_w;
@@ -1685,6 +1712,173 @@ int umma_conv_launch(const tnx_conv2d_problem& p, const tnx_config& cfg,
     kp.trace = t ? reinterpret_cast<unsigned long long*>(strtoull(t, nullptr, 0)) : nullptr;
   }
 #endif
+
+  cudaError_t e = allow_full_smem(fn);
+  if (e != cudaSuccess) {
+    set_error("cudaFuncSetAttribute(%d B dynamic smem): %s", kMaxDynamicSmem, cudaGetErrorString(e));
+    (void)cudaGetLastError();
+    return TNX_ERR_CUDA;
+  }
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = dim3(res.grid, 1, 1);
+  lc.blockDim = dim3(kThreads, 1, 1);
+  lc.dynamicSmemBytes = res.smem_bytes;
+  lc.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cfg.cta_group;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  lc.attrs = attr;
+  lc.numAttrs = 1;
+  e = cudaLaunchKernelEx(&lc, fn, ta, tb, tc, kp);
+  if (e != cudaSuccess) {
+    set_error("convolution kernel launch failed: %s", cudaGetErrorString(e));
+    (void)cudaGetLastError();
+    return TNX_ERR_CUDA;
+  }
+  return TNX_OK;
+}
+
+
+// ---------------------------------------------------------------------------------------------
+// 1 x 1 convolution over NCHW tensors = a batch of GEMMs that share the weights
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+// 3-D tensor map (column, row, matrix) over `batch` row-major matrices of 16-bit elements.
+int make_tmap_batched(CUtensorMap* out, const void* ptr, int dtype, int64_t cols, int64_t rows,
+                      int64_t batch, int box_cols, int box_rows, bool is_operand) {
+  EncodeTiledFn encode = get_encode_fn();
+  if (encode == nullptr) {
+    set_error("cuTensorMapEncodeTiled is not available from the CUDA driver");
+    return TNX_ERR_CUDA;
+  }
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows),
+                              static_cast<cuuint64_t>(batch)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(cols) * 2,
+                                 static_cast<cuuint64_t>(cols * rows) * 2};
+  const cuuint32_t box[3] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows), 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  const CUtensorMapDataType dt =
+      dtype == TNX_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = encode(out, dt, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                      is_operand ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled (3-D) failed with CUresult %d (ptr %p, %lld x %lld x %lld)",
+              static_cast<int>(r), ptr, static_cast<long long>(batch), static_cast<long long>(rows),
+              static_cast<long long>(cols));
+    return TNX_ERR_CUDA;
+  }
+  return TNX_OK;
+}
+
+// The GEMM one image amounts to: M = c_out, N = h*w, K = c_in, all row-major and dense.
+tnx_problem image_gemm(const tnx_conv2d_problem& p) {
+  tnx_problem g = {};
+  g.m = p.c_out;
+  g.n = p.h_in * p.w_in;
+  g.k = p.c_in;
+  g.dtype = p.dtype;
+  g.epilogue = TNX_EPI_NONE;
+  g.stride_am = p.c_in;
+  g.stride_ak = 1;
+  g.stride_bk = g.n;
+  g.stride_bn = 1;
+  g.stride_cm = g.n;
+  g.stride_cn = 1;
+  return g;
+}
+
+}  // namespace
+
+bool conv_is_batched_gemm(const tnx_conv2d_problem& p) {
+  if (getenv("TNX_CONV_NO_BATCHED_GEMM") != nullptr) return false;  // read every time: tests flip it
+  const long long hw = static_cast<long long>(p.h_in) * p.w_in;
+  return p.dtype != TNX_F32 && p.filter_h == 1 && p.filter_w == 1 && p.stride_h == 1 &&
+         p.stride_w == 1 && p.pad_h == 0 && p.pad_w == 0 && p.input_layout == TNX_LAYOUT_NCHW &&
+         p.output_layout == TNX_LAYOUT_NCHW && p.weight_layout == TNX_WEIGHT_KCRS && hw % 8 == 0 &&
+         hw <= 0x7fffffff && p.c_in % 8 == 0;
+}
+
+int umma_conv1x1_query(const tnx_conv2d_problem& p, tnx_config* cfg, tnx_conv2d_resources* out) {
+  const tnx_problem g = image_gemm(p);
+  if (cfg->cta_group == 0 && cfg->tile_m == 0) cfg->cta_group = p.c_out >= 256 ? 2 : 1;
+  if (cfg->tile_n == 0 && cfg->cta_group == 2 && g.n <= 64) cfg->tile_n = 128;
+  if (cfg->tile_k == 0) cfg->tile_k = p.c_in % 128 == 0 ? 128 : 64;
+  cfg->split_k = 1;
+  cfg->tile_order = TNX_ORDER_GROUPED;
+  tnx_resources r;
+  int rc = umma_query(g, cfg, &r);
+  out->kernel = TNX_KERNEL_TCGEN05;
+  out->h_out = p.h_in;
+  out->w_out = p.w_in;
+  out->tile_w = cfg->tile_n;  // here the pixels are the columns of a tile, the rows output channels
+  out->tile_h = 1;
+  out->smem_bytes = r.smem_bytes;
+  out->tmem_columns = r.tmem_columns;
+  out->workspace_bytes = 0;
+  if (rc != TNX_OK) return rc;
+  const long long units = static_cast<long long>(p.batch) * r.tiles_m * r.tiles_n;
+  if (static_cast<long long>(p.batch) * r.tiles_m > 0xffff) {
+    set_error("too many row tiles in the batch (%lld)", static_cast<long long>(p.batch) * r.tiles_m);
+    return TNX_ERR_INVALID;
+  }
+  int max_clusters = device_sm_count() / cfg->cta_group;
+  if (cfg->max_ctas > 0 && cfg->max_ctas / cfg->cta_group < max_clusters)
+    max_clusters = cfg->max_ctas / cfg->cta_group;
+  if (max_clusters < 1) max_clusters = 1;
+  out->grid = static_cast<int32_t>((units < max_clusters ? units : max_clusters) * cfg->cta_group);
+  return TNX_OK;
+}
+
+int umma_conv1x1_launch(const tnx_conv2d_problem& p, const tnx_config& cfg,
+                        const tnx_conv2d_resources& res, const void* x, const void* w,
+                        const void* bias, void* y, int32_t* status_word, cudaStream_t stream) {
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) |
+       reinterpret_cast<uintptr_t>(y)) & 15u) {
+    set_error("tcgen05 convolution needs 16-byte aligned input, weight and output buffers");
+    return TNX_ERR_INVALID;
+  }
+  const tnx_problem g = image_gemm(p);
+  KernelFn fn = pick_kernel(cfg.tile_n, cfg.tile_k, cfg.cta_group, false, p.dtype);
+  if (fn == nullptr) return TNX_ERR_NOT_BUILT;
+  const int a_rows = a_box_rows(g, cfg);
+  CUtensorMap ta, tb, tc;
+  int rc = make_tmap(&ta, w, p.dtype, g.k, g.m, g.k, kAtomElems, a_rows, true);
+  if (rc != TNX_OK) return rc;
+  rc = make_tmap_batched(&tb, x, p.dtype, g.n, g.k, p.batch, kAtomElems, cfg.tile_k, true);
+  if (rc != TNX_OK) return rc;
+  rc = make_tmap_batched(&tc, y, p.dtype, g.n, g.m, p.batch, kAtomElems, kRowsPerCta, false);
+  if (rc != TNX_OK) return rc;
+
+  const int tiles_m_img = cdiv(g.m, kRowsPerCta * cfg.cta_group);
+  UmmaParams kp = {};
+  kp.m = g.m;
+  kp.n = g.n;
+  kp.k = g.k;
+  kp.n_out = g.n;
+  kp.tiles_m = p.batch * tiles_m_img;
+  kp.tiles_n = cdiv(g.n, cfg.tile_n);
+  kp.num_kb = cdiv(g.k, cfg.tile_k);
+  kp.split_k = 1;
+  kp.kb_per_slice = kp.num_kb;
+  kp.tile_k = cfg.tile_k;
+  kp.a_rows = a_rows;
+  kp.staging_bytes = 2 * kStagingBytes;
+  kp.stages = cfg.stages;
+  kp.acc_stages = cfg.acc_stages;
+  kp.group_m = cfg.group_m;
+  kp.tile_order = TNX_ORDER_GROUPED;
+  kp.epilogue = TNX_EPI_NONE;
+  kp.status = status_word;
+  kp.timeout_ns = wait_limit_ns();
+  kp.bias = p.has_bias ? bias : nullptr;
+  kp.bias_per_row = 1;
+  kp.batched = p.batch;
+  kp.bt_tiles_m = tiles_m_img;
 
   cudaError_t e = allow_full_smem(fn);
   if (e != cudaSuccess) {

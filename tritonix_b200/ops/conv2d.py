@@ -94,7 +94,8 @@ class _Conv2dKernel:
         key = (batch, c_in, h_in, w_in, c_out, filter_h, filter_w, stride_h, stride_w, pad_h,
                pad_w, dil_h, dil_w, h_out, w_out, input.dtype, bias is not None, _layout(input),
                _layout(out), packed, tuple(sorted(cfg.items())),
-               os.environ.get("TNX_CONV_TILED"), os.environ.get("TNX_CONV_NO_FOLD"))
+               os.environ.get("TNX_CONV_TILED"), os.environ.get("TNX_CONV_NO_FOLD"),
+               os.environ.get("TNX_CONV_NO_BATCHED_GEMM"))
         plan = self._plans.get(key)
         if plan is None:
             problem = _cabi.make_conv_problem(
@@ -223,7 +224,13 @@ def conv2d_forward(input: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor
                       memory_format=torch.channels_last if channels_last
                       else torch.contiguous_format)
     extra = {}
-    if input.dtype != torch.float32:
+    # A 1 x 1, stride-1, unpadded convolution over NCHW tensors runs as one GEMM per image on the
+    # tensors as they are: nothing to repack, weights included (tnx_conv2d_forward decides by the
+    # same rule).
+    plain_gemm = (r == 1 and s == 1 and stride == (1, 1) and padding == (0, 0) and not channels_last
+                  and (h_in * w_in) % 8 == 0 and c_in % 8 == 0
+                  and os.environ.get("TNX_CONV_NO_BATCHED_GEMM") is None)
+    if input.dtype != torch.float32 and not plain_gemm:
         weight = _packed_weights(weight, lambda: _cabi.make_conv_problem(
             n, c_in, h_in, w_in, c_out, r, s, stride, padding, dilation, input.dtype,
             bias is not None))
