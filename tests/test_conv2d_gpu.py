@@ -13,6 +13,16 @@ TOL = {torch.float16: 2e-3, torch.bfloat16: 8e-3, torch.float32: 1e-5}
 DEV = "cuda"
 
 
+@pytest.fixture(autouse=True)
+def fresh_conv_caches():
+    """Tests flip the TNX_CONV_* switches, which the Python layer reads when it first sees a call
+    signature: start every test without remembered calls."""
+    from tritonix_b200.ops import conv2d as conv_module
+    conv_module.clear_caches()
+    yield
+    conv_module.clear_caches()
+
+
 def run_conv(x, w, b, stride, padding, dilation, cfg=None, channels_last=False):
     """One launch through the C ABI into a NaN-filled output."""
     xd, wd = x.to(DEV), w.to(DEV)

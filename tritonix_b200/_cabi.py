@@ -389,11 +389,15 @@ def launch_splitk_static(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor,
 _conv_workspaces: dict = {}
 
 
-def conv_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+def conv_workspace(device: torch.device, nbytes: int, stream: int | None = None) -> torch.Tensor:
     """Scratch for the repacked input, weights and output of a convolution, one per (device,
-    stream), grown on demand.  Not cleared: the library writes every byte it reads."""
+    stream), grown on demand.  Not cleared: the library writes every byte it reads.  ``stream``
+    is the raw handle of the stream the call will run on (default: torch's current one)."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
-    key = (idx, torch.cuda.current_stream(idx).cuda_stream)
+    key = (idx, torch.cuda.current_stream(idx).cuda_stream if stream is None else stream)
+    w = _conv_workspaces.get(key)
+    if w is not None and w.numel() >= nbytes:
+        return w
     with _scratch_lock:
         w = _conv_workspaces.get(key)
         if w is None or w.numel() < nbytes:
