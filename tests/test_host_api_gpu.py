@@ -26,6 +26,7 @@ def quick_tuning(monkeypatch):
     monkeypatch.setattr(tnx.TunableKernel, "tune", tune)
     mm = __import__("sys").modules["tritonix_b200.ops.matmul"]
     mm._matmul_cfg.clear()
+    mm._FAST_MATMUL.clear()
     mm._splitk_cfg.clear()
     yield
 
@@ -233,6 +234,7 @@ def test_tuned_configuration_is_persisted(tmp_path, monkeypatch):
     (key, cfg), = stored.items()
     assert key.startswith("384,640,512|torch.bfloat16|") and cfg == mm._matmul_cfg[(384, 640, 512)]
     mm._matmul_cfg.clear()
+    mm._FAST_MATMUL.clear()
 
     def no_tuning(self, *args, **kwargs):
         raise AssertionError("the stored configuration should have been used")

@@ -75,6 +75,7 @@ class DynamicDispatcher:
         self._backends: Dict[str, Callable] = {}
         self._forced: Optional[str] = None
         self.cache: Dict[tuple, str] = {}
+        self._key_memo: Dict[tuple, tuple] = {}
         self.timings: Dict[tuple, Dict[str, float]] = {}
         self.__name__ = getattr(fn, "__name__", type(fn).__name__)
         self.__doc__ = fn.__doc__
@@ -88,7 +89,22 @@ class DynamicDispatcher:
             raise RuntimeError(f"[{self.__name__}] No backends registered.")
         if self._forced is not None:
             return self._backends[self._forced](*args, **kwargs)
-        key = _tuning_key(self._key_names, args, kwargs, self._arg_names)
+        key = None
+        quick = None
+        if not kwargs:
+            # the tuning key of a positional call depends only on the tensors' shapes and dtypes
+            # and on the other arguments themselves: remember it instead of rebuilding it
+            try:
+                quick = tuple((a.shape, a.dtype) if isinstance(a, torch.Tensor) else a for a in args)
+                key = self._key_memo.get(quick)
+            except TypeError:  # an unhashable argument
+                quick = None
+        if key is None:
+            key = _tuning_key(self._key_names, args, kwargs, self._arg_names)
+            if quick is not None:
+                if len(self._key_memo) >= 4096:
+                    self._key_memo.clear()
+                self._key_memo[quick] = key
         if key not in self.cache:
             self._bench_and_cache(key, args, kwargs)
         return self._backends[self.cache[key]](*args, **kwargs)
