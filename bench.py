@@ -273,7 +273,8 @@ def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1):
     sw = sys.modules["tritonix_b200.ops.swiglu"]
     mm = sys.modules["tritonix_b200.ops.matmul"]
     mlp = TensorParallelSwiGLU(
-        w12, wd, chunks=chunks if chunks > 0 else (1 if world == 1 else 4), comm_sms=comm_sms,
+        w12, wd, chunks=chunks if (isinstance(chunks, list) or chunks > 0) else (1 if world == 1 else 4),
+        comm_sms=comm_sms,
         gate_up_cfg=GLU_CFG, down_cfg=GEMM_CFG)
     state = {}
 
@@ -440,6 +441,9 @@ def main():
     ap.add_argument("--cfg", type=str, default=None,
                     help="JSON object overriding kernel-config keys of the workload, e.g. "
                          "'{\"group_m\": 8}'")
+    ap.add_argument("--chunk-weights", default="",
+                    help="mlp: comma-separated relative sizes of the row chunks (overrides --chunks), "
+                         "e.g. 3,3,2,1 for a short last chunk")
     ap.add_argument("--chunks", type=int, default=0,
                     help="mlp: row chunks whose all-reduce overlaps the next chunk's GEMMs "
                          "(default: 1 on one GPU, 4 otherwise)")
@@ -494,7 +498,8 @@ def main():
         for base in (GEMM_CFG, SPLITK_CFG, GLU_CFG):
             base.update(override)
     if args.workload == "mlp":
-        step, e2e_step, work = setup_mlp(rank, world, dev, args.chunks, args.comm_sms)
+        chunks = [float(v) for v in args.chunk_weights.split(",")] if args.chunk_weights else args.chunks
+        step, e2e_step, work = setup_mlp(rank, world, dev, chunks, args.comm_sms)
     elif args.workload == "conv":
         step, e2e_step, work = setup_conv(rank, world, dev, json.loads(args.cfg) if args.cfg else None)
     else:

@@ -86,3 +86,23 @@ def test_two_rank_mlp_and_row_sharded_gemm(tmp_path):
     res = [torch.load(tmp_path / f"r{r}.pt") for r in range(world)]
     assert all(r["err"] < 1e-5 and r["err2"] < 1e-6 for r in res), res
     assert [r["rows"] for r in res] == [(0, 512), (512, 1024)]
+
+
+def test_weighted_chunk_bounds_cover_the_rows():
+    """chunks may be a list of relative sizes: contiguous, non-empty, 256-row aligned ranges."""
+    import torch
+    from tritonix_b200.distributed import TensorParallelSwiGLU
+    ident = dict(gate_up_fn=lambda x, w: x, down_fn=lambda h, w, out=None: h)
+    w12, wd = torch.zeros(8, 16), torch.zeros(8, 8)
+    for chunks in (4, [3, 3, 2, 1], [1, 1, 1, 1, 0.5], [5, 0, 1], [1]):
+        tp = TensorParallelSwiGLU(w12, wd, chunks=chunks, **ident)
+        for m in (32768, 4096, 1000, 300):
+            b = tp.chunk_bounds(m)
+            assert b[0][0] == 0 and b[-1][1] == m
+            assert all(b[i][1] == b[i + 1][0] for i in range(len(b) - 1))
+            assert all(hi > lo for lo, hi in b)
+            if m % 256 == 0:
+                assert all(lo % 256 == 0 for lo, _ in b)
+    tp = TensorParallelSwiGLU(w12, wd, chunks=[3, 3, 2, 1], **ident)
+    sizes = [hi - lo for lo, hi in tp.chunk_bounds(32768)]
+    assert sizes[-1] < sizes[0] and sizes[-1] == 3584

@@ -78,7 +78,7 @@ class TensorParallelSwiGLU:
     """
 
     def __init__(self, w12_shard: torch.Tensor, w_down_shard: torch.Tensor,
-                 group: Optional[dist.ProcessGroup] = None, chunks: int = 4,
+                 group: Optional[dist.ProcessGroup] = None, chunks=4,
                  gate_up_fn: Optional[Callable] = None, down_fn: Optional[Callable] = None,
                  comm_sms: Optional[int] = None, gate_up_cfg: Optional[dict] = None,
                  down_cfg: Optional[dict] = None):
@@ -87,7 +87,14 @@ class TensorParallelSwiGLU:
         self.w12 = w12_shard
         self.w_down = w_down_shard
         self.group = group
-        self.chunks = max(1, int(chunks))
+        # an int = that many equal chunks; a sequence of positive weights = chunks of those
+        # relative sizes (a small last chunk shortens the one all-reduce nothing overlaps)
+        if isinstance(chunks, (list, tuple)):
+            self.chunk_weights = [float(w) for w in chunks if float(w) > 0] or [1.0]
+            self.chunks = len(self.chunk_weights)
+        else:
+            self.chunks = max(1, int(chunks))
+            self.chunk_weights = [1.0] * self.chunks
         if comm_sms is None:  # measured on 8 B200: 32 SMs left to NCCL; not worth it on fewer ranks
             comm_sms = 32 if self.world_size >= 8 else 0
         self.comm_sms = max(0, int(comm_sms))
@@ -135,7 +142,17 @@ class TensorParallelSwiGLU:
         """Row ranges of the all-reduce chunks: multiples of 256 rows where possible."""
         n = min(self.chunks, max(1, m // 256))
         mult = 256 if m % 256 == 0 else 1
-        return [shard_bounds(m, i, n, mult) for i in range(n)]
+        if len(set(self.chunk_weights[:n])) <= 1:
+            return [shard_bounds(m, i, n, mult) for i in range(n)]
+        weights = self.chunk_weights[:n]
+        total, bounds, lo, acc = sum(weights), [], 0, 0.0
+        for i, w in enumerate(weights):
+            acc += w
+            hi = m if i == n - 1 else min(m, max(lo, int(round(m * acc / total / mult)) * mult))
+            if hi > lo:
+                bounds.append((lo, hi))
+            lo = hi
+        return bounds
 
     def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         m = x.shape[0]
