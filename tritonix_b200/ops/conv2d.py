@@ -176,17 +176,18 @@ _CANDIDATE_CONFIGS = [
 ]
 
 
-def _time_kernel(fn, iters=6, warmup=2):
-    for _ in range(warmup):
+def _time_kernel(fn, launches: int = 6) -> float:
+    """Milliseconds per launch of ``fn``: one untimed call (compilation of nothing, but first-use
+    set-up such as the shared-memory opt-in), then ``launches`` back-to-back calls between two
+    events on the current stream."""
+    fn()
+    first, last = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    first.record()
+    for _ in range(launches):
         fn()
-    start = torch.cuda.Event(enable_timing=True)
-    end = torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(iters):
-        fn()
-    end.record()
-    end.synchronize()
-    return start.elapsed_time(end) / iters
+    last.record()
+    last.synchronize()
+    return first.elapsed_time(last) / launches
 
 
 # Call signatures seen before (shapes, dtypes, devices, layout, geometry) -> a closure that goes
