@@ -272,6 +272,33 @@ def test_packed_weights_match_and_follow_updates():
     assert not torch.equal(y1, y2)
 
 
+def test_tuner_drives_the_convolution_handle():
+    """conv2d_forward_kernel.tune(launcher): the grid search walks the space under the
+    reference's key names, prunes what does not fit an SM (OutOfResources from the library's
+    resource check) and returns a configuration that computes the right numbers."""
+    x, w, b = seeded((2, 64, 20, 20), (96, 3, 3), torch.bfloat16, seed=13)
+    xd, wd, bd = x.to(DEV), w.to(DEV), b.to(DEV)
+    out = torch.empty((2, 96, 20, 20), device=DEV, dtype=torch.bfloat16)
+    seen = []
+
+    def launcher(cfg):
+        seen.append(dict(cfg))
+        conv2d_forward_kernel[(1,)](out, xd, wd, bd, 2, 64, 20, 20, 96, 20, 20, 3, 3, 1, 1, 1, 1,
+                                    1, 1, **cfg)
+
+    best = conv2d_forward_kernel.tune(launcher, max_configs=24, warmup=1, rep=3)
+    _cabi.check_status(out.device)
+    assert best is not None and set(best) == set(conv2d_forward_kernel.space)
+    assert 1 <= len(seen) and all(c["BLOCK_SIZE_M"] in (128, 256) for c in seen)
+    out.fill_(float("nan"))
+    launcher(best)
+    _cabi.check_status(out.device)
+    check(out.cpu(), OC.conv2d_oracle(x, w, b, (1, 1), (1, 1), (1, 1)), torch.bfloat16)
+    # a ring that cannot fit is reported the way the tuner expects
+    with pytest.raises(_cabi.OutOfResources):
+        launcher(dict(BLOCK_SIZE_M=128, BLOCK_SIZE_N=256, BLOCK_SIZE_K=128, GROUP_SIZE_M=8, num_stages=8))
+
+
 def test_torch_custom_op_and_fake_kernel():
     import tritonix_b200  # noqa: F401  (registers torch.ops.tritonix.*)
     from torch._subclasses.fake_tensor import FakeTensorMode
