@@ -271,6 +271,12 @@ inline long long folded_input_bytes(const tnx_conv2d_problem& p) {
                     ((p.c_in * p.filter_w + 7) / 8 * 8) * 2);
 }
 
+inline int grid_for(long long total);
+
+// N x H_OUT x W_OUT x c_out_pitch (what the kernel wrote) -> the caller's output tensor.
+int repack_output16(const tnx_conv2d_problem& p, const void* y, void* output, long long out_pixels,
+                    int c_out_pitch, cudaStream_t stream);
+
 inline int grid_for(long long total) {
   long long blocks = (total + 255) / 256;
   return static_cast<int>(blocks < 1 ? 1 : (blocks > 148 * 16 ? 148 * 16 : blocks));
@@ -350,6 +356,22 @@ conv2d_direct_f32_kernel(const DirectGeom g, const float* __restrict__ x, const 
       y[img * g.out_sn + n * g.out_sc + ho * g.out_sh + wo * g.out_sw] = v;
     }
   }
+}
+
+int repack_output16(const tnx_conv2d_problem& p, const void* y, void* output, long long out_pixels,
+                    int c_out_pitch, cudaStream_t stream) {
+  if (p.output_layout == TNX_LAYOUT_NCHW)
+    return launch_transpose16(y, output, p.batch, static_cast<int>(out_pixels), p.c_out, c_out_pitch,
+                              out_pixels, out_pixels * c_out_pitch, out_pixels * p.c_out, stream);
+  const long long px = out_pixels * p.batch;
+  unpad_channels16_kernel<<<grid_for(px * p.c_out), 256, 0, stream>>>(
+      static_cast<const uint16_t*>(y), static_cast<uint16_t*>(output), px, p.c_out, c_out_pitch);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("repacking kernel launch failed: %s", cudaGetErrorString(e));
+    return TNX_ERR_CUDA;
+  }
+  return TNX_OK;
 }
 
 int validate_conv(const tnx_conv2d_problem* p) {
@@ -579,24 +601,8 @@ extern "C" int tnx_conv2d_forward(const tnx_conv2d_problem* problem, const tnx_c
     void* yf = plan.repack_output ? static_cast<void*>(ws + plan.off_output) : output;
     rc = tnx::umma_conv_launch(folded, cfg, res, plan, xf, w_packed, bias, yf, status_word, stream);
     if (rc != TNX_OK) return rc;
-    if (plan.repack_output) {
-      if (p.output_layout == TNX_LAYOUT_NCHW) {
-        rc = tnx::launch_transpose16(yf, output, p.batch, static_cast<int>(out_pixels), p.c_out,
-                                     plan.c_out_pitch, out_pixels, out_pixels * plan.c_out_pitch,
-                                     out_pixels * p.c_out, stream);
-        if (rc != TNX_OK) return rc;
-      } else {
-        const long long px = out_pixels * p.batch;
-        tnx::unpad_channels16_kernel<<<tnx::grid_for(px * p.c_out), 256, 0, stream>>>(
-            static_cast<const uint16_t*>(yf), static_cast<uint16_t*>(output), px, p.c_out,
-            plan.c_out_pitch);
-        fe = cudaGetLastError();
-        if (fe != cudaSuccess) {
-          tnx::set_error("repacking kernel launch failed: %s", cudaGetErrorString(fe));
-          return TNX_ERR_CUDA;
-        }
-      }
-    }
+    if (plan.repack_output)
+      return tnx::repack_output16(p, yf, output, out_pixels, plan.c_out_pitch, stream);
     return TNX_OK;
   }
 
@@ -637,23 +643,7 @@ extern "C" int tnx_conv2d_forward(const tnx_conv2d_problem* problem, const tnx_c
   rc = tnx::umma_conv_launch(p, cfg, res, plan, x, w_packed, bias, y, status_word, stream);
   if (rc != TNX_OK) return rc;
   // 4. output in the layout the caller wants
-  if (plan.repack_output) {
-    if (p.output_layout == TNX_LAYOUT_NCHW) {
-      rc = tnx::launch_transpose16(y, output, p.batch, static_cast<int>(out_pixels), p.c_out,
-                                   plan.c_out_pitch, out_pixels, out_pixels * plan.c_out_pitch,
-                                   out_pixels * p.c_out, stream);
-      if (rc != TNX_OK) return rc;
-    } else {
-      const long long px = out_pixels * p.batch;
-      tnx::unpad_channels16_kernel<<<tnx::grid_for(px * p.c_out), 256, 0, stream>>>(
-          static_cast<const uint16_t*>(y), static_cast<uint16_t*>(output), px, p.c_out,
-          plan.c_out_pitch);
-      e = cudaGetLastError();
-      if (e != cudaSuccess) {
-        tnx::set_error("repacking kernel launch failed: %s", cudaGetErrorString(e));
-        return TNX_ERR_CUDA;
-      }
-    }
-  }
+  if (plan.repack_output)
+    return tnx::repack_output16(p, y, output, out_pixels, plan.c_out_pitch, stream);
   return TNX_OK;
 }
