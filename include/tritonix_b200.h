@@ -235,7 +235,7 @@ typedef struct tnx_conv2d_resources {
 } tnx_conv2d_resources;
 
 /* Output geometry, kernel family, resources and the workspace the caller must provide.
- * `config` may be NULL; only tile_n, tile_k, stages, cta_group, group_m and max_ctas are used. */
+XX
 int tnx_conv2d_query(const tnx_conv2d_problem* problem, const tnx_config* config,
                      tnx_conv2d_resources* out);
 
