@@ -235,7 +235,8 @@ typedef struct tnx_conv2d_resources {
 } tnx_conv2d_resources;
 
 /* Output geometry, kernel family, resources and the workspace the caller must provide.
-XX
+ * `config` may be NULL; only tile_m (128 or 256 rows = one CTA or a CTA pair), tile_n, tile_k,
+ * stages, cta_group, group_m and max_ctas are used. */
 int tnx_conv2d_query(const tnx_conv2d_problem* problem, const tnx_config* config,
                      tnx_conv2d_resources* out);
 
