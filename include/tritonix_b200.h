@@ -265,6 +265,10 @@ int tnx_conv2d_pack_weights(const tnx_conv2d_problem* problem, const void* weigh
  *   filter_w * c_in <= 64 are repacked so that the taps of a filter row become channels
  *   (N x H x W_OUT x filter_w*c_in), which shortens K filter_w-fold; TNX_CONV_NO_FOLD in the
  *   environment keeps one zero-padded 64-channel block per tap instead.
+ *   Stride-1 layers with c_in <= 64 and c_out <= 64 whose output rows (plus the filter's halo
+ *   columns) have at most 128 pixels keep the weights of all taps in shared memory and load each
+ *   tile's input patch once, every tap multiplying a shifted window of it (TNX_CONV_NO_HALO in
+ *   the environment disables this).
  *   A 1 x 1, stride-1, unpadded convolution with NCHW input and output, unpacked weights and
  *   h_in*w_in and c_in multiples of 8 runs as one GEMM per image on the tensors as they are (one
  *   launch for the batch, no workspace); TNX_CONV_NO_BATCHED_GEMM in the environment disables it.

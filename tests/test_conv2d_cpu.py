@@ -97,7 +97,30 @@ def test_pointwise_nchw_needs_no_workspace(monkeypatch):
     assert res.workspace_bytes > 0
 
 
+def test_halo_tiles_for_layers_with_few_output_channels(monkeypatch):
+    res, _ = query((1, 64, 56, 56), (64, 3, 3), padding=(1, 1))
+    assert (res.tile_w, res.tile_h) == (58, 2)            # full rows plus the halo columns
+    res, _ = query((1, 64, 28, 28), (32, 3, 3), padding=(1, 1), dilation=(1, 2))
+    assert (res.tile_w, res.tile_h) == (26 + 4, 4)
+    # not for strided or wide layers, more than 64 input or output channels, K steps of 128 or
+    # CTA pairs
+    for kw in (dict(stride=(2, 2)), dict(xshape=(1, 64, 8, 200)), dict(wshape=(128, 3, 3)),
+               dict(xshape=(1, 128, 56, 56)), dict(cfg=dict(tile_n=64, tile_k=128)),
+               dict(cfg=dict(tile_m=256, tile_n=128))):
+        kw = dict(kw)
+        res, _ = query(kw.pop("xshape", (1, 64, 56, 56)), kw.pop("wshape", (64, 3, 3)),
+                       padding=(1, 1), **kw)
+        assert (res.tile_w, res.tile_h) == (128, 1)
+    # 5 x 5 filters: the weights of 25 taps do not fit in shared memory next to two patches
+    res, _ = query((1, 64, 56, 56), (64, 5, 5), padding=(2, 2))
+    assert (res.tile_w, res.tile_h) == (128, 1)
+    monkeypatch.setenv("TNX_CONV_NO_HALO", "1")
+    res, _ = query((1, 64, 56, 56), (64, 3, 3), padding=(1, 1))
+    assert (res.tile_w, res.tile_h) == (128, 1)
+
+
 def test_rectangular_tiles_when_im2col_boxes_cannot_be_used(monkeypatch):
+    monkeypatch.setenv("TNX_CONV_NO_HALO", "1")
     res, _ = query((1, 64, 56, 56), (64, 3, 3), padding=(1, 1))
     assert (res.tile_w, res.tile_h) == (128, 1)
     monkeypatch.setenv("TNX_CONV_TILED", "1")

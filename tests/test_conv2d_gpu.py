@@ -92,13 +92,17 @@ GEOMS = [
 ]
 
 
-@pytest.fixture(params=["im2col", "tiled"])
+@pytest.fixture(params=["default", "im2col", "tiled"])
 def box_mode(request, monkeypatch):
-    """Both ways of fetching the pixels of a tile: im2col-mode boxes (default) and rectangles."""
+    """The ways the kernel fetches input pixels: the library's own choice (a halo patch per
+    channel block for layers of at most 64 output channels where it applies, else one im2col-mode
+    box per tap), im2col-mode boxes everywhere, rectangular tiled boxes everywhere."""
+    monkeypatch.delenv("TNX_CONV_TILED", raising=False)
+    monkeypatch.delenv("TNX_CONV_NO_HALO", raising=False)
+    if request.param != "default":
+        monkeypatch.setenv("TNX_CONV_NO_HALO", "1")
     if request.param == "tiled":
         monkeypatch.setenv("TNX_CONV_TILED", "1")
-    else:
-        monkeypatch.delenv("TNX_CONV_TILED", raising=False)
     return request.param
 
 
@@ -177,7 +181,7 @@ def test_pointwise_on_nchw_is_a_batch_of_gemms(geom, dtype, as_gemm, monkeypatch
 def test_configurations(cfg, box_mode):
     x, w, b = seeded((2, 192, 30, 30), (320, 3, 3), torch.bfloat16, seed=11)
     out, res = run_conv(x, w, b, (1, 1), (1, 1), (1, 1), cfg)
-    assert (res.tile_w, res.tile_h) == ((128, 1) if box_mode == "im2col" else (30, 4))
+    assert (res.tile_w, res.tile_h) == ((30, 4) if box_mode == "tiled" else (128, 1))
     check(out, OC.conv2d_oracle(x, w, b, (1, 1), (1, 1), (1, 1)), torch.bfloat16)
 
 
@@ -237,6 +241,36 @@ def test_linearity_at_full_size():
     # exact whenever they stay below 256 in magnitude; compare in fp32 with the bf16 tolerance
     err = OC.rel_err(y12.float().cpu(), (y1.float() + y2.float()).cpu())
     assert err <= 8e-3
+
+
+HALO = [
+    # xshape, (c_out, r, s), padding, dilation  (stride 1, at most 64 input and 64 output channels)
+    ((2, 64, 56, 56), (64, 3, 3), (1, 1), (1, 1)),     # 58-pixel patch rows, 2 output rows per tile
+    ((3, 48, 28, 28), (48, 3, 3), (1, 1), (1, 1)),     # 30-pixel rows, 4 per tile, ragged channels
+    ((1, 40, 33, 21), (24, 3, 2), (2, 0), (1, 3)),     # 3x2 filter, dilated columns, ragged rows
+    ((2, 64, 12, 126), (32, 3, 3), (1, 1), (1, 1)),    # patch rows of exactly 128 pixels
+    ((5, 24, 9, 9), (64, 2, 2), (0, 0), (1, 1)),       # even filter, no padding, many tiles per CTA
+    ((1, 56, 7, 7), (8, 3, 3), (1, 1), (2, 2)),        # dilated 3x3 on a 7x7 image
+    ((40, 32, 20, 20), (16, 3, 3), (1, 1), (1, 1)),    # 160 tiles: every CTA reuses its resident weights
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("geom", HALO)
+def test_halo_patch_variant(geom, dtype, monkeypatch):
+    """Layers of at most 64 output channels: one patch load per channel block, every tap a
+    shifted window of it.  Same numbers as one load per tap (TNX_CONV_NO_HALO)."""
+    xshape, wshape, padding, dilation = geom
+    x, w, b = seeded(xshape, wshape, dtype, bias=True, seed=wshape[0] + xshape[1])
+    ref = OC.conv2d_oracle(x, w, b, (1, 1), padding, dilation)
+    out, res = run_conv(x, w, b, (1, 1), padding, dilation)
+    halo_w = ref.shape[3] + (wshape[2] - 1) * dilation[1]
+    assert res.tile_w == halo_w and res.tile_h == min(128 // halo_w, ref.shape[2])
+    check(out, ref, dtype)
+    monkeypatch.setenv("TNX_CONV_NO_HALO", "1")
+    per_tap, res2 = run_conv(x, w, b, (1, 1), padding, dilation)
+    assert (res2.tile_w, res2.tile_h) == (128, 1)
+    check(per_tap, ref, dtype)
 
 
 def test_wide_padding_uses_rectangles():

@@ -40,6 +40,10 @@ struct ConvPlan {
   int c_out_pitch;           // channels per pixel of the N x H x W x C output the kernel writes
   bool repack_input, repack_output;
   bool im2col;               // tiles are 128 consecutive pixels fetched with im2col-mode boxes
+  bool halo;                 // tiles are full output rows (plus the filter's halo columns); a stage is
+                             // one channel block's input patch + its weights for all taps
+  int patch_h;               // halo: input rows per patch = tile_h + (filter_h - 1) * dil_h
+  int patch_rows;            // halo: shared-memory rows per patch (multiple of 8)
   int64_t off_input, off_weight, off_output, workspace_bytes;
 };
 int umma_conv_query(const tnx_conv2d_problem& p, tnx_config* cfg, tnx_conv2d_resources* out,

@@ -24,6 +24,7 @@
 
 #include <string.h>
 
+#include <algorithm>
 #include <mutex>
 #include <utility>
 #include <vector>
@@ -80,7 +81,11 @@ struct UmmaParams {
   // Convolution (implicit GEMM): the rows of a CTA's tile are a cv_tw x cv_th rectangle of output
   // pixels of one image, A comes from an N x H x W x C tensor through a 4-D tensor map, and K
   // runs over (filter tap, 64-channel block).
-  int conv;                    // 1: rectangles of pixels (tiled boxes); 2: 128 consecutive pixels (im2col boxes)
+  int conv;                    // 1: rectangles of pixels (tiled boxes); 2: 128 consecutive pixels (im2col boxes);
+                               // 3: full-width rectangles, at most 64 input and 64 output channels: a stage =
+                               //    the tile's input patch with its halo, the weights of all taps stay in
+                               //    shared memory, each tap multiplies a row-shifted window of the patch
+  int a_box_bytes;             // conv == 3: bytes one patch load delivers
   int cv_wout, cv_hout;        // output image size
   int cv_tw, cv_th;            // output pixels per CTA tile (cv_tw * cv_th = a_rows)
   int cv_tiles_w, cv_tiles_h;  // CTA tiles per image
@@ -230,10 +235,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   // rows >= M, which are never written out.
   const int a_stage_bytes = p.a_rows * TILE_K * 2;
   const int a_atom_bytes = p.a_rows * kAtomBytes;  // one 64-element K slab of the A stage
-  const int b_stage_bytes = LOAD_N * TILE_K * 2;
+  const bool halo = CTA_GROUP == 1 && p.conv == 3;
+  const int b_stage_bytes = halo ? p.cv_taps * LOAD_N * kAtomBytes : LOAD_N * TILE_K * 2;
   const uint32_t smem_a = base_addr;
   const uint32_t smem_b = smem_a + p.stages * a_stage_bytes;
-  const uint32_t smem_out = smem_b + p.stages * b_stage_bytes;  // 2 staging buffers
+  // (halo convolution: the weights are loaded once per CTA and stay put: one B buffer, not a ring)
+  const uint32_t smem_out = smem_b + (halo ? 1 : p.stages) * b_stage_bytes;  // 2 staging buffers
   Ctrl* ctrl = reinterpret_cast<Ctrl*>(base_ptr + (smem_out - base_addr) + p.staging_bytes);
 
   const int warp = threadIdx.x >> 5;
@@ -294,7 +301,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      const uint32_t stage_tx = static_cast<uint32_t>(a_stage_bytes + b_stage_bytes) * CTA_GROUP;
+      const uint32_t stage_tx =
+          halo ? static_cast<uint32_t>(p.a_box_bytes)
+               : static_cast<uint32_t>(a_stage_bytes + b_stage_bytes) * CTA_GROUP;
+      bool weights_resident = false;  // halo convolution: this CTA's copy of the weights is in place
       bool ok = true;
       for (int u = cluster_id; u < total_units && ok; u += num_clusters) {
         const int t = xchg ? u : u / p.split_k;
@@ -345,8 +355,23 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const uint32_t b_dst = smem_b + stage * b_stage_bytes;
           const int k0 = kb * TILE_K;
           if (CTA_GROUP == 1) {
-            ptx::mbar_arrive_expect_tx(full_bar, stage_tx);
-            if (p.conv) {  // one box of pixels x 64 channels per (tap, channel block)
+            ptx::mbar_arrive_expect_tx(
+                full_bar, stage_tx + (halo && !weights_resident ? static_cast<uint32_t>(b_stage_bytes) : 0u));
+            if (halo) {
+              // The stage is the tile's input patch (tile rows + halo rows, full width with halo
+              // columns; one channel block).  The first stage of this CTA also brings the weights
+              // of every tap, which then stay in shared memory for all its tiles.
+              const int row_tile = tm;
+              const int img = row_tile / p.cv_tiles_h;
+              const int y0 = (row_tile - img * p.cv_tiles_h) * p.cv_th - p.cv_ph;
+              ptx::tma_load_4d(a_dst, &tmap_a, 0, -p.cv_pw, y0, img, full_bar);
+              if (!weights_resident) {
+                for (int tap = 0; tap < p.cv_taps; ++tap)
+                  ptx::tma_load_2d(smem_b + tap * (LOAD_N * kAtomBytes), &tmap_b, tap * kAtomElems,
+                                   col0, full_bar);
+                weights_resident = true;
+              }
+            } else if (p.conv) {  // one box of pixels x 64 channels per (tap, channel block)
 #pragma unroll
               for (int ka = 0; ka < TILE_K / kAtomElems; ++ka) {
                 // (past the last tap, in the second half of an odd last K block, a channel
@@ -381,7 +406,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 ptx::tma_load_2d(a_dst + ka * a_atom_bytes, &tmap_a, k0 + ka * kAtomElems, row0,
                                  full_bar);
             }
-            if (p.b_kmajor) {
+            if (halo) {
+              // (the weights of this channel block were issued with its patch)
+            } else if (p.b_kmajor) {
 #pragma unroll
               for (int ka = 0; ka < TILE_K / kAtomElems; ++ka)
                 ptx::tma_load_2d(b_dst + ka * (LOAD_N * kAtomBytes), &tmap_b, k0 + ka * kAtomElems,
@@ -510,17 +537,38 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           ptx::tc_fence_after_sync();
           if (u == cluster_id) TNX_TRACE(128 + (kb - kb0));
           const uint32_t a_src = smem_a + stage * a_stage_bytes;
-          const uint32_t b_src = smem_b + stage * b_stage_bytes;
+          const uint32_t b_src = smem_b + (halo ? 0 : stage * b_stage_bytes);
           const uint32_t a16 = a_src >> 4, b16 = b_src >> 4;  // descriptor addresses count 16 B
+          if (halo) {
+            // Every tap multiplies the window of the patch that starts (tap row * patch width +
+            // tap column) pixel rows further down: the 128B swizzle is a function of the
+            // shared-memory address, so a row-shifted start needs no re-layout.
+            const int fh = p.cv_taps / p.cv_fw;
+            int tap = 0;
+            for (int fr = 0; fr < fh; ++fr) {
+              for (int fs = 0; fs < p.cv_fw; ++fs, ++tap) {
+                // one pixel row of the patch = 128 B = 8 descriptor units
+                const uint32_t win16 = a16 + static_cast<uint32_t>(fr * p.cv_dh * p.cv_tw + fs * p.cv_dw) * 8u;
+                const uint32_t wgt16 = b16 + static_cast<uint32_t>(tap) * (LOAD_N * kAtomBytes / 16);
 #pragma unroll
-          for (int k16 = 0; k16 < TILE_K / 16; ++k16) {
-            // K step = (k16 / 4) slabs of 64 elements + (k16 % 4) steps of 16 inside a slab
-            const uint32_t a_off = a16 + (k16 >> 2) * a_slab16 + (k16 & 3) * a_step16;
-            const uint32_t b_off = b16 + (k16 >> 2) * b_slab16 + (k16 & 3) * b_step16;
-            // (in a cluster launch the shared-window address carries the CTA rank above bit 18)
-            ptx::umma_f16<CTA_GROUP>(d_tmem, a_desc_hi | (a_off & 0x3fffu), b_desc_hi | (b_off & 0x3fffu),
-                                     idesc, accumulate);
-            accumulate = 1;
+                for (int k16 = 0; k16 < 4; ++k16) {
+                  ptx::umma_f16<CTA_GROUP>(d_tmem, a_desc_hi | ((win16 + k16 * 2u) & 0x3fffu),
+                                           b_desc_hi | ((wgt16 + k16 * 2u) & 0x3fffu), idesc, accumulate);
+                  accumulate = 1;
+                }
+              }
+            }
+          } else {
+#pragma unroll
+            for (int k16 = 0; k16 < TILE_K / 16; ++k16) {
+              // K step = (k16 / 4) slabs of 64 elements + (k16 % 4) steps of 16 inside a slab
+              const uint32_t a_off = a16 + (k16 >> 2) * a_slab16 + (k16 & 3) * a_step16;
+              const uint32_t b_off = b16 + (k16 >> 2) * b_slab16 + (k16 & 3) * b_step16;
+              // (in a cluster launch the shared-window address carries the CTA rank above bit 18)
+              ptx::umma_f16<CTA_GROUP>(d_tmem, a_desc_hi | (a_off & 0x3fffu),
+                                       b_desc_hi | (b_off & 0x3fffu), idesc, accumulate);
+              accumulate = 1;
+            }
           }
           // Frees this ring slot (in both CTAs of a pair) once the MMAs above have read it.
           if (CTA_GROUP == 1)
@@ -858,7 +906,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (epi_tid == 0) {
           if (p.batched) {
             ptx::tma_store_3d(&tmap_c, out_col, row0, bt_img, buf);
-          } else if (p.conv != 1) {
+          } else if (p.conv != 1 && p.conv != 3) {
             ptx::tma_store_2d(&tmap_c, out_col, row0, buf);
           } else if (row_tile < p.cv_row_tiles) {  // rows are a rectangle of pixels of one image
             const int per_image = p.cv_tiles_h * p.cv_tiles_w;
@@ -1529,9 +1577,40 @@ int umma_conv_query(const tnx_conv2d_problem& p, tnx_config* cfg, tnx_conv2d_res
               p.stride_h, p.stride_w);
     return TNX_ERR_INVALID;
   }
-  plan->im2col = im2col_usable(p);
+  // Shallow layers (at most 64 input and 64 output channels) are bound by re-reading the input
+  // once per filter tap and the weights once per tile; for them (stride 1, rows of at most 128
+  // pixels with the halo) the weights of all taps stay in shared memory, a stage is one tile's
+  // input patch, and every tap multiplies a shifted window of the patch.
+  const int taps = p.filter_h * p.filter_w;
+  const int halo_w = w_out + (p.filter_w - 1) * p.dil_w;
+  const int halo_th = halo_w <= kRowsPerCta ? std::min(kRowsPerCta / halo_w, h_out) : 0;
+  const int halo_ph = halo_th + (p.filter_h - 1) * p.dil_h;
+  const long long halo_rows = (static_cast<long long>(halo_w) * halo_ph + 7) / 8 * 8;
+  const long long halo_weights = static_cast<long long>(taps) * 64 * kAtomBytes;
+  const long long halo_stage = halo_rows * kAtomBytes;
+  plan->halo = getenv("TNX_CONV_NO_HALO") == nullptr && p.stride_h == 1 && p.stride_w == 1 &&
+               taps > 1 && p.c_in <= kAtomElems && p.c_out <= 64 && p.input_layout >= 0 &&
+               halo_w <= kRowsPerCta && halo_ph <= 256 &&
+               (cfg->cta_group == 0 || cfg->cta_group == 1) &&
+               (cfg->tile_m == 0 || cfg->tile_m == kRowsPerCta) &&
+               (cfg->tile_n == 64 || (cfg->tile_n == 0 && p.c_out <= 64)) &&
+               (cfg->tile_k == 0 || cfg->tile_k == kAtomElems) &&
+               2 * halo_stage + halo_weights + 2 * kStagingBytes + kCtrlBytes + kAlignSlack <=
+                   kMaxDynamicSmem;
+  plan->patch_h = plan->halo ? halo_ph : 0;
+  plan->patch_rows = plan->halo ? static_cast<int>(halo_rows) : 0;
+  plan->im2col = !plan->halo && im2col_usable(p);
   long long row_tiles;
-  if (plan->im2col) {  // a tile = 128 consecutive pixels in (image, row, column) order
+  if (plan->halo) {
+    plan->tile_w = halo_w;
+    plan->tile_h = halo_th;
+    plan->tiles_w = 1;
+    plan->tiles_h = cdiv(h_out, halo_th);
+    row_tiles = static_cast<long long>(p.batch) * plan->tiles_h;
+    cfg->cta_group = 1;
+    cfg->tile_n = 64;
+    cfg->tile_k = kAtomElems;
+  } else if (plan->im2col) {  // a tile = 128 consecutive pixels in (image, row, column) order
     plan->tile_w = kRowsPerCta;
     plan->tile_h = 1;
     plan->tiles_w = plan->tiles_h = 0;
@@ -1547,7 +1626,7 @@ int umma_conv_query(const tnx_conv2d_problem& p, tnx_config* cfg, tnx_conv2d_res
     return TNX_ERR_INVALID;
   }
   plan->row_tiles = static_cast<int>(row_tiles);
-  const int a_rows = plan->tile_w * plan->tile_h;
+  const int a_rows = plan->halo ? plan->patch_rows : plan->tile_w * plan->tile_h;
 
   // Workspace: the kernel reads N x H x W x C with C a multiple of 8 and writes the same way.
   plan->repack_input = !(p.input_layout == TNX_LAYOUT_NHWC && p.c_in % 8 == 0);
@@ -1597,8 +1676,10 @@ int umma_conv_query(const tnx_conv2d_problem& p, tnx_config* cfg, tnx_conv2d_res
     return TNX_ERR_NOT_BUILT;
   }
   const int load_n = cfg->tile_n / cfg->cta_group;
-  const int stage_bytes = (a_rows + load_n) * cfg->tile_k * 2;
-  const int fixed = 2 * kStagingBytes + kCtrlBytes + kAlignSlack;
+  // (halo: the ring holds patches only; the weights of all taps are one more, fixed, buffer)
+  const int stage_bytes = plan->halo ? a_rows * kAtomBytes : (a_rows + load_n) * cfg->tile_k * 2;
+  const int fixed = 2 * kStagingBytes + kCtrlBytes + kAlignSlack +
+                    (plan->halo ? taps * load_n * kAtomBytes : 0);
   if (cfg->stages == 0) {
     int s = (kMaxDynamicSmem - fixed) / stage_bytes;
     cfg->stages = s > 8 ? 8 : s;
@@ -1647,9 +1728,12 @@ int umma_conv_launch(const tnx_conv2d_problem& p, const tnx_config& cfg,
   }
   KernelFn fn = pick_kernel(cfg.tile_n, cfg.tile_k, cfg.cta_group, false, p.dtype);
   if (fn == nullptr) return TNX_ERR_NOT_BUILT;
-  const int a_rows = plan.tile_w * plan.tile_h;
+  const int a_rows = plan.halo ? plan.patch_rows : plan.tile_w * plan.tile_h;
   CUtensorMap ta, tb, tc;
-  int rc = plan.im2col
+  int rc = plan.halo
+               ? make_tmap_nhwc(&ta, x, p.dtype, plan.c_pitch, p.w_in, p.h_in, p.batch, plan.tile_w,
+                                plan.patch_h, 1, 1, true)
+           : plan.im2col
                ? make_tmap_im2col(&ta, x, p, plan.c_pitch)
                : make_tmap_nhwc(&ta, x, p.dtype, plan.c_pitch, p.w_in, p.h_in, p.batch,
                                 (plan.tile_w - 1) * p.stride_w + 1,
@@ -1688,7 +1772,12 @@ int umma_conv_launch(const tnx_conv2d_problem& p, const tnx_config& cfg,
   kp.epilogue = TNX_EPI_NONE;
   kp.status = status_word;
   kp.timeout_ns = wait_limit_ns();
-  kp.conv = plan.im2col ? 2 : 1;
+  kp.conv = plan.halo ? 3 : (plan.im2col ? 2 : 1);
+  if (plan.halo) {  // K blocks are channel blocks; the taps are walked inside a stage
+    kp.num_kb = plan.cblocks;
+    kp.kb_per_slice = plan.cblocks;
+    kp.a_box_bytes = plan.tile_w * plan.patch_h * kAtomBytes;
+  }
   kp.cv_wout = plan.w_out;
   kp.cv_hout = plan.h_out;
   kp.cv_tw = plan.tile_w;

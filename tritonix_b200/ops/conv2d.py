@@ -103,7 +103,7 @@ class _Conv2dKernel:
                pad_w, dil_h, dil_w, h_out, w_out, input.dtype, bias is not None, _layout(input),
                _layout(out), packed, tuple(sorted(cfg.items())),
                os.environ.get("TNX_CONV_TILED"), os.environ.get("TNX_CONV_NO_FOLD"),
-               os.environ.get("TNX_CONV_NO_BATCHED_GEMM"))
+               os.environ.get("TNX_CONV_NO_BATCHED_GEMM"), os.environ.get("TNX_CONV_NO_HALO"))
         plan = self._plans.get(key)
         if plan is None:
             problem = _cabi.make_conv_problem(
