@@ -359,3 +359,34 @@ def test_errors():
     with pytest.raises(ValueError):
         conv2d_forward(x, torch.zeros(8, 8, 3, 3, device=DEV, dtype=torch.float16),
                        config=dict(BLOCK_SIZE_M=64))
+
+
+def test_strided_view_does_not_reuse_a_prepared_channels_last_call():
+    """A prepared call is keyed by the input's strides: after a channels_last call, an arbitrary
+    strided view of the same shape must be rejected (as the general path does), not read as
+    dense N x H x W x C memory."""
+    x, w, b = seeded((2, 32, 12, 12), (24, 3, 3), torch.float16, seed=21)
+    xd, wd, bd = x.to(DEV), w.to(DEV), b.to(DEV)
+    cl = xd.contiguous(memory_format=torch.channels_last)
+    y1 = conv2d_forward(cl, wd, bd, padding=1)
+    y2 = conv2d_forward(cl, wd, bd, padding=1)      # prepared call
+    assert torch.equal(y1, y2)
+    wide = torch.zeros(2, 32, 12, 16, device=DEV, dtype=torch.float16)
+    view = wide[..., :12]
+    view.copy_(xd)
+    assert view.shape == cl.shape and not view.is_contiguous()
+    with pytest.raises(ValueError, match="contiguous"):
+        conv2d_forward(view, wd, bd, padding=1)
+    y3 = conv2d_forward(view.contiguous(), wd, bd, padding=1)
+    _cabi.check_status(y3.device)
+    check(y3.cpu(), OC.conv2d_oracle(x, w, b, (1, 1), (1, 1), (1, 1)), torch.float16)
+
+
+def test_weights_written_through_data_need_the_static_switch():
+    x, w, b = seeded((2, 48, 16, 16), (40, 3, 3), torch.float16, seed=8)
+    xd, wd, bd = x.to(DEV), w.to(DEV), b.to(DEV)
+    conv2d_forward(xd, wd, bd, padding=1)
+    wd.data.copy_((w * 3.0).to(DEV))               # does not move the version counter
+    y = conv2d_forward(xd, wd, bd, padding=1, weights_static=False)
+    _cabi.check_status(y.device)
+    check(y.cpu(), OC.conv2d_oracle(x, w * 3.0, b, (1, 1), (1, 1), (1, 1)), torch.float16)

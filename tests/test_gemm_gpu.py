@@ -191,3 +191,28 @@ def test_invalid_launches_raise():
         _cabi.launch(a, b, c, {"tile_n": 256, "stages": 9})
     with pytest.raises(ValueError):
         _cabi.launch(a[:, 1:], b[1:], c, T)  # misaligned base address for TMA
+
+
+def test_auto_kernel_takes_views_at_odd_offsets():
+    """With the kernel family left open, a view whose storage offset is not a multiple of 16
+    bytes runs on the strided kernel (the reference accepts any pointer,
+    tritonix/ops/matmul.py:50-55); forcing the tcgen05 family on it is an error."""
+    import tritonix_b200 as tnx
+    g = torch.Generator().manual_seed(11)
+    big = torch.randn(256, 520, generator=g).to(bf16)
+    b_cpu = (torch.randn(512, 256, generator=g) / 512 ** 0.5).to(bf16)
+    big_d, b = big.to(DEV), b_cpu.to(DEV)
+    view = big_d[:, 4:516]                      # 8-byte offset, pitch 520 elements (16-byte multiple)
+    assert view.data_ptr() % 16 == 8
+    ref = O.matmul_oracle(big[:, 4:516], b_cpu)
+    c = torch.full((256, 256), float("nan"), device=DEV, dtype=bf16)
+    res = _cabi.launch(view, b, c)
+    _cabi.check_status(c.device)
+    assert_close(c.cpu(), ref, bf16)
+    with pytest.raises(ValueError, match="16-byte aligned"):
+        _cabi.launch(view, b, c, T)
+    # the public entry point: first call (general path) and second call (prepared call)
+    for _ in range(2):
+        out = tnx.cuda_matmul(view, b)
+        _cabi.check_status(c.device)
+        assert_close(out.cpu(), ref, bf16)

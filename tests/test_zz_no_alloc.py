@@ -79,3 +79,15 @@ def test_rejects_what_does_not_fit_or_qualify():
     rc = call_static(odd, torch.zeros(70, 90, device=DEV, dtype=f16),
                      torch.empty(100, 90, device=DEV, dtype=f16), {"split_k": 2})
     assert rc == _cabi.ERR_INVALID and "tcgen05 kernel only" in _cabi.last_error()
+
+
+def test_python_wrapper_validates_operands():
+    a = torch.zeros(128, 256, device=DEV, dtype=f16)
+    b = torch.zeros(256, 128, device=DEV, dtype=f16)
+    c = torch.empty(128, 128, device=DEV, dtype=f16)
+    with pytest.raises(ValueError, match="inner dimensions"):
+        _cabi.launch_splitk_static(a, b[:128], c, {"split_k": 2})
+    with pytest.raises(ValueError, match="output must be"):
+        _cabi.launch_splitk_static(a, b, c[:64], {"split_k": 2})
+    with pytest.raises(ValueError, match="dtype mismatch"):
+        _cabi.launch_splitk_static(a, b.to(bf16), c, {"split_k": 2})

@@ -265,7 +265,20 @@ def check_status(device: torch.device | None = None) -> None:
     w = status_word(device)
     code = ctypes.c_int32(0)
     stream = torch.cuda.current_stream(w.device).cuda_stream
-    raise_for(lib.tnx_read_status(w.data_ptr(), ctypes.byref(code), stream))
+    rc = lib.tnx_read_status(w.data_ptr(), ctypes.byref(code), stream)
+    if rc == ERR_DEVICE:
+        # Slices of a split-K tile that gave up never bumped their tile counter, so the counters
+        # of this device's scratch buffers may be left non-zero: clear them (after everything
+        # queued on the device has drained) before any later launch trusts them.
+        message = last_error()
+        torch.cuda.synchronize(w.device)
+        with _scratch_lock:
+            for (idx, _), ws in _workspaces.items():
+                if idx == w.device.index:
+                    ws[:COUNTER_BYTES].zero_()
+        torch.cuda.synchronize(w.device)
+        raise DeviceStatusError(message)
+    raise_for(rc)
 
 
 _hilbert_tables: dict = {}
@@ -340,10 +353,10 @@ def launch_raw(device: torch.device, dtype: torch.dtype, a_ptr: int, b_ptr: int,
     return res
 
 
-def launch(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, cfg: dict | None = None,
-           epilogue: int = EPI_NONE, tile_table=None) -> Resources:
-    """Enqueues C = epilogue(A.B) on torch's current stream.  a: M x K, b: K x N, c: M x N (or
-    M x N/2 for a GLU epilogue); any strides.  Returns the resources the launch used."""
+def _check_operands(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, epilogue: int):
+    """Shape, dtype and device checks shared by the launch functions; returns (m, n, k).  Without
+    them a mismatched operand would make the tensor maps cover memory outside the caller's
+    tensors."""
     if not (a.is_cuda and b.is_cuda and c.is_cuda):
         raise RuntimeError("tritonix_b200 runs on CUDA tensors only (there is no CPU path)")
     if a.dim() != 2 or b.dim() != 2 or c.dim() != 2:
@@ -359,6 +372,14 @@ def launch(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, cfg: dict | None =
     n_out = n // 2 if epilogue != EPI_NONE else n
     if tuple(c.shape) != (m, n_out):
         raise ValueError(f"output must be {(m, n_out)}, got {tuple(c.shape)}")
+    return m, n, k
+
+
+def launch(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, cfg: dict | None = None,
+           epilogue: int = EPI_NONE, tile_table=None) -> Resources:
+    """Enqueues C = epilogue(A.B) on torch's current stream.  a: M x K, b: K x N, c: M x N (or
+    M x N/2 for a GLU epilogue); any strides.  Returns the resources the launch used."""
+    m, n, k = _check_operands(a, b, c, epilogue)
     return launch_raw(a.device, a.dtype, a.data_ptr(), b.data_ptr(), c.data_ptr(), m, n, k,
                       (*a.stride(), *b.stride(), *c.stride()), cfg, epilogue, tile_table)
 
@@ -370,9 +391,7 @@ def launch_splitk_static(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor,
     the caller's).  For hosts that must not allocate device memory while running; problems
     whose scratch exceeds ``STATIC_SCRATCH_BYTES`` raise ``ValueError``.  Calls on one device
     share the array and must be ordered on the GPU."""
-    require_cuda(a, b, c)
-    m, k = a.shape
-    n = b.shape[1]
+    m, n, k = _check_operands(a, b, c, epilogue)
     problem = make_problem(m, n, k, a.dtype, (*a.stride(), *b.stride(), *c.stride()), epilogue)
     config = make_config(cfg)
     stream = torch.cuda.current_stream(a.device).cuda_stream

@@ -120,6 +120,16 @@ int tnx_gemm(const tnx_problem* problem, const tnx_config* config, const void* a
     }
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // TMA needs 16-byte aligned base addresses.  When the caller left the choice of kernel open, a
+  // view that starts at an odd offset (e.g. big[:, 4:4 + K]) runs on the strided kernel, which
+  // honours the reference's "any strides, any pointer" contract (tritonix/ops/matmul.py:50-55).
+  const bool misaligned = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) |
+                            reinterpret_cast<uintptr_t>(c)) & 15u) != 0;
+  if (res.kernel == TNX_KERNEL_TCGEN05 && misaligned &&
+      (config == nullptr || config->kernel == TNX_KERNEL_AUTO)) {
+    rc = tnx::strided_query(*problem, &cfg, &res);
+    if (rc != TNX_OK) return rc;
+  }
   if (res.kernel == TNX_KERNEL_STRIDED) return tnx::strided_launch(*problem, a, b, c, s);
   if (res.workspace_bytes > 0) {
     if (workspace == nullptr || workspace_bytes < static_cast<size_t>(res.workspace_bytes)) {

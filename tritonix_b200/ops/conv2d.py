@@ -140,22 +140,34 @@ conv2d_forward_kernel = tunable(
 # Packed copies of weight tensors seen recently, so that a layer called again with unchanged
 # weights (inference, or several micro-batches per optimiser step) does not repack them.  An
 # entry is valid while the tensor is alive and its version counter (bumped by every in-place
-# write) has not moved.
+# write) has not moved.  Two limits of that test: a write through ``weight.data`` (``p.data.copy_``,
+# some optimisers and state-dict loaders) does not move the counter, so after one call
+# ``clear_caches()`` or pass ``weights_static=False``; and weights that require grad while
+# autograd is recording are assumed to be in training and are repacked on every call.
+# The packed copy is written on the stream of its first use; the event recorded there is waited
+# on by any other stream that reads the copy later.
 _PACKED_WEIGHTS: "dict[tuple, tuple]" = {}
 _PACKED_WEIGHTS_MAX = 64
 
 
-def _packed_weights(weight: torch.Tensor, problem_of) -> torch.Tensor:
+def _packed_weights(weight: torch.Tensor, problem_of, static: bool = True) -> torch.Tensor:
+    if not static or (weight.requires_grad and torch.is_grad_enabled()):
+        return _cabi.conv_pack_weights(problem_of(), weight)
     key = (weight.data_ptr(), weight.shape, weight.dtype, weight.device)
+    stream = torch.cuda.current_stream(weight.device)
     hit = _PACKED_WEIGHTS.get(key)
     if hit is not None:
-        ref, version, packed = hit
+        ref, version, packed, packed_on, done = hit
         if ref() is weight and version == weight._version:
+            if packed_on != stream.cuda_stream:
+                stream.wait_event(done)
             return packed
     packed = _cabi.conv_pack_weights(problem_of(), weight)
+    done = torch.cuda.Event()
+    done.record(stream)
     if len(_PACKED_WEIGHTS) >= _PACKED_WEIGHTS_MAX:
         _PACKED_WEIGHTS.pop(next(iter(_PACKED_WEIGHTS)))
-    _PACKED_WEIGHTS[key] = (weakref.ref(weight), weight._version, packed)
+    _PACKED_WEIGHTS[key] = (weakref.ref(weight), weight._version, packed, stream.cuda_stream, done)
     return packed
 
 
@@ -211,7 +223,7 @@ def _signature(input, weight, bias, stride, padding, dilation):
         stride, padding, dilation = _pair(stride), _pair(padding), _pair(dilation)
     return (input.shape, weight.shape, input.dtype, weight.dtype, input.device, weight.device,
             None if bias is None else (bias.shape, bias.dtype, bias.device, bias.is_contiguous()),
-            stride, padding, dilation, input.is_contiguous(), weight.is_contiguous())
+            stride, padding, dilation, input.stride(), weight.stride())
 
 
 def _prepare_fast_call(plan, out_shape, channels_last, packed, device, dtype):
@@ -244,7 +256,7 @@ def _prepare_fast_call(plan, out_shape, channels_last, packed, device, dtype):
 
 def conv2d_forward(input: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
                    stride=(1, 1), padding=(0, 0), dilation=(1, 1), use_tf32: bool = True,
-                   config: dict | None = None) -> torch.Tensor:
+                   config: dict | None = None, weights_static: bool = True) -> torch.Tensor:
     """Forward of ``torch.nn.functional.conv2d`` (groups = 1), the reference's
     ``conv2d_forward`` (forward.py:202-319): input N x C x H x W, weight C_OUT x C x R x S,
     optional bias, fp32 accumulation, output N x C_OUT x H_OUT x W_OUT of the input's dtype.
@@ -254,9 +266,12 @@ def conv2d_forward(input: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor
     ``GROUP_SIZE_M``, or this package's ``tile_n``/``tile_k``/``stages``/``cta_group``);
     without it the first call for a problem times a handful of candidates and remembers the
     best.  ``use_tf32`` is accepted for compatibility: fp32 inputs are computed in full fp32.
+    ``weights_static=False`` repacks the weights on every call instead of reusing the packed
+    copy of an unchanged tensor (needed when the weights are written through ``.data``, which
+    the version counter does not see).
     """
     signature = None
-    if config is None:
+    if config is None and weights_static:
         signature = _signature(input, weight, bias, stride, padding, dilation)
         fast = _FAST_CALLS.get(signature)
         if fast is not None:
@@ -297,7 +312,7 @@ def conv2d_forward(input: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor
     if input.dtype != torch.float32 and not plain_gemm:
         weight = _packed_weights(weight, lambda: _cabi.make_conv_problem(
             n, c_in, h_in, w_in, c_out, r, s, stride, padding, dilation, input.dtype,
-            bias is not None))
+            bias is not None), weights_static)
         extra["weights_packed"] = True
     args = (out, input, weight, bias, n, c_in, h_in, w_in, c_out, h_out, w_out, r, s,
             stride[0], stride[1], padding[0], padding[1], dilation[0], dilation[1],
