@@ -1,32 +1,44 @@
 #!/usr/bin/env python
 """Benchmark of the dense-contraction path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload gemm|splitk|glu|mlp|conv]
-                    [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload all|gemm|splitk|glu|mlp|conv] [--scaling weak|strong]
 
-Default workload (`gemm`): bf16 C = A.B with M = N = K = 8192, entries N(0,1)/sqrt(K), fp32
-accumulation, bf16 output — one step is one pass of the kernel over one such problem.  With N
-GPUs every rank owns an 8192-row block of a (8192*N) x 8192 A and a replica of B (row-sharded,
-no collective): per-GPU work is fixed, so scaling is "weak".
-Other workloads: `splitk` (fp16 64 x 14336 x 4096, HBM-bound), `glu` (bf16 fused SwiGLU
-8192x4096 . 4096x28672), `mlp` (bf16 SwiGLU MLP d=4096, ff=14336, 32768 tokens, tensor parallel
-over the N GPUs with one chunked NCCL all-reduce; strong scaling), `conv` (bf16 conv2d forward,
-64 x 256 x 28 x 28 NCHW with 256 3x3 filters through `conv2d_forward`; batch-sharded, weak).
+Headline (`value`): bf16 C = A.B with M = N = K = 8192, entries N(0,1)/sqrt(K), fp32 accumulation,
+bf16 output — one step is one pass of the kernel over one such problem.  With N GPUs every rank
+owns an 8192-row block of a (8192*N) x 8192 A and a replica of B (row-sharded, no collective):
+per-GPU work is fixed, so scaling is "weak".
 
-One JSON line is printed by rank 0.  `value` is device-timed with the operands resident in HBM;
-`e2e` is the same metric through the public API (`tritonix_b200.matmul`, ...) with the operands
-in pinned host memory, host<->device copies inside the timed region.
+With the default `--workload all` the same JSON line carries, under "workloads", one entry per
+remaining configuration, each measured to the same rules (device-timed value, roofline, e2e,
+clocks):
+  splitk       fp16 64 x 14336 x 4096, HBM-bound; every GPU runs its own replica
+  glu          bf16 fused SwiGLU 8192x4096 . 4096x28672 (interleaved W12); replicas
+  mlp          bf16 SwiGLU MLP d=4096, ff=14336, 32768 tokens, tensor parallel over the N GPUs
+               with one all-reduce (strong scaling, tokens/s) + parity of sampled rows against the
+               CPU oracle, computed outside the timed region
+  gemm_strong  (N > 1) the 8192^3 problem itself split along M: 8192/N rows per GPU
+and the gemm entry gains "sustained": at least 2 s of back-to-back launches under the power cap.
+`--workload X` measures one of them alone (`conv`: bf16 conv2d forward, 64 x 256 x 28 x 28).
+
+`value` is device-timed with the operands resident in HBM; `e2e` is the same metric through the
+public API (`tritonix_b200.matmul_from_host`, ...) with the operands in pinned host memory and
+the host<->device copies inside the timed region.  "comparators" (N = 1) times, on the same GPU
+and operands, cuBLAS through torch.matmul and the reference's own Triton kernel run by
+oracle/reference_gpu.py in a process of its own — comparisons only, never a backend.
 
 `--impl reference` times the reference's CPU path for the same workload — tritonix.matmul under
 force_backend("pytorch") on host tensors, i.e. torch.matmul on the host cores in fp32
-(tritonix/ops/matmul.py:291-293) — through the oracle port, on a bounded sample per step.
+(tritonix/ops/matmul.py:291-293) — through the oracle port, on the full problem for `gemm`.
 """
 from __future__ import annotations
 
 import argparse
 import json
 import os
+import subprocess
 import sys
+import tempfile
 import threading
 import time
 
@@ -39,9 +51,10 @@ if ROOT not in sys.path:
 L2_BYTES = 126 * 1024 * 1024
 
 WORKLOADS = {
-    # name: (m, n, k, dtype, description)
     "gemm": dict(m=8192, n=8192, k=8192, dtype="bf16",
                  name="gemm_bf16_8192x8192x8192_per_gpu_rows_sharded_B_replicated"),
+    "gemm_strong": dict(m=8192, n=8192, k=8192, dtype="bf16",
+                        name="gemm_bf16_8192x8192x8192_total_rows_sharded_B_replicated"),
     "splitk": dict(m=64, n=4096, k=14336, dtype="f16", name="splitk_gemm_f16_64x14336x4096"),
     "glu": dict(m=8192, n=28672, k=4096, dtype="bf16",
                 name="swiglu_bf16_x8192x4096_w12_4096x28672_interleaved"),
@@ -56,11 +69,22 @@ WORKLOADS = {
 GEMM_CFG = {"kernel": "tcgen05", "tile_n": 256, "tile_k": 128, "stages": 3, "cta_group": 2, "group_m": 16}
 SPLITK_CFG = {"kernel": "tcgen05", "tile_n": 128, "tile_k": 128, "stages": 4, "cta_group": 1, "split_k": 4}
 GLU_CFG = {"kernel": "tcgen05", "tile_n": 256, "tile_k": 128, "stages": 3, "cta_group": 2, "group_m": 16}
+CONFIG_SOURCE = "fixed in bench.py (the configurations that measured best on a B200)"
 
 # DRAM traffic of the dominant kernel per launch, from the ncu captures summarised under
 # profiles/ (None until a capture of that workload exists).
-NCU_TRAFFIC_BYTES = {"gemm": 1_389_138_048, "splitk": 125_974_528, "glu": 885_355_520, "mlp": None,
-                     "conv": 26_989_568}
+NCU_TRAFFIC_BYTES = {"gemm": 1_389_138_048, "gemm_strong": None, "splitk": 125_974_528,
+                     "glu": 885_355_520, "mlp": None, "conv": 26_989_568}
+
+# The reference's Triton kernels are timed with configurations from its own search space
+# (tritonix/ops/matmul.py:33-38; the hand-picked list of tritonix/utils/triton.py:34-53 tops
+# out at 128 x 128 x 64 tiles); the best of these is reported.
+TRITON_REF_CONFIGS = [
+    dict(block_m=128, block_n=128, block_k=64, group_m=8, num_stages=3, num_warps=8),
+    dict(block_m=128, block_n=128, block_k=64, group_m=8, num_stages=4, num_warps=4),
+    dict(block_m=128, block_n=128, block_k=32, group_m=8, num_stages=4, num_warps=4),
+    dict(block_m=128, block_n=64, block_k=64, group_m=8, num_stages=4, num_warps=4),
+]
 
 
 def measured_peaks():
@@ -74,10 +98,10 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+    """Samples SM clock, power and throttle reasons through NVML while a timed region runs."""
 
     def __init__(self, index: int, period_s: float = 0.004):
-        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.samples, self.power, self.reasons, self.max_mhz = [], [], set(), None
         self._stop = threading.Event()
         self._thread = None
         try:
@@ -97,6 +121,7 @@ class ClockSampler:
         while not self._stop.is_set():
             try:
                 self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                self.power.append(nv.nvmlDeviceGetPowerUsage(self._h) / 1000.0)
                 mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
                 for bit, name in names.items():
                     if bit and mask & bit and name not in ("nvmlClocksThrottleReasonAll",):
@@ -124,12 +149,35 @@ class ClockSampler:
                   "HwPowerBrakeSlowdown": "hw_power_brake_slowdown", "DisplayClockSetting": "display_clock_setting",
                   "None": "none"}
         reasons = sorted(pretty.get(r, r) for r in self.reasons if r not in ("None", "GpuIdle"))
-        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz,
-                "reasons": reasons, "samples": len(s)}
+        out = {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz,
+               "reasons": reasons, "samples": len(s)}
+        if self.power:
+            out["power_w_max"] = round(max(self.power), 1)
+        return out
+
+
+class Dist:
+    """The few collective helpers the timing needs; no-ops on one GPU."""
+
+    def __init__(self, world, dev):
+        self.world, self.dev = world, dev
+
+    def barrier(self):
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+
+    def max(self, value):
+        if self.world == 1:
+            return value
+        import torch.distributed as dist
+        t = torch.tensor([value], device=self.dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
 
 
 # ---------------------------------------------------------------------------------------------
-# workloads: each returns (step_fn, e2e_step_fn, work dict)
+# workloads: each setup returns (step_fn, e2e_step_fn, work dict)
 # ---------------------------------------------------------------------------------------------
 def torch_dtype(name):
     return {"bf16": torch.bfloat16, "f16": torch.float16}[name]
@@ -141,19 +189,22 @@ def randn(shape, dtype, device, seed, scale):
 
 
 def setup_contraction(workload, rank, world, dev):
-    """gemm / splitk / glu: one kernel launch per step."""
+    """gemm / gemm_strong / splitk / glu: one kernel launch per step."""
     from tritonix_b200 import _cabi
     import tritonix_b200 as tnx
     w = WORKLOADS[workload]
     m, n, k, dt = w["m"], w["n"], w["k"], torch_dtype(w["dtype"])
-    epi = _cabi.EPI_GLU_SILU if workload == "glu" else _cabi.EPI_NONE
+    if workload == "gemm_strong":
+        m = m // world  # this rank's rows of the one 8192^3 problem
+    glu = workload == "glu"
+    epi = _cabi.EPI_GLU_SILU if glu else _cabi.EPI_NONE
     n_out = n // 2 if epi else n
-    cfg = {"gemm": GEMM_CFG, "splitk": SPLITK_CFG, "glu": GLU_CFG}[workload]
+    cfg = {"gemm": GEMM_CFG, "gemm_strong": GEMM_CFG, "splitk": SPLITK_CFG, "glu": GLU_CFG}[workload]
     algo_bytes = (m * k + k * n + m * n_out) * 2
     # operands smaller than L2 are rotated through enough copies to defeat it
     copies = 1 if algo_bytes > 2 * L2_BYTES else -(-3 * L2_BYTES // algo_bytes)
-    a_scale = 1.0 if workload == "glu" else k ** -0.5
-    b_scale = 0.02 if workload == "glu" else k ** -0.5
+    a_scale = 1.0 if glu else k ** -0.5
+    b_scale = 0.02 if glu else k ** -0.5
     a_dev = [randn((m, k), dt, dev, 1000 * rank + i, a_scale) for i in range(copies)]
     b_dev = [randn((k, n), dt, dev, 1 + 7 * i, b_scale) for i in range(copies)]  # B is replicated
     c_dev = torch.empty((m, n_out), device=dev, dtype=dt)
@@ -171,23 +222,20 @@ def setup_contraction(workload, rank, world, dev):
     a_in, b_in = torch.empty_like(a_dev[0]), torch.empty_like(b_dev[0])
     mm = sys.modules["tritonix_b200.ops.matmul"]
     sw = sys.modules["tritonix_b200.ops.swiglu"]
-    mm._matmul_cfg[(m, n, k)] = {x: v for x, v in GEMM_CFG.items()}
-    mm._matmul_cfg[(1024, n, k)] = dict(GEMM_CFG)   # row chunks of the host pipeline
-    sw._glu_cfg[(1024, n, k)] = dict(GLU_CFG)
+    rows = min(1024, m)
+    mm._matmul_cfg[(m, n, k)] = dict(GEMM_CFG)
+    mm._matmul_cfg[(rows, n, k)] = dict(GEMM_CFG)   # row chunks of the host pipeline
+    sw._glu_cfg[(rows, n, k)] = dict(GLU_CFG)
     mm._splitk_cfg[(m, n, k, SPLITK_CFG["split_k"])] = dict(SPLITK_CFG)
     sw._glu_cfg[(m, n, k)] = dict(GLU_CFG)
-    if workload == "gemm":
-        tnx.matmul.cache[(m, k, str(dt), k, n, str(dt))] = "cuda"  # skip the first-call timing
-
-    rows = 1024
-    pipe = tnx.HostRowPipeline(dev, k, n_out, dt, rows_per_chunk=rows) if workload == "glu" else None
+    pipe = tnx.HostRowPipeline(dev, k, n_out, dt, rows_per_chunk=rows) if glu else None
 
     def e2e_step():
         # every step uploads A and B from pinned host memory and downloads the result; for the
-        # two large workloads the rows of A / C are pipelined against the kernel (public helpers)
-        if workload == "gemm":
+        # large workloads the rows of A / C are pipelined against the kernel (public helpers)
+        if workload in ("gemm", "gemm_strong"):
             tnx.matmul_from_host(a_host, b_host, c_host, rows_per_chunk=rows, b_device=b_in)
-        elif workload == "glu":
+        elif glu:
             pipe.run(lambda xd, od: tnx.swiglu(xd, b_in, out=od), a_host, c_host,
                      before=lambda: b_in.copy_(b_host, non_blocking=True))
         else:
@@ -198,7 +246,7 @@ def setup_contraction(workload, rank, world, dev):
 
     work = dict(flops=2.0 * m * n * k, bytes=float(algo_bytes), units=None, launches=1,
                 h2d=a_host.numel() * 2 + b_host.numel() * 2, d2h=c_host.numel() * 2, copies=copies,
-                cfg=cfg, out=c_dev, check=(a_dev[0], b_dev[0], epi))
+                cfg=cfg, operands=(a_dev, b_dev, c_dev), shape=(m, n, k))
     return step, e2e_step, work
 
 
@@ -247,35 +295,40 @@ def setup_conv(rank, world, dev, fixed_cfg=None):
         state["out"] = tnx.conv2d_forward(xs_cl[i], wt, None, config=cfg, **kw)
 
     work = dict(flops=2.0 * w["m"] * w["n"] * w["k"], bytes=float(algo_bytes), units=None, launches=3,
-                h2d=x_host.numel() * 2, d2h=y_host.numel() * 2, copies=copies, cfg=cfg, out=None,
-                check=None, kernel_step=kernel_step)
+                h2d=x_host.numel() * 2, d2h=y_host.numel() * 2, copies=copies, cfg=cfg,
+                kernel_step=kernel_step)
     return step, e2e_step, work
 
 
+def _mlp_weight_blocks(dev, lo, hi):
+    """Hidden units [lo, hi) of the global weights, generated per 128-unit block from
+    (seed, block) so that every tensor-parallel degree slices the same global matrices."""
+    d, dt = WORKLOADS["mlp"]["d"], torch.bfloat16
+    blocks = range(lo // 128, hi // 128)
+    wg = torch.cat([randn((d, 128), dt, dev, 10_000 + j, 0.02) for j in blocks], 1)
+    wu = torch.cat([randn((d, 128), dt, dev, 20_000 + j, 0.02) for j in blocks], 1)
+    wd = torch.cat([randn((128, d), dt, dev, 30_000 + j, 0.02) for j in blocks], 0)
+    return wg, wu, wd
+
+
 def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1):
-    comm_sms = (32 if world >= 8 else 0) if comm_sms < 0 else comm_sms
     """SwiGLU MLP, tensor parallel: column-parallel fused gate/up, row-parallel down, one
     all-reduce.  Global weights come from fixed seeds and are sliced, so every world size
     computes the same function."""
     import tritonix_b200 as tnx
     from tritonix_b200.distributed import TensorParallelSwiGLU, shard_bounds
+    comm_sms = (32 if world >= 8 else 0) if comm_sms < 0 else comm_sms
     w = WORKLOADS["mlp"]
     m, d, ff, dt = w["m"], w["d"], w["ff"], torch.bfloat16
     lo, hi = shard_bounds(ff, rank, world, 128)
     fr = hi - lo
-    # slice-then-interleave; generating the shard's columns directly from (seed, column block)
-    wg = torch.cat([randn((d, 128), dt, dev, 10_000 + j, 0.02) for j in range(lo // 128, hi // 128)], 1)
-    wu = torch.cat([randn((d, 128), dt, dev, 20_000 + j, 0.02) for j in range(lo // 128, hi // 128)], 1)
-    wd = torch.cat([randn((128, d), dt, dev, 30_000 + j, 0.02) for j in range(lo // 128, hi // 128)], 0)
+    wg, wu, wd = _mlp_weight_blocks(dev, lo, hi)  # slice-then-interleave
     w12 = torch.stack((wg, wu), 2).reshape(d, 2 * fr).contiguous()
     del wg, wu
     x = randn((m, d), dt, dev, 5, 1.0)
-    sw = sys.modules["tritonix_b200.ops.swiglu"]
-    mm = sys.modules["tritonix_b200.ops.matmul"]
     mlp = TensorParallelSwiGLU(
         w12, wd, chunks=chunks if (isinstance(chunks, list) or chunks > 0) else (1 if world == 1 else 4),
-        comm_sms=comm_sms,
-        gate_up_cfg=GLU_CFG, down_cfg=GEMM_CFG)
+        comm_sms=comm_sms, gate_up_cfg=GLU_CFG, down_cfg=GEMM_CFG)
     state = {}
 
     def step():
@@ -283,7 +336,6 @@ def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1):
 
     x_host = x.cpu().pin_memory()
     y_host = torch.empty((m, d), dtype=dt).pin_memory()
-
     pipe = tnx.HostRowPipeline(dev, d, d, dt, rows_per_chunk=4096)
     chunk_mlp = TensorParallelSwiGLU(w12, wd, chunks=1, comm_sms=comm_sms, gate_up_cfg=GLU_CFG,
                                      down_cfg=GEMM_CFG)
@@ -292,11 +344,27 @@ def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1):
         # rows of x stream in, rows of y stream out, 4096 rows (one all-reduce) at a time
         pipe.run(lambda xd, yd: chunk_mlp(xd, out=yd), x_host, y_host)
 
+    def parity():
+        """max|err|/max|ref| of sampled tokens of the last step's output against the CPU oracle
+        applied to the GLOBAL weights (rank 0 rebuilds them; outside any timed region)."""
+        from oracle import contraction as O
+        rows = sorted(set([0, m - 1] + torch.randint(0, m, (14,), generator=torch.Generator().manual_seed(3)).tolist()))
+        y_rows = state["y"][rows].cpu()
+        if rank != 0:
+            return None
+        g, u, dn = _mlp_weight_blocks(dev, 0, ff)
+        w12_cpu = torch.stack((g, u), 2).reshape(d, 2 * ff).cpu()
+        dn_cpu = dn.cpu()
+        del g, u, dn
+        ref = O.swiglu_mlp_oracle(x[rows].cpu(), w12_cpu, dn_cpu, out_dtype=torch.float32,
+                                  hidden_dtype=torch.bfloat16)
+        return O.rel_err(y_rows, ref)
+
     flops = 2.0 * m * d * (2 * ff) + 2.0 * m * ff * d
     nchunks = len(mlp.chunk_bounds(m))
     work = dict(flops=flops, bytes=None, units=float(m), launches=2 * nchunks, h2d=x_host.numel() * 2,
                 d2h=y_host.numel() * 2, copies=1, cfg={"gate_up": GLU_CFG, "down": GEMM_CFG},
-                out=None, check=None, chunks=nchunks, comm_sms=comm_sms)
+                chunks=nchunks, comm_sms=comm_sms, parity=parity)
     return step, e2e_step, work
 
 
@@ -336,8 +404,224 @@ def time_steps(fn, steps, warmup, barrier, graph=False):
     return start.elapsed_time(end)  # ms, on the launching (current) stream
 
 
-def cpu_baseline_sample(workload, seconds_target=15.0):
-    """The reference's CPU path on a bounded sample of the workload, all host threads."""
+def sustained_leg(step, flops, local_rank, seconds, peaks):
+    """At least `seconds` of back-to-back launches: the chip settles at the clock its power cap
+    allows.  Launches are issued in batches sized from a first estimate; the timed region is the
+    whole run (CUDA events), the clock is NVML-sampled during it."""
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(10):
+        step()
+    e1.record()
+    e1.synchronize()
+    per = max(e0.elapsed_time(e1) / 10, 1e-3)
+    launches = int(seconds * 1000.0 / per * 1.05) + 1
+    with ClockSampler(local_rank, period_s=0.02) as clocks:
+        e0.record()
+        for _ in range(launches):
+            step()
+        e1.record()
+        e1.synchronize()
+    ms = e0.elapsed_time(e1)
+    c = clocks.summary()
+    tf = flops * launches / (ms * 1e-3) / 1e12
+    ms_launch = ms / launches
+    return {"seconds": ms * 1e-3, "launches": launches, "ms_per_launch": ms_launch, "value": tf,
+            "unit": "TFLOP/s", "peak": peaks["sustained"], "frac": tf / peaks["sustained"],
+            "peak_source": peaks["source"] + " sustained cuBLAS bf16", "clocks": c,
+            "ms_x_mhz": ms_launch * c["sm_mhz"] if c.get("sm_mhz") else None}
+
+
+def metric_of(workload):
+    if workload == "mlp":
+        return "SwiGLU MLP tokens/s", "tokens/s"
+    if workload == "conv":
+        return "conv2d forward TFLOP/s", "TFLOP/s"
+    return "GEMM TFLOP/s", "TFLOP/s"
+
+
+def to_metric(workload, work_flops, units, ms):
+    if workload == "mlp":
+        return units / (ms * 1e-3)
+    return work_flops / (ms * 1e-3) / 1e12
+
+
+def measure(workload, args, rank, local_rank, world, dev, D, peaks):
+    """One workload, measured to the contract's rules.  Returns the entry (rank 0's view)."""
+    import tritonix_b200 as tnx
+    if workload == "mlp":
+        chunks = [float(v) for v in args.chunk_weights.split(",")] if args.chunk_weights else args.chunks
+        step, e2e_step, work = setup_mlp(rank, world, dev, chunks, args.comm_sms)
+    elif workload == "conv":
+        step, e2e_step, work = setup_conv(rank, world, dev, json.loads(args.cfg) if args.cfg else None)
+    else:
+        step, e2e_step, work = setup_contraction(workload, rank, world, dev)
+
+    # ---- device-timed value (operands resident in HBM)
+    use_graph = args.launch == "graph" or (args.launch == "auto" and workload == "splitk")
+    with ClockSampler(local_rank) as clocks:
+        ms_total = time_steps(step, args.steps, args.warmup, D.barrier, graph=use_graph)
+    tnx.check_status(dev)
+    ms_total = D.max(ms_total)
+    ms_step = ms_total / args.steps
+
+    # ---- end to end through the public API, host buffers
+    ms_e2e = None
+    if not args.no_e2e:
+        e2e_steps = max(3, min(args.steps, 10))
+        ms_e2e = D.max(time_steps(e2e_step, e2e_steps, 3, D.barrier)) / e2e_steps
+        tnx.check_status(dev)
+
+    strong = workload in ("mlp", "gemm_strong")
+    # weak scaling: every rank does the whole per-GPU problem; gemm_strong: each rank 1/N of it
+    scale = 1 if workload == "mlp" else world
+    metric, unit = metric_of(workload)
+    units = work["units"]
+    value = to_metric(workload, work["flops"] * scale, units, ms_step)
+    e2e_value = to_metric(workload, work["flops"] * scale, units, ms_e2e) if ms_e2e else None
+
+    # ---- roofline of the dominant kernel (per launch, per GPU)
+    if workload == "splitk":
+        achieved = work["bytes"] / (ms_step * 1e-3) / 1e9
+        roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
+                "frac": achieved / peaks["hbm"], "traffic": NCU_TRAFFIC_BYTES["splitk"],
+                "peak_source": peaks["source"] + " copy bandwidth",
+                "frac_of_nominal_8000": achieved / 8000.0}
+    else:
+        per_gpu_flops = work["flops"] / (world if workload == "mlp" else 1)
+        ms_kernel = ms_step
+        if work.get("kernel_step") is not None:
+            # a step has several launches: time the dominant kernel on its own
+            ms_kernel = D.max(time_steps(work["kernel_step"], args.steps, args.warmup,
+                                         D.barrier, graph=True)) / args.steps
+            tnx.check_status(dev)
+        achieved = per_gpu_flops / (ms_kernel * 1e-3) / 1e12
+        long_run = ms_total > 1000.0
+        peak = peaks["sustained"] if long_run else peaks["burst"]
+        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES[workload],
+                "peak_source": peaks["source"] + (" sustained" if long_run else " burst") + " cuBLAS bf16",
+                "frac_of_nominal_2250": achieved / 2250.0}
+        if workload == "mlp":
+            roof["note"] = ("whole step (fused gate/up GEMM + down GEMM"
+                            + (" + all-reduce" if world > 1 else "") + ") against the tensor peak")
+        if work.get("kernel_step") is not None:
+            roof["kernel_ms"] = ms_kernel
+            roof["note"] = ("dominant kernel timed alone on channels_last tensors, launches replayed "
+                            "as one CUDA graph; a step on NCHW tensors adds the two repacking passes")
+
+    parallelism = {"mlp": "tp%d", "conv": "batch_sharded_x%d", "splitk": "replicas_x%d",
+                   "glu": "replicas_x%d"}.get(workload, "rows_sharded_x%d") % world
+    entry = {
+        "metric": metric, "value": value, "unit": unit, "ms_per_step": ms_step,
+        "scaling": "strong" if strong else "weak", "dtype": WORKLOADS[workload]["dtype"],
+        "config": {"workload": WORKLOADS[workload]["name"], "kernel_config": work["cfg"],
+                   "kernel_config_source": CONFIG_SOURCE,
+                   **({"allreduce_chunks": work["chunks"], "comm_sms": work["comm_sms"]}
+                      if workload == "mlp" and world > 1 else {}),
+                   "parallelism": parallelism,
+                   "launch": "cuda_graph_of_%d_steps" % args.steps if use_graph else "eager",
+                   "l2": ("operands rotate through %d copies (> 3x L2)" % work["copies"]) if work["copies"] > 1
+                   else "operands exceed the 126 MB L2"},
+        "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": work["h2d"],
+                "d2h_bytes_per_step": work["d2h"], "ms_per_step": ms_e2e},
+        "gpu_launches": work["launches"] * args.steps,
+        "clocks": clocks.summary(),
+        "roofline": roof,
+    }
+    if workload == "mlp":
+        step()  # one more step outside any timed region; its output is what parity checks
+        torch.cuda.synchronize(dev)
+        err = work["parity"]()
+        if err is not None:
+            entry["parity_err"] = err
+            entry["parity"] = ("max|err|/max|ref| over 16 sampled tokens against the CPU oracle "
+                               "(fp32, intermediate rounded to bf16) on the global weights; tolerance 8e-3")
+        tnx.check_status(dev)
+    if workload == "gemm" and not args.no_sustained:
+        entry["sustained"] = sustained_leg(step, work["flops"], local_rank, args.sustained_seconds, peaks)
+        tnx.check_status(dev)
+    if workload in ("gemm", "glu", "splitk") and world == 1 and rank == 0 and not args.no_comparators:
+        entry["comparators"] = comparators(workload, work, args, dev)
+    return entry
+
+
+# ---------------------------------------------------------------------------------------------
+# comparisons on the same GPU (never a backend of the product)
+# ---------------------------------------------------------------------------------------------
+def comparators(workload, work, args, dev):
+    out = {}
+    a_all, b_all, c = work["operands"]
+    m, n, k = work["shape"]
+    steps = max(5, min(args.steps, 20))
+    noop = lambda: None  # noqa: E731
+    state = {"i": 0}
+    if workload == "glu":
+        a, b = a_all[0], b_all[0]
+        w1, w2 = b[:, 0::2].contiguous(), b[:, 1::2].contiguous()
+        fn = lambda: torch.nn.functional.silu(a @ w1) * (a @ w2)  # noqa: E731
+        label = "unfused F.silu(x @ W1) * (x @ W2), cuBLAS + elementwise kernels"
+    else:
+        def fn():  # the same rotation through operand copies as the kernel under test
+            i = state["i"] % len(a_all)
+            state["i"] += 1
+            torch.matmul(a_all[i], b_all[i], out=c)
+        label = "torch.matmul (cuBLAS), same operands"
+    ms = time_steps(fn, steps, 3, noop, graph=(workload == "splitk")) / steps
+    out["cublas"] = {"what": label, "ms_per_step": ms, "value": work["flops"] / (ms * 1e-3) / 1e12,
+                     "unit": "TFLOP/s"}
+    if workload == "glu":
+        del w1, w2
+    out["triton_ref"] = triton_reference_timing(workload, m, n, k)
+    return out
+
+
+def triton_reference_timing(workload, m, n, k):
+    """The reference's own Triton kernel on this GPU, in a process of its own (its package name
+    collides with this one's alias, and its JIT should not share this context)."""
+    if not os.path.isdir(os.path.join(ROOT, "oracle", "_ref", "tritonix")):
+        return {"unavailable": "the reference package is not staged under oracle/_ref "
+                               "(python oracle/make_ref.py <reference tree>)"}
+    kind = {"gemm": "matmul", "splitk": "splitk", "glu": "glu"}[workload]
+    dtype = "float16" if workload == "splitk" else "bfloat16"
+    cases = []
+    for i, cfg in enumerate(TRITON_REF_CONFIGS[:4 if workload == "gemm" else 2]):
+        cfg = dict(cfg)
+        if kind == "splitk":
+            cfg.update(block_m=64, split_k=4)
+        cases.append(dict(name=f"cfg{i}", kind=kind, m=m, n=n, k=k, dtype=dtype, seed=i,
+                          a_scale=1.0 if kind == "glu" else k ** -0.5,
+                          b_scale=0.02 if kind == "glu" else k ** -0.5, cfg=cfg, rows=[0], time=True,
+                          reps=10, activation="silu"))
+    try:
+        with tempfile.TemporaryDirectory() as tmp:
+            spec, raw = os.path.join(tmp, "spec.json"), os.path.join(tmp, "raw.npz")
+            with open(spec, "w") as f:
+                json.dump(cases, f)
+            env = {k_: v for k_, v in os.environ.items() if k_ != "TRITON_INTERPRET"}
+            done = subprocess.run([sys.executable, os.path.join(ROOT, "oracle", "reference_gpu.py"),
+                                   "--spec", spec, "--out", raw], env=env, capture_output=True,
+                                  text=True, timeout=600)
+            if done.returncode != 0:
+                return {"unavailable": "reference kernels failed to run: " + done.stderr.strip()[-300:]}
+            import numpy as np
+            got = np.load(raw)
+            best = min(range(len(cases)), key=lambda i: float(got[f"cfg{i}/ms"][0]))
+            ms = float(got[f"cfg{best}/ms"][0])
+    except Exception as exc:  # a comparison that cannot run must not take the benchmark down
+        return {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
+    return {"what": "the reference's Triton kernel (JIT for this GPU), best of %d configurations of its own "
+                    "search space, mean of 10 launches with L2 flushed" % len(cases),
+            "config": cases[best]["cfg"], "ms_per_step": ms, "value": 2.0 * m * n * k / (ms * 1e-3) / 1e12,
+            "unit": "TFLOP/s"}
+
+
+# ---------------------------------------------------------------------------------------------
+# the reference's CPU path
+# ---------------------------------------------------------------------------------------------
+def cpu_baseline_sample(workload, seconds_target=15.0, full=False):
+    """The reference's CPU path on the workload (or a bounded sample of it), all host threads."""
     from oracle import contraction as O
     if torch.get_num_threads() < (os.cpu_count() or 1):
         torch.set_num_threads(os.cpu_count() or 1)
@@ -364,7 +648,7 @@ def cpu_baseline_sample(workload, seconds_target=15.0):
         units = None
     else:
         m, n, k = w["m"], w["n"], w["k"]
-        m_s = min(m, 512 if workload == "glu" else 1024)
+        m_s = m if full else min(m, 512 if workload == "glu" else 1024)
         a = torch.randn(m_s, k, generator=g)
         b = torch.randn(k, n, generator=g) * (0.02 if workload == "glu" else k ** -0.5)
         if workload == "glu":
@@ -372,7 +656,8 @@ def cpu_baseline_sample(workload, seconds_target=15.0):
         else:
             fn = lambda: O.matmul_oracle(a, b, out_dtype=torch.float32)  # noqa: E731
         flops = 2.0 * m_s * n * k
-        sample = f"{m_s} of {m} rows of A against the full B, fp32 torch.matmul on host"
+        sample = (f"the full problem ({m} x {k} . {k} x {n})" if m_s == m else
+                  f"{m_s} of {m} rows of A against the full B") + ", fp32 torch.matmul on host"
         units = None
     fn()  # warm-up
     t0 = time.perf_counter()
@@ -387,41 +672,29 @@ def cpu_baseline_sample(workload, seconds_target=15.0):
     return dict(flops=flops, seconds=best, threads=threads, sample=sample, units=units, fn=fn)
 
 
-def metric_of(workload):
-    if workload == "mlp":
-        return "SwiGLU MLP tokens/s", "tokens/s"
-    if workload == "conv":
-        return "conv2d forward TFLOP/s", "TFLOP/s"
-    return "GEMM TFLOP/s", "TFLOP/s"
-
-
-def to_metric(workload, work_flops, units, ms):
-    if workload == "mlp":
-        return units / (ms * 1e-3)
-    return work_flops / (ms * 1e-3) / 1e12
-
-
 def run_reference(args, rank):
-    """CPU arm: rank 0 only; every step is one pass over the bounded sample."""
+    """CPU arm: rank 0 only.  For the headline workload every step is one pass over the FULL
+    8192^3 problem (about half a second on 16 cores); the others use a bounded sample."""
     if rank != 0:
         return
     # launchers such as torchrun pin OMP_NUM_THREADS=1; the CPU arm uses every host core
     torch.set_num_threads(os.cpu_count() or 1)
-    metric, unit = metric_of(args.workload)
-    base = cpu_baseline_sample(args.workload, seconds_target=2.0)
+    workload = "gemm" if args.workload == "all" else args.workload
+    metric, unit = metric_of(workload)
+    base = cpu_baseline_sample(workload, seconds_target=1.0, full=(workload == "gemm"))
     fn = base["fn"]
-    for _ in range(max(0, args.warmup - 1)):
+    for _ in range(max(0, args.warmup - 2)):
         fn()
     t0 = time.perf_counter()
     for _ in range(args.steps):
         fn()
     sec = (time.perf_counter() - t0) / args.steps
-    value = base["units"] / sec if args.workload == "mlp" else base["flops"] / sec / 1e12
+    value = base["units"] / sec if workload == "mlp" else base["flops"] / sec / 1e12
     line = {
         "impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
-        "scaling": "strong" if args.workload == "mlp" else "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic", "config": {"workload": WORKLOADS[args.workload]["name"]},
+        "scaling": "strong" if workload == "mlp" else "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": {"workload": WORKLOADS[workload]["name"]},
         "cpu_baseline": {"value": value, "unit": unit, "cores": base["threads"], "kind": "port",
                          "sample": base["sample"]},
         "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -435,9 +708,15 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", choices=list(WORKLOADS), default="gemm")
+    ap.add_argument("--workload", choices=["all"] + list(WORKLOADS), default="all")
+    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak",
+                    help="--workload gemm on N GPUs: weak = 8192 rows per GPU, strong = 8192/N rows "
+                         "per GPU of the one 8192^3 problem")
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-sustained", action="store_true")
+    ap.add_argument("--no-comparators", action="store_true")
+    ap.add_argument("--sustained-seconds", type=float, default=2.0)
     ap.add_argument("--cfg", type=str, default=None,
                     help="JSON object overriding kernel-config keys of the workload, e.g. "
                          "'{\"group_m\": 8}'")
@@ -469,116 +748,55 @@ def main():
     import torch.distributed as dist
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
+    everything = args.workload == "all"
+    headline = "gemm" if everything else args.workload
+    if headline == "gemm" and args.scaling == "strong":
+        headline = "gemm_strong"
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         pg_options = None
         reserve = (32 if world >= 8 else 0) if args.comm_sms < 0 else args.comm_sms
-        if args.workload == "mlp" and reserve > 0:
+        if (everything or headline == "mlp") and reserve > 0:
             try:  # keep the all-reduce inside the SMs that the GEMM grids leave free
                 pg_options = dist.ProcessGroupNCCL.Options()
                 pg_options.config.max_ctas = reserve
             except Exception:
                 pg_options = None
         dist.init_process_group("nccl", device_id=dev, pg_options=pg_options)
+    D = Dist(world, dev)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-
-    def max_over_ranks(ms):
-        if world == 1:
-            return ms
-        t = torch.tensor([ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    import tritonix_b200 as tnx
-    if args.cfg:
+    import tritonix_b200 as tnx  # noqa: F401
+    if args.cfg and headline != "conv":
         override = json.loads(args.cfg)
         for base in (GEMM_CFG, SPLITK_CFG, GLU_CFG):
             base.update(override)
-    if args.workload == "mlp":
-        chunks = [float(v) for v in args.chunk_weights.split(",")] if args.chunk_weights else args.chunks
-        step, e2e_step, work = setup_mlp(rank, world, dev, chunks, args.comm_sms)
-    elif args.workload == "conv":
-        step, e2e_step, work = setup_conv(rank, world, dev, json.loads(args.cfg) if args.cfg else None)
-    else:
-        step, e2e_step, work = setup_contraction(args.workload, rank, world, dev)
-
-    # ---- device-timed value (operands resident in HBM)
-    use_graph = args.launch == "graph" or (args.launch == "auto" and args.workload == "splitk")
-    with ClockSampler(local_rank) as clocks:
-        ms_total = time_steps(step, args.steps, args.warmup, barrier, graph=use_graph)
-    tnx.check_status(dev)
-    ms_total = max_over_ranks(ms_total)
-    ms_step = ms_total / args.steps
-
-    # ---- end to end through the public API, host buffers
-    ms_e2e = None
-    if not args.no_e2e:
-        e2e_steps = max(3, min(args.steps, 10))
-        ms_e2e = max_over_ranks(time_steps(e2e_step, e2e_steps, 3, barrier)) / e2e_steps
-        tnx.check_status(dev)
-
-    strong = args.workload == "mlp"
-    scale = 1 if strong else world  # weak scaling: every rank does the whole per-GPU problem
-    metric, unit = metric_of(args.workload)
-    units = work["units"]
-    value = to_metric(args.workload, work["flops"] * scale, units, ms_step)
-    e2e_value = to_metric(args.workload, work["flops"] * scale, units, ms_e2e) if ms_e2e else None
-
-    # ---- roofline of the dominant kernel (per launch, per GPU)
     peaks = measured_peaks()
-    launches_per_step = work["launches"]
-    if args.workload == "splitk":
-        achieved = work["bytes"] / (ms_step * 1e-3) / 1e9
-        roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm"], "unit": "GB/s",
-                "frac": achieved / peaks["hbm"], "traffic": NCU_TRAFFIC_BYTES["splitk"],
-                "peak_source": peaks["source"] + " copy bandwidth"}
-    else:
-        per_gpu_flops = work["flops"] / (world if strong else 1)
-        ms_kernel = ms_step
-        if work.get("kernel_step") is not None:
-            # a step has several launches: time the dominant kernel on its own
-            ms_kernel = max_over_ranks(time_steps(work["kernel_step"], args.steps, args.warmup,
-                                                  barrier, graph=True)) / args.steps
-            tnx.check_status(dev)
-        achieved = per_gpu_flops / (ms_kernel * 1e-3) / 1e12
-        long_run = ms_total > 1000.0
-        peak = peaks["sustained"] if long_run else peaks["burst"]
-        roof = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES[args.workload],
-                "peak_source": peaks["source"] + (" sustained" if long_run else " burst") + " cuBLAS bf16",
-                "frac_of_nominal_2250": achieved / 2250.0}
-        if work.get("kernel_step") is not None:
-            roof["kernel_ms"] = ms_kernel
-            roof["note"] = ("dominant kernel timed alone on channels_last tensors, launches replayed "
-                            "as one CUDA graph; a step on NCHW tensors adds the two repacking passes")
 
+    entry = measure(headline, args, rank, local_rank, world, dev, D, peaks)
     line = {
-        "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
-        "scaling": "strong" if strong else "weak", "vs_baseline": None, "dtype": WORKLOADS[args.workload]["dtype"],
-        "data": "synthetic",
-        "config": {"workload": WORKLOADS[args.workload]["name"], "kernel_config": work["cfg"],
-                   **({"allreduce_chunks": work["chunks"], "comm_sms": work["comm_sms"]}
-                      if args.workload == "mlp" and world > 1 else {}),
-                   "parallelism": ("tp%d" % world) if strong else
-                   (("batch_sharded_x%d" if args.workload == "conv" else "rows_sharded_x%d") % world),
-                   "launch": "cuda_graph_of_%d_steps" % args.steps if use_graph else "eager",
-                   "l2": ("operands rotate through %d copies (> 3x L2)" % work["copies"]) if work["copies"] > 1
-                   else "operands exceed the 126 MB L2"},
-        "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": work["h2d"],
-                "d2h_bytes_per_step": work["d2h"], "ms_per_step": ms_e2e},
-        "gpu_launches": launches_per_step * args.steps,
-        "clocks": clocks.summary(),
-        "roofline": roof,
+        "metric": entry["metric"], "value": entry["value"], "unit": entry["unit"], "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": entry["ms_per_step"],
+        "higher_is_better": True, "scaling": entry["scaling"], "vs_baseline": None,
+        "dtype": entry["dtype"], "data": "synthetic", "config": entry["config"], "e2e": entry["e2e"],
+        "gpu_launches": entry["gpu_launches"], "clocks": entry["clocks"], "roofline": entry["roofline"],
     }
-    if rank == 0 and world >= 1 and not args.no_cpu_baseline and args.gpus == 1:
-        base = cpu_baseline_sample(args.workload)
-        v = base["units"] / base["seconds"] if strong else base["flops"] / base["seconds"] / 1e12
-        line["cpu_baseline"] = {"value": v, "unit": unit, "cores": base["threads"], "kind": "port",
-                                "sample": base["sample"]}
+    for extra in ("sustained", "comparators", "parity_err", "parity"):
+        if extra in entry:
+            line[extra] = entry[extra]
+    if rank == 0 and not args.no_cpu_baseline and world == 1:
+        wl = "gemm" if headline == "gemm_strong" else headline
+        base = cpu_baseline_sample(wl)
+        v = base["units"] / base["seconds"] if wl == "mlp" else base["flops"] / base["seconds"] / 1e12
+        line["cpu_baseline"] = {"value": v, "unit": entry["unit"], "cores": base["threads"],
+                                "kind": "port", "sample": base["sample"]}
+    if everything:
+        line["workloads"] = {}
+        others = ["splitk", "glu", "mlp"] + (["gemm_strong"] if world > 1 else [])
+        for wl in others:
+            torch.cuda.empty_cache()
+            sub = measure(wl, args, rank, local_rank, world, dev, D, peaks)
+            sub["steps"], sub["warmup"], sub["n_gpus"] = args.steps, args.warmup, world
+            line["workloads"][wl] = sub
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -1,6 +1,8 @@
 """Loads the reference implementation (ayghri/tritonix) from a source tree for comparison runs.
-TEST INFRASTRUCTURE ONLY — used by tests/golden/make_golden.py in a container that has the
-reference tree; nothing on a GPU box or in the product imports it.
+TEST INFRASTRUCTURE ONLY — used by tests/golden/make_golden.py (CPU, Triton's interpreter) where
+the reference tree is mounted, and by oracle/reference_gpu.py (a process of its own that runs the
+reference's kernels on a GPU from the copy staged by oracle/make_ref.py); nothing in the product
+imports it.
 
 `import tritonix` fails on the reference as shipped: tritonix/autotune.py:8-11 imports
 `CoordinateMonotonicFunction`, which tritonix/utils/pruners.py:172 defines under the name
