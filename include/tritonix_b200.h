@@ -187,6 +187,66 @@ int tnx_glu(const tnx_problem* problem, const tnx_config* config, int activation
 int tnx_gemm_splitk_static(const tnx_problem* problem, const tnx_config* config, const void* a,
                            const void* b, void* c, int32_t* status_word, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * The SwiGLU MLP block in one launch:  Y = ( act(X.W1) * (X.W2) ) . W3.
+ * Replaces a launch of swiglu_kernel[grid](x, w12, w3, z, m, n, k, f, stride_xm, stride_xk,
+ * stride_wk, stride_wn, stride_w3n, stride_w3l, stride_zm, stride_zl, ...) (tritonix/ops/
+ * swiglu.py:113-230; the two-phase design with a workspace and per-row-block flags is sketched
+ * in playground/fused_mlp.py:10-161).  Unlike the reference's kernel it is correct for any size,
+ * takes fp16/bf16, and is deterministic (no atomics on data).
+ * ------------------------------------------------------------------------------------------- */
+typedef struct tnx_mlp_problem {
+  int32_t m;          /* rows of X and Y (tokens)                                               */
+  int32_t d_model;    /* columns of X = rows of W12           (the reference's k)               */
+  int32_t d_ff;       /* hidden units F: W12 has 2F interleaved columns (the reference's n / 2) */
+  int32_t n_out;      /* columns of W3 and Y                  (the reference's f)               */
+  int32_t dtype;      /* TNX_F16 or TNX_BF16, shared by X, W12, W3, Y and the hidden activation */
+  int32_t activation; /* TNX_EPI_GLU_LINEAR / _SILU / _SIGMOID                                  */
+  int64_t stride_xm;  /* row pitches in elements; rows are contiguous (inner stride 1)          */
+  int64_t stride_w12k;
+  int64_t stride_w3k;
+  int64_t stride_ym;
+} tnx_mlp_problem;
+
+typedef struct tnx_mlp_resources {
+  int32_t smem_bytes, tmem_columns, grid;
+  int32_t tiles_m;             /* 256-row tiles                                                 */
+  int32_t band_rows;           /* rows of X per band = group_m * 256                            */
+  int32_t num_bands;
+  int64_t min_workspace_bytes; /* counters + two bands of the hidden activation (or all of it)  */
+  int64_t workspace_bytes;     /* recommended: counters + three bands                           */
+} tnx_mlp_resources;
+
+/* Validates (problem, config) and reports what the launch needs.  `config` may be NULL; used
+ * fields: tile_k (64 or 128), stages, group_m (256-row tiles per band, default 4), max_ctas.
+ * tile_m / tile_n / cta_group, if set, must be 256 / 256 / 2. */
+int tnx_swiglu_mlp_query(const tnx_mlp_problem* problem, const tnx_config* config,
+                         tnx_mlp_resources* out);
+
+/*
+ * The fixed global order in which the kernel's work units are walked (host-side, no device
+ * needed; used to check the dependency rule: a unit only waits for units earlier in the order).
+ * Writes up to `capacity` entries (down << 30) | (row_tile << 14) | column_tile — down = 0 for a
+ * hidden-activation tile, 1 for an output tile — and returns the number of units, or minus a
+ * TNX_ERR_* code.
+ */
+int tnx_swiglu_mlp_unit_order(const tnx_mlp_problem* problem, const tnx_config* config,
+                              int32_t* units, int32_t capacity);
+
+/*
+ * Enqueues the fused MLP on `stream`.  `workspace` (256-byte aligned, at least
+ * min_workspace_bytes) holds the dependency counters, which this call clears on `stream`, and
+ * a ring of bands of the hidden activation: the larger it is (up to counters + the whole
+ * m x d_ff activation) the further a band's readers are ahead of its slot's next writers.
+ * Its content before and after the call is meaningless.  Calls sharing a workspace must be
+ * ordered on one stream.  The kernel's CTAs wait for one another through the counters (bounded
+ * waits that report through `status_word`), so the launch is sized to what the GPU can hold
+ * at once.
+ */
+int tnx_swiglu_mlp(const tnx_mlp_problem* problem, const tnx_config* config, const void* x,
+                   const void* w12, const void* w3, void* y, void* workspace,
+                   size_t workspace_bytes, int32_t* status_word, void* stream);
+
 /*
  * Synchronises `stream`, copies *status_word to the host and returns TNX_OK if it is zero,
  * else TNX_ERR_DEVICE (code available in *code_out if not NULL) after resetting it to zero.

@@ -82,13 +82,25 @@ class ConvResources(ctypes.Structure):
         [("workspace_bytes", ctypes.c_int64)]
 
 
+class MlpProblem(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int32) for n in ("m", "d_model", "d_ff", "n_out", "dtype", "activation")] + \
+        [(n, ctypes.c_int64) for n in ("stride_xm", "stride_w12k", "stride_w3k", "stride_ym")]
+
+
+class MlpResources(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int32) for n in ("smem_bytes", "tmem_columns", "grid", "tiles_m",
+                                              "band_rows", "num_bands")] + \
+        [("min_workspace_bytes", ctypes.c_int64), ("workspace_bytes", ctypes.c_int64)]
+
+
 LAYOUT_NCHW, LAYOUT_NHWC = 0, 1
 WEIGHT_KCRS, WEIGHT_PACKED = 0, 1
 
 EXPORTS = ("tnx_version", "tnx_last_error", "tnx_sm_count", "tnx_gemm_query", "tnx_gemm",
            "tnx_glu", "tnx_read_status", "tnx_gemm_splitk_static", "tnx_selftest_bounded_wait",
            "tnx_conv2d_query", "tnx_conv2d_forward", "tnx_conv2d_packed_weight_bytes",
-           "tnx_conv2d_pack_weights")
+           "tnx_conv2d_pack_weights", "tnx_swiglu_mlp_query", "tnx_swiglu_mlp",
+           "tnx_swiglu_mlp_unit_order")
 STATIC_SCRATCH_BYTES = 16 * 1024 * 1024 + 65536
 
 
@@ -125,6 +137,16 @@ def _load() -> ctypes.CDLL:
     lib.tnx_read_status.restype = ctypes.c_int
     lib.tnx_read_status.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32),
                                     ctypes.c_void_p]
+    lib.tnx_swiglu_mlp_query.restype = ctypes.c_int
+    lib.tnx_swiglu_mlp_query.argtypes = [ctypes.POINTER(MlpProblem), ctypes.POINTER(Config),
+                                         ctypes.POINTER(MlpResources)]
+    lib.tnx_swiglu_mlp_unit_order.restype = ctypes.c_int
+    lib.tnx_swiglu_mlp_unit_order.argtypes = [ctypes.POINTER(MlpProblem), ctypes.POINTER(Config),
+                                              ctypes.POINTER(ctypes.c_int32), ctypes.c_int32]
+    lib.tnx_swiglu_mlp.restype = ctypes.c_int
+    lib.tnx_swiglu_mlp.argtypes = [ctypes.POINTER(MlpProblem), ctypes.POINTER(Config),
+                                   ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                   ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p]
     lib.tnx_conv2d_query.restype = ctypes.c_int
     lib.tnx_conv2d_query.argtypes = [ctypes.POINTER(ConvProblem), ctypes.POINTER(Config),
                                      ctypes.POINTER(ConvResources)]
@@ -400,6 +422,89 @@ def launch_splitk_static(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor,
                                         b.data_ptr(), c.data_ptr(),
                                         status_word(a.device).data_ptr(), stream)
     raise_for(rc)
+
+
+# ---------------------------------------------------------------------------------------------
+# Fused SwiGLU MLP (one launch)
+# ---------------------------------------------------------------------------------------------
+_mlp_workspaces: dict = {}
+_mlp_plans: dict = {}
+
+
+def mlp_eligible(x: torch.Tensor, w12: torch.Tensor, w3: torch.Tensor, y: torch.Tensor | None = None) -> bool:
+    """True when the one-launch MLP kernel can take these operands (16-bit type, contiguous rows,
+    16-byte aligned bases and pitches, sizes that are multiples of 8)."""
+    ts = [x, w12, w3] + ([y] if y is not None else [])
+    if not all(t.is_cuda and t.dim() == 2 and t.dtype == x.dtype and t.stride(1) == 1
+               and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0 and t.shape[1] % 8 == 0 for t in ts):
+        return False
+    return (x.dtype in (torch.float16, torch.bfloat16) and w12.shape[0] == x.shape[1]
+            and w12.shape[1] == 2 * w3.shape[0] and x.shape[0] >= 1)
+
+
+def mlp_query(problem: MlpProblem, config: Config) -> MlpResources:
+    res = MlpResources()
+    raise_for(lib.tnx_swiglu_mlp_query(ctypes.byref(problem), ctypes.byref(config), ctypes.byref(res)))
+    return res
+
+
+def mlp_unit_order(m: int, d_model: int, d_ff: int, n_out: int, cfg: dict | None = None):
+    """The kernel's global work-unit order as a list of (down, row_tile, column_tile); computed
+    on the host by the library (no GPU needed)."""
+    problem = MlpProblem(m, d_model, d_ff, n_out, BF16, EPI_GLU_SILU, d_model, 2 * d_ff, n_out, n_out)
+    config = make_config(cfg)
+    total = lib.tnx_swiglu_mlp_unit_order(ctypes.byref(problem), ctypes.byref(config), None, 0)
+    if total < 0:
+        raise_for(-total)
+    buf = (ctypes.c_int32 * total)()
+    lib.tnx_swiglu_mlp_unit_order(ctypes.byref(problem), ctypes.byref(config), buf, total)
+    return [(v >> 30, (v >> 14) & 0xffff, v & 0x3fff) for v in buf]
+
+
+def launch_mlp(x: torch.Tensor, w12: torch.Tensor, w3: torch.Tensor, y: torch.Tensor,
+               cfg: dict | None = None, activation: int = EPI_GLU_SILU,
+               workspace: torch.Tensor | None = None, ring_bands: int | None = None) -> MlpResources:
+    """Enqueues y = (act(x W1) * (x W2)) W3 as ONE kernel (``tnx_swiglu_mlp``) on torch's current
+    stream.  The workspace (dependency counters + a ring of bands of the hidden activation) is a
+    cached per-(device, stream) tensor unless one is passed; ``ring_bands`` sizes the cached one
+    (default: the library's recommendation, three bands)."""
+    require_cuda(x, w12, w3, y)
+    if not mlp_eligible(x, w12, w3, y):
+        raise ValueError("the one-launch MLP needs 2-D fp16/bf16 CUDA tensors with contiguous rows, "
+                         "16-byte aligned bases and pitches, and w12 (K, 2F), w3 (F, N)")
+    m, d_model = x.shape
+    d_ff, n_out = w3.shape
+    if tuple(y.shape) != (m, n_out):
+        raise ValueError(f"output must be {(m, n_out)}, got {tuple(y.shape)}")
+    key = (m, d_model, d_ff, n_out, x.dtype, activation, x.stride(0), w12.stride(0), w3.stride(0),
+           y.stride(0), tuple(cfg.items()) if cfg else ())
+    plan = _mlp_plans.get(key)
+    if plan is None:
+        problem = MlpProblem(m, d_model, d_ff, n_out, DTYPES[x.dtype], activation, x.stride(0),
+                             w12.stride(0), w3.stride(0), y.stride(0))
+        config = make_config(cfg)
+        plan = _mlp_plans[key] = (problem, config, mlp_query(problem, config))
+    problem, config, res = plan
+    idx = x.device.index if x.device.index is not None else torch.cuda.current_device()
+    with torch.cuda.device(idx):
+        stream = torch.cuda.current_stream(idx).cuda_stream
+        if workspace is None:
+            want = int(res.workspace_bytes)
+            if ring_bands is not None:
+                band_bytes = (int(res.workspace_bytes) - int(res.min_workspace_bytes)) or 0
+                per_band = band_bytes if res.num_bands >= 3 else 0
+                if per_band:
+                    want = int(res.min_workspace_bytes) + (max(2, ring_bands) - 2) * per_band
+            wkey = (idx, stream)
+            workspace = _mlp_workspaces.get(wkey)
+            if workspace is None or workspace.numel() < want:
+                workspace = torch.empty(want, dtype=torch.uint8, device=torch.device("cuda", idx))
+                _mlp_workspaces[wkey] = workspace
+        rc = lib.tnx_swiglu_mlp(ctypes.byref(problem), ctypes.byref(config), x.data_ptr(), w12.data_ptr(),
+                                w3.data_ptr(), y.data_ptr(), workspace.data_ptr(), workspace.numel(),
+                                status_word(x.device).data_ptr(), stream)
+    raise_for(rc)
+    return res
 
 
 # ---------------------------------------------------------------------------------------------

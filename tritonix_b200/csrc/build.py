@@ -16,7 +16,8 @@ CSRC = Path(__file__).resolve().parent
 PKG = CSRC.parent
 LIB_DIR = PKG / "lib"
 LIB_PATH = LIB_DIR / "libtritonix_b200.so"
-SOURCES = ["tnx_api.cu", "tnx_umma_gemm.cu", "tnx_strided_gemm.cu", "tnx_conv2d.cu"]
+SOURCES = ["tnx_api.cu", "tnx_umma_gemm.cu", "tnx_strided_gemm.cu", "tnx_conv2d.cu",
+           "tnx_swiglu_mlp.cu"]
 HEADERS = ["tnx_ptx.cuh", "tnx_internal.h", "../../include/tritonix_b200.h"]
 
 NVCC_FLAGS = [

@@ -1,5 +1,6 @@
 // Declarations shared by the translation units of libtritonix_b200.so (not part of the ABI).
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -22,6 +23,15 @@ int umma_query(const tnx_problem& p, tnx_config* cfg, tnx_resources* out);
 int umma_launch(const tnx_problem& p, const tnx_config& cfg, const tnx_resources& res,
                 const void* a, const void* b, void* c, void* workspace, const int32_t* tile_table,
                 int32_t* status_word, cudaStream_t stream);
+
+// Helpers of the tcgen05 GEMM translation unit that other kernels of the library share.
+// 2-D row-major tensor of 16-bit elements -> tensor map with 128-byte swizzle: `cols` contiguous
+// elements per row, `rows` rows, `pitch_elems` between rows, boxes of box_cols x box_rows
+// (encoded maps are cached).  is_operand selects the L2 promotion used for loads.
+int make_tmap_2d(CUtensorMap* out, const void* ptr, int dtype, int64_t cols, int64_t rows,
+                 int64_t pitch_elems, int box_cols, int box_rows, bool is_operand);
+int sm_count();                             // SMs of the current device (148 when none is visible)
+unsigned long long bounded_wait_limit_ns(); // wall-clock limit of every device-side wait
 
 // True when the operands can use the TMA/tcgen05 path (16-bit type, unit inner strides,
 // 16-byte aligned row pitches).  Pointer alignment is checked at launch.

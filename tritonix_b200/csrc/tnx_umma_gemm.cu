@@ -1179,6 +1179,13 @@ inline int a_box_rows(const tnx_problem& p, const tnx_config& cfg) {
 
 }  // namespace
 
+int make_tmap_2d(CUtensorMap* out, const void* ptr, int dtype, int64_t cols, int64_t rows,
+                 int64_t pitch_elems, int box_cols, int box_rows, bool is_operand) {
+  return make_tmap(out, ptr, dtype, cols, rows, pitch_elems, box_cols, box_rows, is_operand);
+}
+int sm_count() { return device_sm_count(); }
+unsigned long long bounded_wait_limit_ns() { return wait_limit_ns(); }
+
 // Split-K slices can exchange partials through distributed shared memory when they fit one
 // portable cluster (2, 4 or 8 CTAs, one SM each) and a slice's fp32 partial fits the epilogue
 // staging area.  Then no workspace is needed at all.

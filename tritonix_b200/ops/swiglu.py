@@ -10,9 +10,11 @@ is the reference's behaviour for any non-"silu" value.
 
 ``swiglu_kernel`` has the call signature of the reference's three-matrix kernel
 (tritonix/ops/swiglu.py:113-230), Z = (silu(X.W1) * (X.W2)).W3.  The reference's version
-accumulates with atomics and indexes W3 incorrectly beyond one tile; here it is two
-deterministic launches (fused gate/up, then the down projection) with the intermediate kept
-in the input precision.
+accumulates with atomics and indexes W3 incorrectly beyond one tile; here it is ONE
+deterministic launch (``tnx_swiglu_mlp``: hidden-activation tiles and output tiles interleaved
+in one persistent kernel, the hidden activation kept in the input precision in a small ring
+that stays in L2) for fp16/bf16 operands with contiguous rows, and two launches (fused
+gate/up, then the down projection) for anything else.
 
 Host wrappers: ``glu``, ``swiglu``, ``swiglu_mlp``, ``interleave_weights``.
 """
@@ -52,12 +54,39 @@ class _SwigluMlpKernel(CudaKernel):
             stride_w3n, stride_w3l, stride_zm, stride_zl, grid=None, **cfg):
         activation = cfg.pop("activation", "silu")
         cfg.pop("block_l", None)
+        fused = cfg.pop("fused", True)
+        if fused and self._run_fused(x, w12, w3, z, m, n, k, f, stride_xm, stride_xk, stride_wk,
+                                     stride_wn, stride_w3n, stride_w3l, stride_zm, stride_zl,
+                                     activation, cfg):
+            return
         hidden = torch.empty((m, n // 2), device=x.device, dtype=x.dtype)
         glu_kernel[grid](x, w12, hidden, m, n, k, stride_xm, stride_xk, stride_wk, stride_wn,
                          hidden.stride(0), hidden.stride(1), activation=activation, **cfg)
         down_cfg = _mm.default_config(m, f, n // 2)
         _mm.matmul_kernel[grid](hidden, w3, z, m, f, n // 2, hidden.stride(0), hidden.stride(1),
                                 stride_w3n, stride_w3l, stride_zm, stride_zl, **down_cfg)
+
+
+    @staticmethod
+    def _run_fused(x, w12, w3, z, m, n, k, f, stride_xm, stride_xk, stride_wk, stride_wn, stride_w3n,
+                   stride_w3l, stride_zm, stride_zl, activation, cfg) -> bool:
+        """One launch when the operands qualify and the arguments describe the tensors as they
+        are; returns False to let the two-launch path take the call."""
+        tensors = all(isinstance(t, torch.Tensor) for t in (x, w12, w3, z))
+        if not tensors or not _cabi.mlp_eligible(x, w12, w3, z):
+            return False
+        if (tuple(x.shape) != (m, k) or tuple(w12.shape) != (k, n) or tuple(w3.shape) != (n // 2, f)
+                or tuple(z.shape) != (m, f)
+                or (stride_xm, stride_xk, stride_wk, stride_wn) != (*x.stride(), *w12.stride())
+                or (stride_w3n, stride_w3l, stride_zm, stride_zl) != (*w3.stride(), *z.stride())):
+            return False
+        keep = {"block_k": "tile_k", "tile_k": "tile_k", "num_stages": "stages", "stages": "stages",
+                "group_m": "group_m", "max_ctas": "max_ctas"}
+        mlp_cfg = {keep[key]: v for key, v in cfg.items() if key in keep}
+        if mlp_cfg.get("tile_k") not in (None, 64, 128):
+            return False
+        _cabi.launch_mlp(x, w12, w3, z, mlp_cfg, _cabi.ACTIVATIONS.get(activation, _cabi.EPI_GLU_LINEAR))
+        return True
 
 
 swiglu_kernel = tunable(
@@ -128,8 +157,17 @@ def swiglu(x: torch.Tensor, w12: torch.Tensor, cfg: dict | None = None,
 
 def swiglu_mlp(x: torch.Tensor, w12: torch.Tensor, w_down: torch.Tensor,
                cfg: dict | None = None, down_cfg: dict | None = None,
-               out: torch.Tensor | None = None) -> torch.Tensor:
-    """The SwiGLU MLP block (silu(x W1) * (x W2)) W_down as two launches."""
+               out: torch.Tensor | None = None, fused: bool = False,
+               fused_cfg: dict | None = None) -> torch.Tensor:
+    """The SwiGLU MLP block (silu(x W1) * (x W2)) W_down: two launches (fused gate/up, then the
+    down projection), or with ``fused=True`` the one-launch kernel (``fused_cfg``: tile_k,
+    stages, group_m = 256-row tiles per band)."""
+    if fused:
+        _cabi.require_cuda(x, w12, w_down)
+        y = out if out is not None else torch.empty((x.shape[0], w_down.shape[1]), device=x.device,
+                                                    dtype=x.dtype)
+        _cabi.launch_mlp(x, w12, w_down, y, fused_cfg, _cabi.EPI_GLU_SILU)
+        return y
     hidden = swiglu(x, w12, cfg=cfg)
     if down_cfg is not None:
         return _mm._launch_matmul(hidden, w_down, down_cfg, out)
