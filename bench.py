@@ -311,12 +311,16 @@ def _mlp_weight_blocks(dev, lo, hi):
     return wg, wu, wd
 
 
-def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1):
-    """SwiGLU MLP, tensor parallel: column-parallel fused gate/up, row-parallel down, one
-    all-reduce.  Global weights come from fixed seeds and are sliced, so every world size
-    computes the same function."""
+def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1, mode="auto", comm_ctas=4, band=4):
+    """SwiGLU MLP, tensor parallel: hidden units split over the ranks (column-parallel gate/up,
+    row-parallel down projection), partial outputs summed across the ranks.  Global weights come
+    from fixed seeds and are sliced, so every world size computes the same function.
+    Two implementations: "two_launch" = fused gate/up kernel + down GEMM per row chunk with a
+    chunked NCCL all-reduce on a side stream; "one_launch" = the one-launch MLP kernel, which on
+    several GPUs also sums the partial outputs itself (multimem over NVLink) while computing."""
     import tritonix_b200 as tnx
-    from tritonix_b200.distributed import TensorParallelSwiGLU, shard_bounds
+    from tritonix_b200.distributed import (FusedTensorParallelSwiGLU, TensorParallelSwiGLU,
+                                           shard_bounds)
     comm_sms = (32 if world >= 8 else 0) if comm_sms < 0 else comm_sms
     w = WORKLOADS["mlp"]
     m, d, ff, dt = w["m"], w["d"], w["ff"], torch.bfloat16
@@ -330,9 +334,35 @@ def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1):
         w12, wd, chunks=chunks if (isinstance(chunks, list) or chunks > 0) else (1 if world == 1 else 4),
         comm_sms=comm_sms, gate_up_cfg=GLU_CFG, down_cfg=GEMM_CFG)
     state = {}
+    fused_cfg = {"tile_k": 128, "stages": 3, "group_m": band}
+    fused = None
+    fused_note = None
+    if world > 1:
+        try:
+            fused = FusedTensorParallelSwiGLU(w12, wd, max_tokens=m, comm_ctas=comm_ctas, cfg=fused_cfg)
+        except Exception as exc:  # no multicast mapping on this system: the NCCL path remains
+            fused_note = f"{type(exc).__name__}: {exc}"[:200]
 
-    def step():
+    def step_two_launch():
         state["y"] = mlp(x)
+
+    def step_one_launch():
+        if world > 1:
+            state["y"] = fused(x)
+        else:
+            state["y"] = tnx.swiglu_mlp(x, w12, wd, fused=True, fused_cfg=fused_cfg)
+
+    one_launch_ok = world == 1 or fused is not None
+    if mode == "auto":
+        mode = "one_launch" if (world > 1 and fused is not None) else "two_launch"
+    if mode == "one_launch" and not one_launch_ok:
+        raise RuntimeError("the one-launch tensor-parallel MLP is unavailable: " + str(fused_note))
+    step = step_one_launch if mode == "one_launch" else step_two_launch
+    other = None
+    if mode == "one_launch":
+        other = ("two_launch", step_two_launch)
+    elif one_launch_ok:
+        other = ("one_launch", step_one_launch)
 
     x_host = x.cpu().pin_memory()
     y_host = torch.empty((m, d), dtype=dt).pin_memory()
@@ -362,9 +392,19 @@ def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1):
 
     flops = 2.0 * m * d * (2 * ff) + 2.0 * m * ff * d
     nchunks = len(mlp.chunk_bounds(m))
-    work = dict(flops=flops, bytes=None, units=float(m), launches=2 * nchunks, h2d=x_host.numel() * 2,
-                d2h=y_host.numel() * 2, copies=1, cfg={"gate_up": GLU_CFG, "down": GEMM_CFG},
-                chunks=nchunks, comm_sms=comm_sms, parity=parity)
+    if mode == "one_launch":
+        cfg = {"one_launch": dict(fused_cfg, tile_m=256, tile_n=256, cta_group=2)}
+        launches = 1
+        exchange = ("inside the kernel: multimem.ld_reduce / multimem.st per 256-row tile, %d exchanging CTAs"
+                    % comm_ctas) if world > 1 else "none (one GPU)"
+    else:
+        cfg = {"gate_up": GLU_CFG, "down": GEMM_CFG}
+        launches = 2 * nchunks
+        exchange = ("NCCL all-reduce per row chunk on a side stream (%d chunks, %d SMs left to it)"
+                    % (nchunks, comm_sms)) if world > 1 else "none (one GPU)"
+    work = dict(flops=flops, bytes=None, units=float(m), launches=launches, h2d=x_host.numel() * 2,
+                d2h=y_host.numel() * 2, copies=1, cfg=cfg, chunks=nchunks, comm_sms=comm_sms,
+                parity=parity, mode=mode, exchange=exchange, other=other, fused_note=fused_note)
     return step, e2e_step, work
 
 
@@ -452,7 +492,8 @@ def measure(workload, args, rank, local_rank, world, dev, D, peaks):
     import tritonix_b200 as tnx
     if workload == "mlp":
         chunks = [float(v) for v in args.chunk_weights.split(",")] if args.chunk_weights else args.chunks
-        step, e2e_step, work = setup_mlp(rank, world, dev, chunks, args.comm_sms)
+        step, e2e_step, work = setup_mlp(rank, world, dev, chunks, args.comm_sms, args.mlp_mode,
+                                         args.comm_ctas, args.mlp_band)
     elif workload == "conv":
         step, e2e_step, work = setup_conv(rank, world, dev, json.loads(args.cfg) if args.cfg else None)
     else:
@@ -518,8 +559,10 @@ def measure(workload, args, rank, local_rank, world, dev, D, peaks):
         "scaling": "strong" if strong else "weak", "dtype": WORKLOADS[workload]["dtype"],
         "config": {"workload": WORKLOADS[workload]["name"], "kernel_config": work["cfg"],
                    "kernel_config_source": CONFIG_SOURCE,
+                   **({"implementation": work["mode"], "exchange": work["exchange"]}
+                      if workload == "mlp" else {}),
                    **({"allreduce_chunks": work["chunks"], "comm_sms": work["comm_sms"]}
-                      if workload == "mlp" and world > 1 else {}),
+                      if workload == "mlp" and world > 1 and work["mode"] == "two_launch" else {}),
                    "parallelism": parallelism,
                    "launch": "cuda_graph_of_%d_steps" % args.steps if use_graph else "eager",
                    "l2": ("operands rotate through %d copies (> 3x L2)" % work["copies"]) if work["copies"] > 1
@@ -530,6 +573,16 @@ def measure(workload, args, rank, local_rank, world, dev, D, peaks):
         "clocks": clocks.summary(),
         "roofline": roof,
     }
+    if workload == "mlp" and work["other"] is not None:
+        # the other implementation of the same step, timed the same way (a comparison: `value`
+        # is the implementation named in config.implementation)
+        name, other_step = work["other"]
+        ms_other = D.max(time_steps(other_step, args.steps, args.warmup, D.barrier)) / args.steps
+        tnx.check_status(dev)
+        entry["variants"] = {work["mode"]: {"ms_per_step": ms_step, "value": value},
+                             name: {"ms_per_step": ms_other, "value": units / (ms_other * 1e-3)}}
+    if workload == "mlp" and work.get("fused_note"):
+        entry["one_launch_unavailable"] = work["fused_note"]
     if workload == "mlp":
         step()  # one more step outside any timed region; its output is what parity checks
         torch.cuda.synchronize(dev)
@@ -729,6 +782,14 @@ def main():
     ap.add_argument("--comm-sms", type=int, default=-1,
                     help="mlp on >1 GPU: SMs the GEMM grids leave free for the all-reduce kernel "
                          "(-1: 32 on 8 or more GPUs, else 0)")
+    ap.add_argument("--mlp-mode", choices=["auto", "two_launch", "one_launch"], default="auto",
+                    help="mlp: which implementation `value` times (auto: one_launch on several GPUs when "
+                         "the NVLink multicast mapping is available, else two_launch); the other one is "
+                         "timed too and reported under `variants`")
+    ap.add_argument("--comm-ctas", type=int, default=4,
+                    help="mlp one_launch on >1 GPU: CTAs that only exchange partial outputs")
+    ap.add_argument("--mlp-band", type=int, default=4,
+                    help="mlp one_launch: 256-row tiles per band")
     ap.add_argument("--launch", choices=["auto", "eager", "graph"], default="auto",
                     help="how the timed steps are issued: one by one, or as one CUDA graph of "
                          "`steps` launches (auto: graph for the launch-latency-bound splitk workload)")

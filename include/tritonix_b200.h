@@ -217,6 +217,35 @@ typedef struct tnx_mlp_resources {
   int64_t workspace_bytes;     /* recommended: counters + three bands                           */
 } tnx_mlp_resources;
 
+/*
+ * Tensor-parallel use: the hidden dimension is split over `world` GPUs (rank r holds columns
+ * [2 r F/p, 2 (r+1) F/p) of W12 and rows [r F/p, (r+1) F/p) of W3, d_ff = F/p in the problem), so
+ * every rank computes a partial Y; the kernel then sums the partials itself, row tile by row
+ * tile while later tiles are still being computed, through an NVLink multicast mapping
+ * (multimem.ld_reduce / multimem.st), and every rank ends up with the full Y.  No counterpart in
+ * the reference (it has no multi-GPU code).  Requirements, all the caller's to set up:
+ *   - `y` (the pointer passed to tnx_swiglu_mlp) is this rank's mapping of a buffer that every
+ *     rank allocated symmetrically and bound to ONE multicast object; y_multicast is the
+ *     multicast address of the same bytes;
+ *   - signal_local / signal_multicast: likewise for an array of (m + 255) / 256 + 1 uint32
+ *     counters, zero before the first call and never written by the caller afterwards;
+ *   - epoch: 1 for the first call on these buffers, 2 for the second, ... identical on every
+ *     rank (counters are never reset; call number e waits for e * world arrivals).  After a
+ *     call that reported TNX_ERR_DEVICE the counters are undefined: zero them on every rank and
+ *     restart at 1;
+ *   - every rank makes the same sequence of calls with the same m, n_out and comm_ctas.
+ * comm_ctas CTAs (even; 0 = 4) take no tiles and only exchange; the persistent grid shrinks
+ * accordingly.
+ */
+typedef struct tnx_mlp_exchange {
+  int32_t world, rank;
+  int32_t comm_ctas;
+  uint32_t epoch;
+  void* y_multicast;
+  uint32_t* signal_multicast;
+  const uint32_t* signal_local;
+} tnx_mlp_exchange;
+
 /* Validates (problem, config) and reports what the launch needs.  `config` may be NULL; used
  * fields: tile_k (64 or 128), stages, group_m (256-row tiles per band, default 4), max_ctas.
  * tile_m / tile_n / cta_group, if set, must be 256 / 256 / 2. */
@@ -241,11 +270,13 @@ int tnx_swiglu_mlp_unit_order(const tnx_mlp_problem* problem, const tnx_config* 
  * Its content before and after the call is meaningless.  Calls sharing a workspace must be
  * ordered on one stream.  The kernel's CTAs wait for one another through the counters (bounded
  * waits that report through `status_word`), so the launch is sized to what the GPU can hold
- * at once.
+ * at once.  With `exchange` the grid query of tnx_swiglu_mlp_query does not include the
+ * exchanging CTAs.
  */
 int tnx_swiglu_mlp(const tnx_mlp_problem* problem, const tnx_config* config, const void* x,
                    const void* w12, const void* w3, void* y, void* workspace,
-                   size_t workspace_bytes, int32_t* status_word, void* stream);
+                   size_t workspace_bytes, const tnx_mlp_exchange* exchange /* NULL: one GPU */,
+                   int32_t* status_word, void* stream);
 
 /*
  * Synchronises `stream`, copies *status_word to the host and returns TNX_OK if it is zero,

@@ -1,14 +1,16 @@
-"""Two-GPU runs of the sharded layouts with the real kernels and NCCL: the tensor-parallel
-SwiGLU MLP (column-parallel fused gate/up, row-parallel down projection, one chunked
-all-reduce) and the row-sharded GEMM (no collective).  Skipped with fewer than two GPUs."""
+"""Multi-process runs of the sharded layouts with the real kernels: the tensor-parallel SwiGLU
+MLP — column-parallel fused gate/up, row-parallel down projection, partial outputs summed either
+by one chunked NCCL all-reduce or inside the one-launch MLP kernel over an NVLink multicast
+mapping — and the row-sharded GEMM (no collective).  The two-rank tests are skipped with fewer
+than two GPUs; the one-rank test runs the in-kernel exchange protocol with a single participant."""
 import os
 import socket
 
 import pytest
 import torch
 
-pytestmark = [pytest.mark.gpu,
-              pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")]
+pytestmark = pytest.mark.gpu
+two_gpus = pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 
 
 def _free_port():
@@ -58,6 +60,7 @@ def _worker(rank, world, port, out_dir):
         dist.destroy_process_group()
 
 
+@two_gpus
 def test_tensor_parallel_mlp_and_row_sharded_gemm(tmp_path):
     import torch.multiprocessing as mp
     world = 2
@@ -65,3 +68,70 @@ def test_tensor_parallel_mlp_and_row_sharded_gemm(tmp_path):
     for r in range(world):
         res = torch.load(tmp_path / f"r{r}.pt")
         assert res["err_mlp"] <= 8e-3 and res["err_mm"] <= 8e-3 and res["same"], res
+
+
+def _fused_worker(rank, world, port, out_dir):
+    import torch.distributed as dist
+
+    import tritonix_b200 as tnx
+    from oracle import contraction as O
+    from tritonix_b200.distributed import FusedTensorParallelSwiGLU, shard_mlp_weights
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), TRITONIX_B200_TUNE="0")
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    result = {}
+    try:
+        g = torch.Generator().manual_seed(77)  # identical global tensors on every rank
+        m, d, ff = 2304, 512, 2048             # nine 256-row tiles: the last band is short
+        bf16 = torch.bfloat16
+        x = torch.randn(m, d, generator=g).to(bf16)
+        wg = (torch.randn(d, ff, generator=g) * 0.05).to(bf16)
+        wu = (torch.randn(d, ff, generator=g) * 0.05).to(bf16)
+        wd = (torch.randn(ff, d, generator=g) * 0.05).to(bf16)
+        w12, wdr = shard_mlp_weights(wg, wu, wd, rank, world)
+        try:
+            mlp = FusedTensorParallelSwiGLU(w12.to(dev), wdr.to(dev), max_tokens=m, comm_ctas=4,
+                                            cfg={"group_m": 2})
+        except RuntimeError as exc:
+            result["skip"] = str(exc)
+        else:
+            ref = O.swiglu_mlp_oracle(x, torch.stack((wg, wu), 2).reshape(d, 2 * ff), wd)
+            xd = x.to(dev)
+            outs = []
+            for _ in range(3):                 # the counters are never reset: epochs 1, 2, 3
+                y = mlp(xd)
+                tnx.check_status(dev)
+                outs.append(y.clone())
+            result["err"] = max(O.rel_err(o.cpu(), ref) for o in outs)
+            result["repeatable"] = all(torch.equal(outs[0], o) for o in outs[1:])
+            gathered = [torch.empty_like(outs[0]) for _ in range(world)]
+            dist.all_gather(gathered, outs[0])
+            result["same"] = all(torch.equal(gathered[0], t) for t in gathered)
+            short = mlp(xd[:700])              # fewer tokens than the instance was sized for
+            tnx.check_status(dev)
+            result["err_short"] = O.rel_err(short.cpu(), ref[:700])
+        torch.save(result, os.path.join(out_dir, f"f{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def _run_fused(world, tmp_path):
+    import torch.multiprocessing as mp
+    mp.spawn(_fused_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    results = [torch.load(tmp_path / f"f{r}.pt") for r in range(world)]
+    if any("skip" in r for r in results):
+        pytest.skip(results[0].get("skip", "no multicast support"))
+    for res in results:
+        assert res["err"] <= 8e-3 and res["err_short"] <= 8e-3 and res["repeatable"] and res["same"], res
+
+
+def test_in_kernel_exchange_with_one_participant(tmp_path):
+    """World size 1: the exchanging CTAs run the whole protocol (row-tile counters, multicast
+    signals, multimem sum and store, closing barrier, epochs) with a single rank."""
+    _run_fused(1, tmp_path)
+
+
+@two_gpus
+def test_in_kernel_exchange_between_two_ranks(tmp_path):
+    _run_fused(2, tmp_path)

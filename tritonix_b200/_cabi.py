@@ -93,6 +93,12 @@ class MlpResources(ctypes.Structure):
         [("min_workspace_bytes", ctypes.c_int64), ("workspace_bytes", ctypes.c_int64)]
 
 
+class MlpExchange(ctypes.Structure):
+    _fields_ = [("world", ctypes.c_int32), ("rank", ctypes.c_int32), ("comm_ctas", ctypes.c_int32),
+                ("epoch", ctypes.c_uint32), ("y_multicast", ctypes.c_void_p),
+                ("signal_multicast", ctypes.c_void_p), ("signal_local", ctypes.c_void_p)]
+
+
 LAYOUT_NCHW, LAYOUT_NHWC = 0, 1
 WEIGHT_KCRS, WEIGHT_PACKED = 0, 1
 
@@ -146,7 +152,8 @@ def _load() -> ctypes.CDLL:
     lib.tnx_swiglu_mlp.restype = ctypes.c_int
     lib.tnx_swiglu_mlp.argtypes = [ctypes.POINTER(MlpProblem), ctypes.POINTER(Config),
                                    ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
-                                   ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_void_p]
+                                   ctypes.c_void_p, ctypes.c_size_t, ctypes.POINTER(MlpExchange),
+                                   ctypes.c_void_p, ctypes.c_void_p]
     lib.tnx_conv2d_query.restype = ctypes.c_int
     lib.tnx_conv2d_query.argtypes = [ctypes.POINTER(ConvProblem), ctypes.POINTER(Config),
                                      ctypes.POINTER(ConvResources)]
@@ -463,11 +470,13 @@ def mlp_unit_order(m: int, d_model: int, d_ff: int, n_out: int, cfg: dict | None
 
 def launch_mlp(x: torch.Tensor, w12: torch.Tensor, w3: torch.Tensor, y: torch.Tensor,
                cfg: dict | None = None, activation: int = EPI_GLU_SILU,
-               workspace: torch.Tensor | None = None, ring_bands: int | None = None) -> MlpResources:
+               workspace: torch.Tensor | None = None, ring_bands: int | None = None,
+               exchange: MlpExchange | None = None) -> MlpResources:
     """Enqueues y = (act(x W1) * (x W2)) W3 as ONE kernel (``tnx_swiglu_mlp``) on torch's current
     stream.  The workspace (dependency counters + a ring of bands of the hidden activation) is a
     cached per-(device, stream) tensor unless one is passed; ``ring_bands`` sizes the cached one
-    (default: the library's recommendation, three bands)."""
+    (default: the library's recommendation, three bands).  ``exchange`` describes the
+    tensor-parallel sum of the ranks' partial outputs inside the kernel (``tnx_mlp_exchange``)."""
     require_cuda(x, w12, w3, y)
     if not mlp_eligible(x, w12, w3, y):
         raise ValueError("the one-launch MLP needs 2-D fp16/bf16 CUDA tensors with contiguous rows, "
@@ -502,6 +511,7 @@ def launch_mlp(x: torch.Tensor, w12: torch.Tensor, w3: torch.Tensor, y: torch.Te
                 _mlp_workspaces[wkey] = workspace
         rc = lib.tnx_swiglu_mlp(ctypes.byref(problem), ctypes.byref(config), x.data_ptr(), w12.data_ptr(),
                                 w3.data_ptr(), y.data_ptr(), workspace.data_ptr(), workspace.numel(),
+                                ctypes.byref(exchange) if exchange is not None else None,
                                 status_word(x.device).data_ptr(), stream)
     raise_for(rc)
     return res

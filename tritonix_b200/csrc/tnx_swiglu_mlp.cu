@@ -25,6 +25,17 @@
 //    what is resident at once, so the unit with the smallest index never waits: no deadlock.
 //    Every wait is bounded all the same (wall clock), and gives up through the status word.
 //  * Deterministic: no atomics on data, fixed summation order per tile.
+//  * Tensor parallel (optional): when the hidden dimension is split over `world` GPUs, every rank
+//    computes a partial Y and the partials must be summed.  The sum runs INSIDE this kernel, row
+//    tile by row tile, while later tiles are still being computed: the last few CTAs of the grid
+//    take no tiles; they watch a third counter (y_done: output tiles of a row tile stored), tell
+//    the other ranks through a multicast counter (multimem.red), wait until every rank has the
+//    row tile, and then sum their 1/world share of its rows across all ranks with
+//    multimem.ld_reduce (fp32 accumulation in the NVSwitch) and write the result to all ranks
+//    with multimem.st.  Y and the counters live in symmetric memory mapped into one multicast
+//    object; no TMA operation touches another GPU's memory.  The computing CTAs never wait for the
+//    exchanging ones.  Cross-rank counters are never reset: call number `epoch` waits for
+//    epoch * world arrivals.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -44,7 +55,8 @@ namespace {
 constexpr int kRows = 128;       // rows per CTA (TMEM lanes); a pair owns 256
 constexpr int kTileN = 256;      // accumulator columns per unit
 constexpr int kLoadN = 128;      // B columns each CTA of the pair loads
-constexpr int kThreads = 192;
+constexpr int kThreads = 192;         // producer warp, MMA warp, four epilogue warps
+constexpr int kExchangeThreads = 512; // block size of a tensor-parallel launch: more loads in flight per exchanging CTA
 constexpr int kEpiThreads = 128;
 constexpr int kEpiBarrier = 1;
 constexpr int kAtomBytes = 128;
@@ -57,6 +69,7 @@ constexpr int kAlignSlack = 1024;
 constexpr int kAbortProducer = 0x201;
 constexpr int kAbortMma = 0x202;
 constexpr int kAbortEpilogue = 0x203;
+constexpr int kAbortExchange = 0x204;
 
 struct MlpParams {
   int m, d_model, d_ff, n_out;
@@ -73,6 +86,15 @@ struct MlpParams {
   int* d_done;             // [tiles_m] CTAs that finished a D unit of the row tile
   int* status;
   unsigned long long timeout_ns;
+  // tensor-parallel exchange (world == 1: none of this is used)
+  int world, rank;
+  int comm_ctas;           // CTAs at the end of the grid that only exchange (even: whole clusters)
+  int* y_done;             // [tiles_m] CTAs that finished STORING a D unit of the row tile
+  void* y_mc;              // multicast address of Y (the same buffer on every rank)
+  long long ldy;           // row pitch of Y in elements
+  unsigned* sig_mc;        // [tiles_m + 1] arrival counters: multicast address ...
+  const unsigned* sig_local;  // ... and this rank's copy
+  unsigned epoch;          // ordinal of this call (1, 2, ...)
 };
 
 struct Ctrl {
@@ -161,6 +183,57 @@ __device__ __forceinline__ bool wait_counter(const int* counter, int target, vol
   }
 }
 
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* ptr) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+  return v;
+}
+// Same bounded wait on a counter that other GPUs increment.
+__device__ __forceinline__ bool wait_counter_sys(const unsigned* counter, unsigned target,
+                                                 volatile int* abort_flag, const int* status,
+                                                 uint64_t limit_ns) {
+  if (ld_acquire_sys(counter) >= target) return true;
+  const uint64_t t0 = ptx::globaltimer_ns();
+  for (uint32_t it = 1;; ++it) {
+    if (ld_acquire_sys(counter) >= target) return true;
+    __nanosleep(200);
+    if ((it & 0x3fu) == 0) {
+      if (*abort_flag != 0) return false;
+      if ((status != nullptr && ld_acquire_gpu(status) != 0) ||
+          ptx::globaltimer_ns() - t0 > limit_ns) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+// Adds 1 to the counter's copy on every GPU of the multicast object; earlier writes of this
+// thread (and those it has observed) are visible to whoever acquires the new value.
+__device__ __forceinline__ void multimem_signal(unsigned* mc_counter) {
+  asm volatile("multimem.red.release.sys.global.add.u32 [%0], 1;" ::"l"(mc_counter) : "memory");
+}
+// 16 bytes (eight 16-bit values) summed over all GPUs with fp32 accumulation in the switch.
+template <bool BF16>
+__device__ __forceinline__ uint4 multimem_sum(const void* mc_addr) {
+  uint4 v;
+  if (BF16)
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(mc_addr)
+                 : "memory");
+  else
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(mc_addr)
+                 : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_store(void* mc_addr, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr),
+               "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
 __device__ __forceinline__ float gate_act(float g, int epilogue) {
   if (epilogue == TNX_EPI_GLU_LINEAR) return g;
   const float s = __fdividef(1.0f, 1.0f + __expf(-g));
@@ -186,7 +259,7 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
 }
 
 template <int TILE_K, bool BF16>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kExchangeThreads, 1)
 swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w12,
                   const __grid_constant__ CUtensorMap tmap_h_st, const __grid_constant__ CUtensorMap tmap_h_ld,
                   const __grid_constant__ CUtensorMap tmap_w3, const __grid_constant__ CUtensorMap tmap_y,
@@ -209,7 +282,9 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
   const uint32_t cta_rank = ptx::cluster_ctarank();
   const bool leader = cta_rank == 0;
   const int cluster_id = blockIdx.x >> 1;
-  const int num_clusters = gridDim.x >> 1;
+  // the last comm_ctas CTAs (whole clusters) exchange instead of computing
+  const int num_clusters = (static_cast<int>(gridDim.x) - p.comm_ctas) >> 1;
+  const bool exchanging = static_cast<int>(blockIdx.x) >= static_cast<int>(gridDim.x) - p.comm_ctas;
   volatile int* abort_flag = &ctrl->abort;
 
   if (threadIdx.x == 0) {
@@ -243,7 +318,64 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = ctrl->tmem_base;
 
-  if (warp == 0) {
+  if (exchanging) {
+    // ===== cross-rank sum of Y, row tile by row tile (every thread of the CTA) =====
+    const int c = static_cast<int>(blockIdx.x) - (static_cast<int>(gridDim.x) - p.comm_ctas);
+    const int rows_per_rank = (2 * kRows) / p.world;
+    const int vec_per_row = p.n_out >> 3;  // 16-byte vectors per row
+    char* y_mc = static_cast<char*>(p.y_mc);
+    bool ok = true;
+    for (int t = c; t < p.tiles_m && ok; t += p.comm_ctas) {
+      if (threadIdx.x == 0) {
+        // this rank's partial rows are complete (every output tile of the row tile is stored) ...
+        bool got = wait_counter(p.y_done + t, 2 * p.n_d, abort_flag, p.status, p.timeout_ns);
+        if (got) {
+          multimem_signal(p.sig_mc + t);  // ... tell every rank ...
+          // ... and wait until every rank has said the same in this call
+          got = wait_counter_sys(p.sig_local + t, p.epoch * static_cast<unsigned>(p.world), abort_flag,
+                                 p.status, p.timeout_ns);
+        }
+        ctrl->flag = got ? 1 : 0;
+      }
+      __syncthreads();
+      ok = ctrl->flag != 0;
+      if (ok) {
+        const int row_lo = t * 2 * kRows + p.rank * rows_per_rank;
+        const int rows = min(rows_per_rank, p.m - row_lo);
+        const int total = rows > 0 ? rows * vec_per_row : 0;
+        constexpr int kInFlight = 8;
+        for (int base = threadIdx.x; base < total; base += blockDim.x * kInFlight) {
+          uint4 v[kInFlight];
+          size_t off[kInFlight];
+#pragma unroll
+          for (int i = 0; i < kInFlight; ++i) {
+            const int idx = base + i * static_cast<int>(blockDim.x);
+            const int safe = idx < total ? idx : base;
+            const int r = safe / vec_per_row;
+            off[i] = (static_cast<size_t>(row_lo + r) * p.ldy + static_cast<size_t>(safe - r * vec_per_row) * 8) * 2;
+            v[i] = multimem_sum<BF16>(y_mc + off[i]);
+          }
+#pragma unroll
+          for (int i = 0; i < kInFlight; ++i)
+            if (base + i * static_cast<int>(blockDim.x) < total) multimem_store(y_mc + off[i], v[i]);
+        }
+      }
+      __syncthreads();  // ctrl->flag is rewritten for the next row tile
+    }
+    // Every rank leaves only when all ranks have written all their shares: Y is complete
+    // everywhere, and nobody still reads this rank's partial rows.
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      if (ok) {
+        multimem_signal(p.sig_mc + p.tiles_m);
+        ok = wait_counter_sys(p.sig_local + p.tiles_m,
+                              p.epoch * static_cast<unsigned>(p.world) * static_cast<unsigned>(p.comm_ctas),
+                              abort_flag, p.status, p.timeout_ns);
+      }
+      if (!ok && p.status != nullptr) atomicCAS(p.status, 0, kAbortExchange);
+    }
+  } else if (warp == 0) {
     // ===== TMA producer =====
     if (lane == 0) {
       int stage = 0;
@@ -354,7 +486,7 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
       }
       if (!ok && p.status != nullptr) atomicCAS(p.status, 0, kAbortMma);
     }
-  } else {
+  } else if (warp < 6) {
     // ===== epilogue =====
     const int quarter = warp & 3;
     const int row_in_tile = quarter * 32 + lane;
@@ -460,13 +592,13 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
         acc = 0;
         acc_phase ^= 1u;
       }
-      if (!un.down && epi_tid == 0) {
-        // Publish this CTA's part of H: the stores must have landed (not merely have been read
-        // out of shared memory) before the counter moves.
+      if ((!un.down || p.comm_ctas > 0) && epi_tid == 0) {
+        // Publish this CTA's part of H (or, when ranks exchange, of Y): the stores must have
+        // landed (not merely have been read out of shared memory) before the counter moves.
         ptx::tma_store_wait_all<0>();
         fence_proxy_async_global();
         __threadfence();
-        atomicAdd(p.g_done + un.t, 1);
+        atomicAdd((un.down ? p.y_done : p.g_done) + un.t, 1);
       }
     }
     if (epi_tid == 0) ptx::tma_store_wait_all<0>();
@@ -510,7 +642,8 @@ struct MlpPlan {
   int64_t counter_bytes, band_bytes;
 };
 
-int plan_mlp(const tnx_mlp_problem* p, const tnx_config* config, MlpPlan* plan, tnx_mlp_resources* out) {
+int plan_mlp(const tnx_mlp_problem* p, const tnx_config* config, MlpPlan* plan, tnx_mlp_resources* out,
+             int comm_ctas = 0) {
   if (p == nullptr || out == nullptr) {
     set_error("problem or out is NULL");
     return TNX_ERR_INVALID;
@@ -571,7 +704,7 @@ int plan_mlp(const tnx_mlp_problem* p, const tnx_config* config, MlpPlan* plan, 
   plan->num_bands = cdiv(plan->tiles_m, plan->band);
   plan->last_rows = plan->tiles_m - (plan->num_bands - 1) * plan->band;
   plan->ring_bands_min = plan->num_bands < 2 ? plan->num_bands : 2;
-  plan->counter_bytes = align256(2LL * plan->tiles_m * 4);
+  plan->counter_bytes = align256(3LL * plan->tiles_m * 4);
   plan->band_bytes = static_cast<int64_t>(plan->band) * 2 * kRows * p->d_ff * 2;
 
   out->smem_bytes = static_cast<int32_t>(smem > 0x7fffffff ? 0x7fffffff : smem);
@@ -580,10 +713,10 @@ int plan_mlp(const tnx_mlp_problem* p, const tnx_config* config, MlpPlan* plan, 
   out->band_rows = plan->band * 2 * kRows;
   out->num_bands = plan->num_bands;
   const long long units = static_cast<long long>(plan->tiles_m) * (plan->n_g + plan->n_d);
-  int clusters = sm_count() / 2;
-  if (cfg.max_ctas > 0 && cfg.max_ctas / 2 < clusters) clusters = cfg.max_ctas / 2;
+  int clusters = (sm_count() - comm_ctas) / 2;  // exchanging CTAs take SMs of their own
+  if (cfg.max_ctas > 0 && (cfg.max_ctas - comm_ctas) / 2 < clusters) clusters = (cfg.max_ctas - comm_ctas) / 2;
   if (clusters < 1) clusters = 1;
-  out->grid = static_cast<int32_t>((units < clusters ? units : clusters) * 2);
+  out->grid = static_cast<int32_t>((units < clusters ? units : clusters) * 2 + comm_ctas);
   out->min_workspace_bytes = plan->counter_bytes + plan->ring_bands_min * plan->band_bytes;
   // three bands keep a slot's previous readers a whole band of work behind its next writers
   const int want = plan->num_bands < 3 ? plan->num_bands : 3;
@@ -650,12 +783,30 @@ int tnx_swiglu_mlp_unit_order(const tnx_mlp_problem* problem, const tnx_config* 
 }
 
 int tnx_swiglu_mlp(const tnx_mlp_problem* problem, const tnx_config* config, const void* x, const void* w12,
-                   const void* w3, void* y, void* workspace, size_t workspace_bytes, int32_t* status_word,
-                   void* stream) {
+                   const void* w3, void* y, void* workspace, size_t workspace_bytes,
+                   const tnx_mlp_exchange* exchange, int32_t* status_word, void* stream) {
   using namespace tnx;
   MlpPlan plan;
   tnx_mlp_resources res;
-  int rc = plan_mlp(problem, config, &plan, &res);
+  int comm_ctas = 0;
+  // (world == 1 with comm_ctas > 0 is the degenerate exchange: same protocol, one participant)
+  if (exchange != nullptr && (exchange->world > 1 || exchange->comm_ctas > 0)) {
+    const tnx_mlp_exchange& ex = *exchange;
+    comm_ctas = ex.comm_ctas > 0 ? ex.comm_ctas : 4;
+    if (ex.world < 1 || ex.world > 2 * kRows || (2 * kRows) % ex.world != 0 || ex.rank < 0 || ex.rank >= ex.world ||
+        (comm_ctas % 2) != 0 || comm_ctas > 64 || ex.epoch == 0) {
+      set_error("exchange: world must divide 256, 0 <= rank < world, comm_ctas even and <= 64, epoch >= 1 "
+                "(got world=%d rank=%d comm_ctas=%d epoch=%u)", ex.world, ex.rank, comm_ctas, ex.epoch);
+      return TNX_ERR_INVALID;
+    }
+    if (ex.y_multicast == nullptr || ex.signal_multicast == nullptr || ex.signal_local == nullptr ||
+        (reinterpret_cast<uintptr_t>(ex.y_multicast) & 15u) ||
+        (reinterpret_cast<uintptr_t>(ex.signal_multicast) & 3u)) {
+      set_error("exchange: y_multicast (16-byte aligned), signal_multicast and signal_local must be set");
+      return TNX_ERR_INVALID;
+    }
+  }
+  int rc = plan_mlp(problem, config, &plan, &res, comm_ctas);
   if (rc != TNX_OK) return rc;
   if (x == nullptr || w12 == nullptr || w3 == nullptr || y == nullptr || workspace == nullptr) {
     set_error("NULL operand or workspace pointer");
@@ -716,6 +867,18 @@ int tnx_swiglu_mlp(const tnx_mlp_problem* problem, const tnx_config* config, con
   kp.d_done = counters + plan.tiles_m;
   kp.status = status_word;
   kp.timeout_ns = bounded_wait_limit_ns();
+  kp.world = 1;
+  kp.y_done = counters + 2 * plan.tiles_m;
+  if (comm_ctas > 0) {
+    kp.world = exchange->world;
+    kp.rank = exchange->rank;
+    kp.comm_ctas = comm_ctas;
+    kp.y_mc = exchange->y_multicast;
+    kp.ldy = p.stride_ym;
+    kp.sig_mc = exchange->signal_multicast;
+    kp.sig_local = exchange->signal_local;
+    kp.epoch = exchange->epoch;
+  }
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t e = allow_full_smem_mlp(fn);
@@ -727,7 +890,7 @@ int tnx_swiglu_mlp(const tnx_mlp_problem* problem, const tnx_config* config, con
   }
   cudaLaunchConfig_t lc = {};
   lc.gridDim = dim3(res.grid, 1, 1);
-  lc.blockDim = dim3(kThreads, 1, 1);
+  lc.blockDim = dim3(comm_ctas > 0 ? kExchangeThreads : kThreads, 1, 1);
   lc.dynamicSmemBytes = res.smem_bytes;
   lc.stream = s;
   cudaLaunchAttribute attr[1];
@@ -745,7 +908,12 @@ int tnx_swiglu_mlp(const tnx_mlp_problem* problem, const tnx_config* config, con
     (void)cudaGetLastError();
     return TNX_ERR_CUDA;
   }
+  // (the exchanging CTAs are the last of the grid, whatever its size; at least one cluster computes)
   if (static_cast<int>(lc.gridDim.x) > fit * 2) lc.gridDim.x = static_cast<unsigned>(fit * 2);
+  if (static_cast<int>(lc.gridDim.x) < comm_ctas + 2) {
+    set_error("the GPU cannot hold %d exchanging CTAs next to a computing cluster", comm_ctas);
+    return TNX_ERR_CUDA;
+  }
   e = cudaLaunchKernelEx(&lc, fn, tx, tw12, thst, thld, tw3, ty, kp);
   if (e != cudaSuccess) {
     set_error("kernel launch failed: %s", cudaGetErrorString(e));

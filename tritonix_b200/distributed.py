@@ -188,3 +188,85 @@ class TensorParallelSwiGLU:
         return y
 
     __call__ = forward
+
+
+class FusedTensorParallelSwiGLU:
+    """The tensor-parallel SwiGLU MLP as ONE kernel per rank and step: the one-launch MLP kernel
+    (``tnx_swiglu_mlp``) computes this rank's hidden units and its partial output row tile by row
+    tile, and a few of its CTAs sum the partial outputs across the ranks as the row tiles
+    complete — ``multimem.ld_reduce`` / ``multimem.st`` through an NVLink multicast mapping of the
+    output buffer — so the exchange is spread over the whole step instead of following it.  No
+    collective library call is made in ``forward``.
+
+    The output buffer and the exchange counters live in symmetric memory
+    (``torch.distributed._symmetric_memory``: the same allocation on every rank, bound to one
+    multicast object).  ``forward`` returns a view of that buffer: it holds the full result on
+    every rank and is overwritten by the next call.  Needs NVSwitch multicast support; when it
+    is missing the constructor raises and ``TensorParallelSwiGLU`` (NCCL all-reduce) is the
+    alternative.
+
+    Every rank must call ``forward`` the same number of times with the same token count.
+    """
+
+    def __init__(self, w12_shard: torch.Tensor, w_down_shard: torch.Tensor, max_tokens: int,
+                 group: Optional[dist.ProcessGroup] = None, comm_ctas: int = 4,
+                 cfg: Optional[dict] = None):
+        import torch.distributed._symmetric_memory as symm
+
+        from tritonix_b200 import _cabi
+        if w12_shard.shape[1] != 2 * w_down_shard.shape[0]:
+            raise ValueError("w12 shard must have twice as many columns as w_down shard has rows")
+        self._cabi = _cabi
+        self.w12, self.w_down = w12_shard, w_down_shard
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        if 256 % self.world:
+            raise ValueError("the in-kernel exchange splits 256-row tiles over the ranks: "
+                             f"world size {self.world} does not divide 256")
+        self.comm_ctas = int(comm_ctas)
+        self.cfg = dict(cfg or {})
+        self.d_out = w_down_shard.shape[1]
+        self.max_tokens = int(max_tokens)
+        dev, dtype = w12_shard.device, w12_shard.dtype
+        tiles = -(-self.max_tokens // 256)
+        self._y_bytes = tiles * 256 * self.d_out * dtype.itemsize
+        sig_bytes = (tiles + 1) * 4
+        total = self._y_bytes + -(-sig_bytes // 256) * 256
+        try:  # older releases need the group enabled explicitly; newer ones deprecate the call
+            symm.enable_symm_mem_for_group(self.group.group_name)
+        except Exception:
+            pass
+        self._buf = symm.empty(total, dtype=torch.uint8, device=dev)
+        self._handle = symm.rendezvous(self._buf, self.group.group_name)
+        mc = int(getattr(self._handle, "multicast_ptr", 0) or 0)
+        if mc == 0:
+            raise RuntimeError("symmetric memory on this system has no multicast mapping (NVSwitch "
+                               "multimem); use TensorParallelSwiGLU (NCCL all-reduce) instead")
+        self._mc = mc
+        self._epoch = 0
+        self.reset()
+
+    def reset(self) -> None:
+        """Zeroes the exchange counters on every rank and restarts the call count (collective;
+        needed after a call that raised ``DeviceStatusError``)."""
+        torch.cuda.synchronize(self._buf.device)
+        self._buf[self._y_bytes:].zero_()
+        torch.cuda.synchronize(self._buf.device)
+        self._handle.barrier()
+        torch.cuda.synchronize(self._buf.device)
+        self._epoch = 0
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        m = x.shape[0]
+        if m > self.max_tokens:
+            raise ValueError(f"{m} tokens exceed the {self.max_tokens} this instance was sized for")
+        cabi = self._cabi
+        y = self._buf[:m * self.d_out * x.element_size()].view(x.dtype).view(m, self.d_out)
+        self._epoch += 1
+        local = self._buf.data_ptr()
+        exchange = cabi.MlpExchange(self.world, self.rank, self.comm_ctas, self._epoch, self._mc,
+                                    self._mc + self._y_bytes, local + self._y_bytes)
+        cabi.launch_mlp(x, self.w12, self.w_down, y, self.cfg, cabi.EPI_GLU_SILU, exchange=exchange)
+        return y
+
+    __call__ = forward
