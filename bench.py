@@ -311,7 +311,7 @@ def _mlp_weight_blocks(dev, lo, hi):
     return wg, wu, wd
 
 
-def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1, mode="auto", comm_ctas=4, band=4):
+def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1, mode="auto", comm_ctas=4, band=8):
     """SwiGLU MLP, tensor parallel: hidden units split over the ranks (column-parallel gate/up,
     row-parallel down projection), partial outputs summed across the ranks.  Global weights come
     from fixed seeds and are sliced, so every world size computes the same function.
@@ -788,7 +788,7 @@ def main():
                          "timed too and reported under `variants`")
     ap.add_argument("--comm-ctas", type=int, default=4,
                     help="mlp one_launch on >1 GPU: CTAs that only exchange partial outputs")
-    ap.add_argument("--mlp-band", type=int, default=4,
+    ap.add_argument("--mlp-band", type=int, default=8,
                     help="mlp one_launch: 256-row tiles per band")
     ap.add_argument("--launch", choices=["auto", "eager", "graph"], default="auto",
                     help="how the timed steps are issued: one by one, or as one CUDA graph of "
@@ -841,7 +841,7 @@ def main():
         "dtype": entry["dtype"], "data": "synthetic", "config": entry["config"], "e2e": entry["e2e"],
         "gpu_launches": entry["gpu_launches"], "clocks": entry["clocks"], "roofline": entry["roofline"],
     }
-    for extra in ("sustained", "comparators", "parity_err", "parity"):
+    for extra in ("sustained", "comparators", "parity_err", "parity", "variants", "one_launch_unavailable"):
         if extra in entry:
             line[extra] = entry[extra]
     if rank == 0 and not args.no_cpu_baseline and world == 1:

@@ -214,7 +214,7 @@ typedef struct tnx_mlp_resources {
   int32_t band_rows;           /* rows of X per band = group_m * 256                            */
   int32_t num_bands;
   int64_t min_workspace_bytes; /* counters + two bands of the hidden activation (or all of it)  */
-  int64_t workspace_bytes;     /* recommended: counters + three bands                           */
+  int64_t workspace_bytes;     /* recommended size (currently the minimum: it measured best)    */
 } tnx_mlp_resources;
 
 /*
@@ -247,7 +247,7 @@ typedef struct tnx_mlp_exchange {
 } tnx_mlp_exchange;
 
 /* Validates (problem, config) and reports what the launch needs.  `config` may be NULL; used
- * fields: tile_k (64 or 128), stages, group_m (256-row tiles per band, default 4), max_ctas.
+ * fields: tile_k (64 or 128), stages, group_m (256-row tiles per band, default 8), max_ctas.
  * tile_m / tile_n / cta_group, if set, must be 256 / 256 / 2. */
 int tnx_swiglu_mlp_query(const tnx_mlp_problem* problem, const tnx_config* config,
                          tnx_mlp_resources* out);

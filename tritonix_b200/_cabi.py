@@ -475,7 +475,7 @@ def launch_mlp(x: torch.Tensor, w12: torch.Tensor, w3: torch.Tensor, y: torch.Te
     """Enqueues y = (act(x W1) * (x W2)) W3 as ONE kernel (``tnx_swiglu_mlp``) on torch's current
     stream.  The workspace (dependency counters + a ring of bands of the hidden activation) is a
     cached per-(device, stream) tensor unless one is passed; ``ring_bands`` sizes the cached one
-    (default: the library's recommendation, three bands).  ``exchange`` describes the
+    (default: the library's recommendation, two bands).  ``exchange`` describes the
     tensor-parallel sum of the ranks' partial outputs inside the kernel (``tnx_mlp_exchange``)."""
     require_cuda(x, w12, w3, y)
     if not mlp_eligible(x, w12, w3, y):
@@ -497,20 +497,20 @@ def launch_mlp(x: torch.Tensor, w12: torch.Tensor, w3: torch.Tensor, y: torch.Te
     idx = x.device.index if x.device.index is not None else torch.cuda.current_device()
     with torch.cuda.device(idx):
         stream = torch.cuda.current_stream(idx).cuda_stream
+        ws_bytes = workspace.numel() if workspace is not None else 0
         if workspace is None:
             want = int(res.workspace_bytes)
-            if ring_bands is not None:
-                band_bytes = (int(res.workspace_bytes) - int(res.min_workspace_bytes)) or 0
-                per_band = band_bytes if res.num_bands >= 3 else 0
-                if per_band:
-                    want = int(res.min_workspace_bytes) + (max(2, ring_bands) - 2) * per_band
+            if ring_bands is not None and res.num_bands > 2:
+                per_band = res.band_rows * d_ff * x.element_size()
+                want = int(res.min_workspace_bytes) + (min(max(2, ring_bands), res.num_bands) - 2) * per_band
             wkey = (idx, stream)
             workspace = _mlp_workspaces.get(wkey)
             if workspace is None or workspace.numel() < want:
                 workspace = torch.empty(want, dtype=torch.uint8, device=torch.device("cuda", idx))
                 _mlp_workspaces[wkey] = workspace
+            ws_bytes = want  # a larger cached buffer must not turn into a deeper ring
         rc = lib.tnx_swiglu_mlp(ctypes.byref(problem), ctypes.byref(config), x.data_ptr(), w12.data_ptr(),
-                                w3.data_ptr(), y.data_ptr(), workspace.data_ptr(), workspace.numel(),
+                                w3.data_ptr(), y.data_ptr(), workspace.data_ptr(), ws_bytes,
                                 ctypes.byref(exchange) if exchange is not None else None,
                                 status_word(x.device).data_ptr(), stream)
     raise_for(rc)

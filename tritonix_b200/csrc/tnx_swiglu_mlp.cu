@@ -674,7 +674,7 @@ int plan_mlp(const tnx_mlp_problem* p, const tnx_config* config, MlpPlan* plan, 
   if (cfg.tile_m == 0) cfg.tile_m = 256;
   if (cfg.tile_n == 0) cfg.tile_n = 256;
   if (cfg.cta_group == 0) cfg.cta_group = 2;
-  if (cfg.group_m == 0) cfg.group_m = 4;
+  if (cfg.group_m == 0) cfg.group_m = 8;
   if (cfg.tile_m != 256 || cfg.tile_n != 256 || cfg.cta_group != 2 || (cfg.tile_k != 64 && cfg.tile_k != 128)) {
     set_error("the fused MLP kernel is built for 256 x 256 tiles on CTA pairs with tile_k 64 or 128 "
               "(got tile_m=%d tile_n=%d cta_group=%d tile_k=%d)", cfg.tile_m, cfg.tile_n, cfg.cta_group,
@@ -718,9 +718,9 @@ int plan_mlp(const tnx_mlp_problem* p, const tnx_config* config, MlpPlan* plan, 
   if (clusters < 1) clusters = 1;
   out->grid = static_cast<int32_t>((units < clusters ? units : clusters) * 2 + comm_ctas);
   out->min_workspace_bytes = plan->counter_bytes + plan->ring_bands_min * plan->band_bytes;
-  // three bands keep a slot's previous readers a whole band of work behind its next writers
-  const int want = plan->num_bands < 3 ? plan->num_bands : 3;
-  out->workspace_bytes = plan->counter_bytes + want * plan->band_bytes;
+  // Two bands measured best: a slot's previous readers are already a whole band of work ahead
+  // of its next writers, and the smaller the ring the more of it stays in L2.
+  out->workspace_bytes = out->min_workspace_bytes;
   if (smem > kMaxDynamicSmem) {
     set_error("shared memory budget exceeded: %lld B needed (%d stages x %d B + %d B), %d B per SM", smem,
               cfg.stages, stage_bytes, fixed, kMaxDynamicSmem);
