@@ -227,13 +227,15 @@ typedef struct tnx_mlp_resources {
  *   - `y` (the pointer passed to tnx_swiglu_mlp) is this rank's mapping of a buffer that every
  *     rank allocated symmetrically and bound to ONE multicast object; y_multicast is the
  *     multicast address of the same bytes;
- *   - signal_local / signal_multicast: likewise for an array of (m + 255) / 256 + 1 uint32
- *     counters, zero before the first call and never written by the caller afterwards;
+ *   - signal_local / signal_multicast: likewise for an array of 1 + signal_tiles uint32
+ *     counters (signal_tiles >= (m + 255) / 256 for the largest m ever passed with these
+ *     buffers), zero before the first call and never written by the caller afterwards;
  *   - epoch: 1 for the first call on these buffers, 2 for the second, ... identical on every
  *     rank (counters are never reset; call number e waits for e * world arrivals).  After a
  *     call that reported TNX_ERR_DEVICE the counters are undefined: zero them on every rank and
  *     restart at 1;
- *   - every rank makes the same sequence of calls with the same m, n_out and comm_ctas.
+ *   - every rank makes the same sequence of calls with the same m, n_out, comm_ctas and
+ *     signal_tiles (m may change from call to call).
  * comm_ctas CTAs (even; 0 = 4) take no tiles and only exchange; the persistent grid shrinks
  * accordingly.
  */
@@ -241,6 +243,8 @@ typedef struct tnx_mlp_exchange {
   int32_t world, rank;
   int32_t comm_ctas;
   uint32_t epoch;
+  int32_t signal_tiles;
+  int32_t reserved0;
   void* y_multicast;
   uint32_t* signal_multicast;
   const uint32_t* signal_local;

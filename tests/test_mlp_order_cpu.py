@@ -28,6 +28,12 @@ def test_struct_layouts_match_header():
                 fields += [f.strip() for f in decl.split(None, 1)[1].split(",")]
         assert fields == [n for n, _ in cls._fields_], struct
     assert ctypes.sizeof(_cabi.MlpProblem) == 56 and ctypes.sizeof(_cabi.MlpResources) == 40
+    body = re.search(r"typedef struct tnx_mlp_exchange \{(.*?)\} tnx_mlp_exchange;", text, re.S).group(1)
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    names = [re.sub(r"[^a-z0-9_]", "", part.split()[-1]) for decl in body.split(";") if decl.strip()
+             for part in decl.split(",")]
+    assert names == [n for n, _ in _cabi.MlpExchange._fields_]
+    assert ctypes.sizeof(_cabi.MlpExchange) == 48
 
 
 def query(m, d, ff, n_out, cfg=None, dtype=_cabi.BF16):

@@ -92,8 +92,9 @@ struct MlpParams {
   int* y_done;             // [tiles_m] CTAs that finished STORING a D unit of the row tile
   void* y_mc;              // multicast address of Y (the same buffer on every rank)
   long long ldy;           // row pitch of Y in elements
-  unsigned* sig_mc;        // [tiles_m + 1] arrival counters: multicast address ...
-  const unsigned* sig_local;  // ... and this rank's copy
+  unsigned* sig_mc;        // [1 + sig_tiles] arrival counters: multicast address ...
+  const unsigned* sig_local;  // ... and this rank's copy.  [0]: closing barrier; [1 + t]: row tile t
+  int sig_tiles;           // row-tile counters in the array (>= tiles_m)
   unsigned epoch;          // ordinal of this call (1, 2, ...)
 };
 
@@ -330,9 +331,9 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
         // this rank's partial rows are complete (every output tile of the row tile is stored) ...
         bool got = wait_counter(p.y_done + t, 2 * p.n_d, abort_flag, p.status, p.timeout_ns);
         if (got) {
-          multimem_signal(p.sig_mc + t);  // ... tell every rank ...
+          multimem_signal(p.sig_mc + 1 + t);  // ... tell every rank ...
           // ... and wait until every rank has said the same in this call
-          got = wait_counter_sys(p.sig_local + t, p.epoch * static_cast<unsigned>(p.world), abort_flag,
+          got = wait_counter_sys(p.sig_local + 1 + t, p.epoch * static_cast<unsigned>(p.world), abort_flag,
                                  p.status, p.timeout_ns);
         }
         ctrl->flag = got ? 1 : 0;
@@ -362,14 +363,18 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
       }
       __syncthreads();  // ctrl->flag is rewritten for the next row tile
     }
+    // Counters of row tiles this call does not have (it has fewer rows than the array was sized
+    // for) advance all the same, so that "epoch * world" stays the target of every counter.
+    if (threadIdx.x == 0 && ok)
+      for (int t = p.tiles_m + c; t < p.sig_tiles; t += p.comm_ctas) multimem_signal(p.sig_mc + 1 + t);
     // Every rank leaves only when all ranks have written all their shares: Y is complete
     // everywhere, and nobody still reads this rank's partial rows.
     __threadfence_system();
     __syncthreads();
     if (threadIdx.x == 0) {
       if (ok) {
-        multimem_signal(p.sig_mc + p.tiles_m);
-        ok = wait_counter_sys(p.sig_local + p.tiles_m,
+        multimem_signal(p.sig_mc);
+        ok = wait_counter_sys(p.sig_local,
                               p.epoch * static_cast<unsigned>(p.world) * static_cast<unsigned>(p.comm_ctas),
                               abort_flag, p.status, p.timeout_ns);
       }
@@ -794,9 +799,11 @@ int tnx_swiglu_mlp(const tnx_mlp_problem* problem, const tnx_config* config, con
     const tnx_mlp_exchange& ex = *exchange;
     comm_ctas = ex.comm_ctas > 0 ? ex.comm_ctas : 4;
     if (ex.world < 1 || ex.world > 2 * kRows || (2 * kRows) % ex.world != 0 || ex.rank < 0 || ex.rank >= ex.world ||
-        (comm_ctas % 2) != 0 || comm_ctas > 64 || ex.epoch == 0) {
-      set_error("exchange: world must divide 256, 0 <= rank < world, comm_ctas even and <= 64, epoch >= 1 "
-                "(got world=%d rank=%d comm_ctas=%d epoch=%u)", ex.world, ex.rank, comm_ctas, ex.epoch);
+        (comm_ctas % 2) != 0 || comm_ctas > 64 || ex.epoch == 0 ||
+        ex.signal_tiles < (problem != nullptr ? (problem->m + 2 * kRows - 1) / (2 * kRows) : 0)) {
+      set_error("exchange: world must divide 256, 0 <= rank < world, comm_ctas even and <= 64, epoch >= 1, "
+                "signal_tiles >= row tiles (got world=%d rank=%d comm_ctas=%d epoch=%u signal_tiles=%d)",
+                ex.world, ex.rank, comm_ctas, ex.epoch, ex.signal_tiles);
       return TNX_ERR_INVALID;
     }
     if (ex.y_multicast == nullptr || ex.signal_multicast == nullptr || ex.signal_local == nullptr ||
@@ -877,6 +884,7 @@ int tnx_swiglu_mlp(const tnx_mlp_problem* problem, const tnx_config* config, con
     kp.ldy = p.stride_ym;
     kp.sig_mc = exchange->signal_multicast;
     kp.sig_local = exchange->signal_local;
+    kp.sig_tiles = exchange->signal_tiles;
     kp.epoch = exchange->epoch;
   }
 

@@ -229,6 +229,7 @@ class FusedTensorParallelSwiGLU:
         self.max_tokens = int(max_tokens)
         dev, dtype = w12_shard.device, w12_shard.dtype
         tiles = -(-self.max_tokens // 256)
+        self._tiles = tiles
         self._y_bytes = tiles * 256 * self.d_out * dtype.itemsize
         sig_bytes = (tiles + 1) * 4
         total = self._y_bytes + -(-sig_bytes // 256) * 256
@@ -264,8 +265,8 @@ class FusedTensorParallelSwiGLU:
         y = self._buf[:m * self.d_out * x.element_size()].view(x.dtype).view(m, self.d_out)
         self._epoch += 1
         local = self._buf.data_ptr()
-        exchange = cabi.MlpExchange(self.world, self.rank, self.comm_ctas, self._epoch, self._mc,
-                                    self._mc + self._y_bytes, local + self._y_bytes)
+        exchange = cabi.MlpExchange(self.world, self.rank, self.comm_ctas, self._epoch, self._tiles, 0,
+                                    self._mc, self._mc + self._y_bytes, local + self._y_bytes)
         cabi.launch_mlp(x, self.w12, self.w_down, y, self.cfg, cabi.EPI_GLU_SILU, exchange=exchange)
         return y
 
