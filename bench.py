@@ -354,7 +354,7 @@ def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1, mode="auto", comm_ctas=4,
 
     one_launch_ok = world == 1 or fused is not None
     if mode == "auto":
-        mode = "one_launch" if (world > 1 and fused is not None) else "two_launch"
+        mode = "one_launch" if one_launch_ok else "two_launch"
     if mode == "one_launch" and not one_launch_ok:
         raise RuntimeError("the one-launch tensor-parallel MLP is unavailable: " + str(fused_note))
     step = step_one_launch if mode == "one_launch" else step_two_launch
@@ -501,6 +501,9 @@ def measure(workload, args, rank, local_rank, world, dev, D, peaks):
 
     # ---- device-timed value (operands resident in HBM)
     use_graph = args.launch == "graph" or (args.launch == "auto" and workload == "splitk")
+    if workload == "mlp":
+        torch.cuda.synchronize()
+        time.sleep(1.0)  # (see the variants below: same rest before either implementation is timed)
     with ClockSampler(local_rank) as clocks:
         ms_total = time_steps(step, args.steps, args.warmup, D.barrier, graph=use_graph)
     tnx.check_status(dev)
@@ -577,6 +580,7 @@ def measure(workload, args, rank, local_rank, world, dev, D, peaks):
         # the other implementation of the same step, timed the same way (a comparison: `value`
         # is the implementation named in config.implementation)
         name, other_step = work["other"]
+        time.sleep(1.0)  # both implementations start from a GPU that has had a moment to cool
         ms_other = D.max(time_steps(other_step, args.steps, args.warmup, D.barrier)) / args.steps
         tnx.check_status(dev)
         entry["variants"] = {work["mode"]: {"ms_per_step": ms_step, "value": value},
@@ -783,9 +787,9 @@ def main():
                     help="mlp on >1 GPU: SMs the GEMM grids leave free for the all-reduce kernel "
                          "(-1: 32 on 8 or more GPUs, else 0)")
     ap.add_argument("--mlp-mode", choices=["auto", "two_launch", "one_launch"], default="auto",
-                    help="mlp: which implementation `value` times (auto: one_launch on several GPUs when "
-                         "the NVLink multicast mapping is available, else two_launch); the other one is "
-                         "timed too and reported under `variants`")
+                    help="mlp: which implementation `value` times (auto: one_launch; on several GPUs only "
+                         "when the NVLink multicast mapping is available, else two_launch); the other one "
+                         "is timed too and reported under `variants`")
     ap.add_argument("--comm-ctas", type=int, default=4,
                     help="mlp one_launch on >1 GPU: CTAs that only exchange partial outputs")
     ap.add_argument("--mlp-band", type=int, default=8,

@@ -131,6 +131,43 @@ def test_shipped_kernel_spaces_are_consistent():
     for tk in (t.matmul_kernel, t.gemm_splitk_kernel, t.glu_kernel, t.swiglu_kernel):
         assert isinstance(tk, TunableKernel) and tk.keys == ["m", "n", "k"]
         names, values = tk._memory_axes()
-        assert set(names) == {"block_m", "block_n", "block_k", "num_stages"}  # the reference's axes
+        # the reference's memory axes plus the TMEM accumulator count
+        assert set(names) == {"block_m", "block_n", "block_k", "num_stages", "acc_stages"}
         assert values[names.index("block_m")][0] == max(tk.space["block_m"].values())
-    assert len(t.matmul_kernel.configs()) == 2 * 3 * 2 * 3 * 4 * 7
+    assert len(t.matmul_kernel.configs()) == 2 * 3 * 2 * 3 * 4 * 7 * 2
+
+
+def test_seeds_steady_state_and_finalists():
+    """Seeds are timed first (and only if they are points of the space), the sweep still covers
+    the rest, and the final alternating round can overturn the sweep's ranking."""
+    from tritonix_b200 import autotune as A
+    calls = []
+
+    class Kernel:
+        pass
+    tk = tunable(keys=[], space={"a": Choice([1, 2, 3]), "stages": Range(2, 4)})(Kernel())
+    cost = {(1, 2): 5.0, (2, 2): 4.0, (3, 2): 6.0, (1, 3): 5.5, (2, 3): 3.0, (3, 3): 7.0,
+            (1, 4): 5.2, (2, 4): 3.5, (3, 4): 8.0}
+    state = {"final": False}
+
+    def fake_bench(fn, warmup=None, rep=None, **kw):
+        cfg = fn()
+        key = (cfg["a"], cfg["stages"])
+        calls.append(key)
+        # in the final round (short budgets) the sweep's runner-up turns out to be faster
+        if rep is not None and rep <= 30 and key == (2, 4):
+            return 2.5
+        return cost[key]
+    old = A.do_bench
+    A.do_bench = fake_bench
+    try:
+        best = tk.tune(lambda c: c, seeds=[{"a": 3, "stages": 4}, {"a": 9, "stages": 2}, {"a": 1}])
+        assert best == {"a": 2, "stages": 3}
+        assert calls[0] == (3, 4)                       # the valid seed came first, the others were dropped
+        assert len(calls) == len(set(calls))            # and it was not timed twice
+        calls.clear()
+        best = tk.tune(lambda c: c, finalists=3)
+        assert best == {"a": 2, "stages": 4}
+        assert calls[-9:].count((2, 4)) == 3 and calls[-9:].count((2, 3)) == 3
+    finally:
+        A.do_bench = old

@@ -79,19 +79,32 @@ class TunableKernel:
     def tune(self, launcher: Callable[[dict], Any], method: str = "grid",
              max_configs: Optional[int] = None, max_evals: int = 100,
              filter_fn: Optional[Callable[[dict], bool]] = None, warmup: float = 25,
-             rep: float = 100, verbose: bool = False):
+             rep: float = 100, verbose: bool = False, seeds: Optional[Iterable[dict]] = None,
+             finalists: int = 1, steady_state_ms: float = 0.0):
         """Times ``launcher(cfg)`` over the space and returns the fastest ``cfg`` (a dict with
         every key of the space), or ``None`` if nothing could be run.
 
         ``launcher`` raises ``OutOfResources`` for a configuration that does not fit (its memory
         coordinates and everything above them are then pruned) and ``ValueError`` for one that
         is invalid or not built (skipped).
+
+        Three additions to the reference's grid search (tritonix/autotune.py:75-140), all off by
+        default.  ``seeds``: configurations timed before the sweep starts — known-good points
+        play the role of the reference's hand-picked lists (tritonix/utils/triton.py:34-90) and
+        give the unimodality pruner a good start.  ``steady_state_ms``: the first runnable
+        configuration is launched back to back for that long before anything is timed, so that
+        a power-capped GPU has settled at its sustained clock and early configurations are not
+        flattered by boost clocks.  ``finalists`` > 1: the best few configurations of the sweep
+        are timed again, alternating, and the median decides — a ranking taken under equal
+        conditions instead of minutes apart.
         """
         if method == "grid":
-            return self._tune_grid(launcher, max_configs, filter_fn, warmup, rep, verbose)
+            return self._tune_grid(launcher, max_configs, filter_fn, warmup, rep, verbose,
+                                   list(seeds or ()), max(1, int(finalists)), steady_state_ms)
         return self._tune_bayesian(launcher, max_evals, filter_fn, warmup, rep, verbose)
 
-    def _tune_grid(self, launcher, max_configs, filter_fn, warmup, rep, verbose):
+    def _tune_grid(self, launcher, max_configs, filter_fn, warmup, rep, verbose, seeds=(),
+                   finalists=1, steady_state_ms=0.0):
         trie, mem_names, mem_values = self._build_trie()
         names = list(self.space)
         axis_values = {n: sorted(self.space[n].values()) for n in names}
@@ -102,6 +115,51 @@ class TunableKernel:
 
         best_ms, best_cfg, evaluated = float("inf"), None, 0
         budget_left = lambda: max_configs is None or evaluated < max_configs  # noqa: E731
+        timed: Dict[tuple, float] = {}   # coordinates -> ms, for the seeds and the final round
+        settled = steady_state_ms <= 0
+
+        def measure(cfg, mem_idx):
+            """ms of one configuration, or None (skipped) / "oom" (pruned)."""
+            nonlocal best_ms, best_cfg, evaluated, settled
+            coords = tuple(position[n][cfg[n]] for n in names)
+            if coords in timed:
+                return timed[coords]
+            try:
+                if not settled:
+                    launcher(cfg)  # raises here if the configuration cannot run at all
+                    _busy_for(lambda: launcher(cfg), steady_state_ms)
+                    settled = True
+                ms = do_bench(lambda: launcher(cfg), warmup=warmup, rep=rep)
+            except ValueError as exc:
+                if verbose:
+                    print(f"  SKIP      {cfg}  ({exc})", flush=True)
+                return None
+            except OutOfResources:
+                trie.prune(mem_idx)
+                if verbose:
+                    print(f"  OOM       {cfg}", flush=True)
+                return "oom"
+            landscape.record(coords, ms)
+            timed[coords] = ms
+            evaluated += 1
+            improved = ms < best_ms
+            if improved:
+                best_ms, best_cfg = ms, cfg
+            if verbose:
+                print(f"  {ms:8.3f}ms  {cfg}{' *' if improved else ''}", flush=True)
+            return ms
+
+        for seed in seeds:
+            if not budget_left():
+                break
+            if set(seed) != set(names) or any(seed[n] not in position[n] for n in names):
+                continue  # not a point of this space
+            if filter_fn is not None and not filter_fn(seed):
+                continue
+            mem_idx = tuple(mem_values[d].index(seed[n]) for d, n in enumerate(mem_names))
+            if trie.is_pruned(mem_idx):
+                continue
+            measure({n: seed[n] for n in names}, mem_idx)
 
         for mem_idx in trie.generate_all_unpruned_midpoint():
             if not budget_left():
@@ -114,26 +172,28 @@ class TunableKernel:
                 if filter_fn is not None and not filter_fn(cfg):
                     continue
                 coords = tuple(position[n][cfg[n]] for n in names)
-                if landscape.is_pruned(coords):
+                if landscape.is_pruned(coords) and coords not in timed:
                     continue
-                try:
-                    ms = do_bench(lambda: launcher(cfg), warmup=warmup, rep=rep)
-                except ValueError as exc:
-                    if verbose:
-                        print(f"  SKIP      {cfg}  ({exc})", flush=True)
-                    continue
-                except OutOfResources:
-                    trie.prune(mem_idx)
-                    if verbose:
-                        print(f"  OOM       {cfg}", flush=True)
+                if measure(cfg, mem_idx) == "oom":
                     break  # nothing else at these memory coordinates can fit
-                landscape.record(coords, ms)
-                evaluated += 1
-                improved = ms < best_ms
-                if improved:
-                    best_ms, best_cfg = ms, cfg
-                if verbose:
-                    print(f"  {ms:8.3f}ms  {cfg}{' *' if improved else ''}", flush=True)
+
+        if finalists > 1 and len(timed) > 1:
+            # The sweep's best few, timed again in alternation: whatever the clocks do in the
+            # meantime, they do it to all of them.
+            ranked = sorted(timed, key=timed.get)[:finalists]
+            cfg_of = lambda coords: {n: axis_values[n][i] for n, i in zip(names, coords)}  # noqa: E731
+            rounds: Dict[tuple, List[float]] = {c: [] for c in ranked}
+            for _ in range(3):
+                for coords in ranked:
+                    cfg = cfg_of(coords)
+                    rounds[coords].append(do_bench(lambda: launcher(cfg), warmup=min(warmup, 5),
+                                                   rep=min(rep, 30)))
+            median = {c: sorted(v)[1] for c, v in rounds.items()}
+            winner = min(ranked, key=median.get)
+            best_cfg = cfg_of(winner)
+            if verbose:
+                for c in ranked:
+                    print(f"  final {median[c]:8.3f}ms  {cfg_of(c)}{' *' if c == winner else ''}", flush=True)
         return best_cfg
 
     def _tune_bayesian(self, launcher, max_evals, filter_fn, warmup, rep, verbose,
@@ -185,6 +245,18 @@ class TunableKernel:
                 print(f"  [{trial + 1}/{max_evals}] {ms:.3f}ms — {cfg}")
         best, _ = client.get_best_parameters()
         return {**fixed, **best}
+
+
+def _busy_for(fn: Callable[[], Any], milliseconds: float) -> None:
+    """Launches ``fn`` back to back for about ``milliseconds`` of wall-clock time."""
+    import time
+
+    import torch
+    deadline = time.perf_counter() + milliseconds / 1e3
+    while time.perf_counter() < deadline:
+        for _ in range(8):
+            fn()
+        torch.cuda.synchronize()
 
 
 def tunable(keys: Iterable[str], space: Dict[str, ConfigParam],

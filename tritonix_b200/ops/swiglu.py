@@ -40,8 +40,9 @@ glu_kernel = tunable(
         "block_k": PowerOfTwo(64, 128),
         "group_m": Choice([4, 8, 16]),
         "num_stages": Range(2, 8),
+        "acc_stages": Choice([1, 2]),
     },
-    memory_params={"block_m", "block_n", "block_k", "num_stages"},
+    memory_params={"block_m", "block_n", "block_k", "num_stages", "acc_stages"},
     memory_rank={"block_m": lambda rows: -rows},
 )(CudaKernel("glu_kernel", glu=True,
              doc="Z = act(X.W1) * (X.W2) over interleaved W12; n counts W12's columns (2F)."))
@@ -92,7 +93,7 @@ class _SwigluMlpKernel(CudaKernel):
 swiglu_kernel = tunable(
     keys=["m", "n", "k"],
     space=dict(glu_kernel.space),
-    memory_params={"block_m", "block_n", "block_k", "num_stages"},
+    memory_params={"block_m", "block_n", "block_k", "num_stages", "acc_stages"},
     memory_rank={"block_m": lambda rows: -rows},
 )(_SwigluMlpKernel("swiglu_kernel",
                    doc="Z[M, f] = (silu(X.W1) * (X.W2)) . W3, W12 interleaved, W3 is (n/2, f)."))
@@ -142,8 +143,10 @@ def glu(x: torch.Tensor, w12: torch.Tensor, activation: str = "sigmoid",
         if cfg is None:
             tune = os.environ.get("TRITONIX_B200_TUNE", "1") not in ("0", "false", "off")
             if tune and _cabi.umma_eligible_tensors(x, w12) and (n // 2) % 8 == 0:
+                seeds = [dict(block_m=256, block_n=256, block_k=bk, group_m=16, num_stages=st, acc_stages=2)
+                         for bk, st in ((128, 3), (64, 6))]
                 cfg = _mm._tuned(glu_kernel, lambda c: _launch_glu(x, w12, c, activation), key, x,
-                                 _mm._plausible(m, n))
+                                 _mm._plausible(m, n), seeds, 2.0 * m * n * k)
             cfg = cfg or default_glu_config(m, n, k)
             _glu_cfg[key] = cfg
     return _launch_glu(x, w12, cfg, activation, out)
