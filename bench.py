@@ -599,9 +599,47 @@ def measure(workload, args, rank, local_rank, world, dev, D, peaks):
     if workload == "gemm" and not args.no_sustained:
         entry["sustained"] = sustained_leg(step, work["flops"], local_rank, args.sustained_seconds, peaks)
         tnx.check_status(dev)
+    if workload == "gemm" and world == 1 and not args.no_drop_in:
+        entry["drop_in"] = drop_in_leg(work, args, dev)
     if workload in ("gemm", "glu", "splitk") and world == 1 and rank == 0 and not args.no_comparators:
         entry["comparators"] = comparators(workload, work, args, dev)
     return entry
+
+
+def drop_in_leg(work, args, dev):
+    """The call a user of the reference makes — `matmul(a, b)` with nothing configured — on the
+    same operands: its first call tunes (seeded grid search with out-of-resources pruning, no
+    disk cache), later calls go through the dispatcher to the tuned kernel and allocate C."""
+    import tritonix_b200 as tnx
+    mm = sys.modules["tritonix_b200.ops.matmul"]
+    a_all, b_all, _ = work["operands"]
+    a, b = a_all[0], b_all[0]
+    m, n, k = work["shape"]
+    keep = {key: os.environ.get(key) for key in ("TRITONIX_B200_TUNE_CACHE", "TRITONIX_B200_TUNE")}
+    os.environ["TRITONIX_B200_TUNE_CACHE"], os.environ["TRITONIX_B200_TUNE"] = "0", "1"
+    mm._matmul_cfg.pop((m, n, k), None)
+    mm._FAST_MATMUL.clear()
+    tnx.matmul.clear_cache()
+    try:
+        t0 = time.perf_counter()
+        tnx.matmul(a, b)
+        torch.cuda.synchronize(dev)
+        first = time.perf_counter() - t0
+        cfg = dict(mm._matmul_cfg[(m, n, k)])
+        time.sleep(1.0)
+        steps = max(5, min(args.steps, 20))
+        ms = time_steps(lambda: tnx.matmul(a, b), steps, 3, lambda: None) / steps
+        tnx.check_status(dev)
+    finally:
+        for key, value in keep.items():
+            if value is None:
+                os.environ.pop(key, None)
+            else:
+                os.environ[key] = value
+        mm._matmul_cfg[(m, n, k)] = dict(GEMM_CFG)
+    return {"call": "tritonix_b200.matmul(a, b), untuned process, no disk cache", "first_call_seconds": first,
+            "tuned_config": cfg, "ms_per_step": ms, "value": work["flops"] / (ms * 1e-3) / 1e12,
+            "unit": "TFLOP/s"}
 
 
 # ---------------------------------------------------------------------------------------------
@@ -773,6 +811,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sustained", action="store_true")
     ap.add_argument("--no-comparators", action="store_true")
+    ap.add_argument("--no-drop-in", action="store_true",
+                    help="gemm on one GPU: skip the leg that tunes and times the plain matmul(a, b) call")
     ap.add_argument("--sustained-seconds", type=float, default=2.0)
     ap.add_argument("--cfg", type=str, default=None,
                     help="JSON object overriding kernel-config keys of the workload, e.g. "
@@ -845,7 +885,8 @@ def main():
         "dtype": entry["dtype"], "data": "synthetic", "config": entry["config"], "e2e": entry["e2e"],
         "gpu_launches": entry["gpu_launches"], "clocks": entry["clocks"], "roofline": entry["roofline"],
     }
-    for extra in ("sustained", "comparators", "parity_err", "parity", "variants", "one_launch_unavailable"):
+    for extra in ("sustained", "drop_in", "comparators", "parity_err", "parity", "variants",
+                  "one_launch_unavailable"):
         if extra in entry:
             line[extra] = entry[extra]
     if rank == 0 and not args.no_cpu_baseline and world == 1:
