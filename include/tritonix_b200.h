@@ -222,11 +222,15 @@ typedef struct tnx_mlp_resources {
  * [2 r F/p, 2 (r+1) F/p) of W12 and rows [r F/p, (r+1) F/p) of W3, d_ff = F/p in the problem), so
  * every rank computes a partial Y; the kernel then sums the partials itself, row tile by row
  * tile while later tiles are still being computed, through an NVLink multicast mapping
- * (multimem.ld_reduce / multimem.st), and every rank ends up with the full Y.  No counterpart in
- * the reference (it has no multi-GPU code).  Requirements, all the caller's to set up:
+ * (multimem.ld_reduce / multimem.st), and every rank ends up with the full Y.  The partial
+ * outputs stay in fp32 until they have been summed, so Y carries one rounding, as on one GPU.
+ * No counterpart in the reference (it has no multi-GPU code).  Requirements, all the caller's to
+ * set up:
  *   - `y` (the pointer passed to tnx_swiglu_mlp) is this rank's mapping of a buffer that every
  *     rank allocated symmetrically and bound to ONE multicast object; y_multicast is the
  *     multicast address of the same bytes;
+ *   - partial_local / partial_multicast: likewise for a buffer of m x n_out fp32 values (rows
+ *     contiguous, pitch n_out) that receives this rank's partial outputs;
  *   - signal_local / signal_multicast: likewise for an array of 1 + signal_tiles uint32
  *     counters (signal_tiles >= (m + 255) / 256 for the largest m ever passed with these
  *     buffers), zero before the first call and never written by the caller afterwards;
@@ -246,6 +250,8 @@ typedef struct tnx_mlp_exchange {
   int32_t signal_tiles;
   int32_t reserved0;
   void* y_multicast;
+  float* partial_local;
+  const float* partial_multicast;
   uint32_t* signal_multicast;
   const uint32_t* signal_local;
 } tnx_mlp_exchange;

@@ -33,7 +33,7 @@ def test_struct_layouts_match_header():
     names = [re.sub(r"[^a-z0-9_]", "", part.split()[-1]) for decl in body.split(";") if decl.strip()
              for part in decl.split(",")]
     assert names == [n for n, _ in _cabi.MlpExchange._fields_]
-    assert ctypes.sizeof(_cabi.MlpExchange) == 48
+    assert ctypes.sizeof(_cabi.MlpExchange) == 64
 
 
 def query(m, d, ff, n_out, cfg=None, dtype=_cabi.BF16):

@@ -25,9 +25,10 @@ int umma_launch(const tnx_problem& p, const tnx_config& cfg, const tnx_resources
                 int32_t* status_word, cudaStream_t stream);
 
 // Helpers of the tcgen05 GEMM translation unit that other kernels of the library share.
-// 2-D row-major tensor of 16-bit elements -> tensor map with 128-byte swizzle: `cols` contiguous
-// elements per row, `rows` rows, `pitch_elems` between rows, boxes of box_cols x box_rows
-// (encoded maps are cached).  is_operand selects the L2 promotion used for loads.
+// 2-D row-major tensor of 16-bit elements (TNX_F16 / TNX_BF16; TNX_F32 = 32-bit elements) ->
+// tensor map with 128-byte swizzle: `cols` contiguous elements per row, `rows` rows,
+// `pitch_elems` between rows, boxes of box_cols x box_rows (a box row must be 128 bytes; encoded
+// maps are cached).  is_operand selects the L2 promotion used for loads.
 int make_tmap_2d(CUtensorMap* out, const void* ptr, int dtype, int64_t cols, int64_t rows,
                  int64_t pitch_elems, int box_cols, int box_rows, bool is_operand);
 int sm_count();                             // SMs of the current device (148 when none is visible)

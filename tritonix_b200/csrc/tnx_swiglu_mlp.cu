@@ -31,9 +31,11 @@
 //    take no tiles; they watch a third counter (y_done: output tiles of a row tile stored), tell
 //    the other ranks through a multicast counter (multimem.red), wait until every rank has the
 //    row tile, and then sum their 1/world share of its rows across all ranks with
-//    multimem.ld_reduce (fp32 accumulation in the NVSwitch) and write the result to all ranks
-//    with multimem.st.  Y and the counters live in symmetric memory mapped into one multicast
-//    object; no TMA operation touches another GPU's memory.  The computing CTAs never wait for the
+//    multimem.ld_reduce and write the result to all ranks with multimem.st.  The partial outputs
+//    are kept in fp32 (a buffer of their own) and rounded to the output type only after the
+//    cross-rank sum, so the result carries ONE rounding, as on a single GPU.  The partial
+//    buffer, Y and the counters live in symmetric memory mapped into one multicast object; no
+//    TMA operation touches another GPU's memory.  The computing CTAs never wait for the
 //    exchanging ones.  Cross-rank counters are never reset: call number `epoch` waits for
 //    epoch * world arrivals.
 #include <cuda.h>
@@ -92,6 +94,7 @@ struct MlpParams {
   int* y_done;             // [tiles_m] CTAs that finished STORING a D unit of the row tile
   void* y_mc;              // multicast address of Y (the same buffer on every rank)
   long long ldy;           // row pitch of Y in elements
+  const float* part_mc;    // multicast address of the fp32 partial outputs ([rows, n_out], pitch n_out)
   unsigned* sig_mc;        // [1 + sig_tiles] arrival counters: multicast address ...
   const unsigned* sig_local;  // ... and this rank's copy.  [0]: closing barrier; [1 + t]: row tile t
   int sig_tiles;           // row-tile counters in the array (>= tiles_m)
@@ -213,20 +216,13 @@ __device__ __forceinline__ bool wait_counter_sys(const unsigned* counter, unsign
 __device__ __forceinline__ void multimem_signal(unsigned* mc_counter) {
   asm volatile("multimem.red.release.sys.global.add.u32 [%0], 1;" ::"l"(mc_counter) : "memory");
 }
-// 16 bytes (eight 16-bit values) summed over all GPUs with fp32 accumulation in the switch.
-template <bool BF16>
-__device__ __forceinline__ uint4 multimem_sum(const void* mc_addr) {
-  uint4 v;
-  if (BF16)
-    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(mc_addr)
-                 : "memory");
-  else
-    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(mc_addr)
-                 : "memory");
+// Four fp32 values summed over all GPUs of the multicast object (the switch adds them).
+__device__ __forceinline__ float4 multimem_sum(const float* mc_addr) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(mc_addr)
+               : "memory");
   return v;
 }
 __device__ __forceinline__ void multimem_store(void* mc_addr, const uint4& v) {
@@ -264,7 +260,7 @@ __global__ void __launch_bounds__(kExchangeThreads, 1)
 swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w12,
                   const __grid_constant__ CUtensorMap tmap_h_st, const __grid_constant__ CUtensorMap tmap_h_ld,
                   const __grid_constant__ CUtensorMap tmap_w3, const __grid_constant__ CUtensorMap tmap_y,
-                  const MlpParams p) {
+                  const __grid_constant__ CUtensorMap tmap_part, const MlpParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
   const uint32_t base_addr = (raw_addr + 1023u) & ~1023u;
@@ -295,6 +291,7 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
     ptx::prefetch_tensormap(&tmap_h_ld);
     ptx::prefetch_tensormap(&tmap_w3);
     ptx::prefetch_tensormap(&tmap_y);
+    if (p.comm_ctas > 0) ptx::prefetch_tensormap(&tmap_part);
     for (int s = 0; s < p.stages; ++s) {
       ptx::mbar_init(ptx::smem_u32(&ctrl->full[s]), 1);
       ptx::mbar_init(ptx::smem_u32(&ctrl->empty[s]), 1);
@@ -323,7 +320,7 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
     // ===== cross-rank sum of Y, row tile by row tile (every thread of the CTA) =====
     const int c = static_cast<int>(blockIdx.x) - (static_cast<int>(gridDim.x) - p.comm_ctas);
     const int rows_per_rank = (2 * kRows) / p.world;
-    const int vec_per_row = p.n_out >> 3;  // 16-byte vectors per row
+    const int vec_per_row = p.n_out >> 3;  // 16-byte vectors (eight values) per output row
     char* y_mc = static_cast<char*>(p.y_mc);
     bool ok = true;
     for (int t = c; t < p.tiles_m && ok; t += p.comm_ctas) {
@@ -344,21 +341,31 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
         const int row_lo = t * 2 * kRows + p.rank * rows_per_rank;
         const int rows = min(rows_per_rank, p.m - row_lo);
         const int total = rows > 0 ? rows * vec_per_row : 0;
-        constexpr int kInFlight = 8;
+        constexpr int kInFlight = 4;  // output vectors per thread and round = 8 sums in flight
         for (int base = threadIdx.x; base < total; base += blockDim.x * kInFlight) {
-          uint4 v[kInFlight];
+          float4 lo[kInFlight], hi[kInFlight];
           size_t off[kInFlight];
 #pragma unroll
           for (int i = 0; i < kInFlight; ++i) {
             const int idx = base + i * static_cast<int>(blockDim.x);
             const int safe = idx < total ? idx : base;
             const int r = safe / vec_per_row;
-            off[i] = (static_cast<size_t>(row_lo + r) * p.ldy + static_cast<size_t>(safe - r * vec_per_row) * 8) * 2;
-            v[i] = multimem_sum<BF16>(y_mc + off[i]);
+            const size_t col = static_cast<size_t>(safe - r * vec_per_row) * 8;
+            off[i] = (static_cast<size_t>(row_lo + r) * p.ldy + col) * 2;
+            const float* src = p.part_mc + static_cast<size_t>(row_lo + r) * p.n_out + col;
+            lo[i] = multimem_sum(src);
+            hi[i] = multimem_sum(src + 4);
           }
 #pragma unroll
           for (int i = 0; i < kInFlight; ++i)
-            if (base + i * static_cast<int>(blockDim.x) < total) multimem_store(y_mc + off[i], v[i]);
+            if (base + i * static_cast<int>(blockDim.x) < total) {
+              uint4 v;  // the one rounding of the cross-rank fp32 sum
+              v.x = pack2<BF16>(lo[i].x, lo[i].y);
+              v.y = pack2<BF16>(lo[i].z, lo[i].w);
+              v.z = pack2<BF16>(hi[i].x, hi[i].y);
+              v.w = pack2<BF16>(hi[i].z, hi[i].w);
+              multimem_store(y_mc + off[i], v);
+            }
         }
       }
       __syncthreads();  // ctrl->flag is rewritten for the next row tile
@@ -506,8 +513,11 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
     for (int u = cluster_id; u < p.total_units && ok; u += num_clusters) {
       const Unit un = decode_unit(p, u);
       const int row0 = ((un.down ? un.t : ring_tile(p, un.t)) * 2 + static_cast<int>(cta_rank)) * kRows;
-      const CUtensorMap* map_c = un.down ? &tmap_y : &tmap_h_st;
-      const int acc_per_chunk = un.down ? 64 : 128;     // accumulator columns per 128-byte output row
+      // (when ranks exchange, a D unit stores its fp32 accumulator as it is: 32 columns per chunk)
+      const bool raw = un.down && p.comm_ctas > 0;
+      const CUtensorMap* map_c = raw ? &tmap_part : (un.down ? &tmap_y : &tmap_h_st);
+      const int acc_per_chunk = raw ? 32 : (un.down ? 64 : 128);  // accumulator columns per 128-byte output row
+      const int out_per_chunk = raw ? 32 : kAtomElems;            // output elements per 128-byte row
       const int out_col0 = un.j * (un.down ? kTileN : kTileN / 2);
       const int out_cols = un.down ? p.n_out : p.d_ff;
 
@@ -532,7 +542,7 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
       const uint32_t t_acc = tmem_base + lane_sel + acc * kTileN;
       const int chunks = kTileN / acc_per_chunk;
       for (int chunk = 0; chunk < chunks; ++chunk) {
-        const int out_col = out_col0 + chunk * kAtomElems;
+        const int out_col = out_col0 + chunk * out_per_chunk;
         if (out_col >= out_cols) break;
         const uint32_t buf = smem_out + (stores & 1u) * kStagingBytes;
         if (epi_tid == 0) ptx::tma_store_wait_read<1>();
@@ -556,6 +566,16 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
               st_shared_v4(buf + stage_row + pos * 16, o[piece * 4], o[piece * 4 + 1], o[piece * 4 + 2],
                            o[piece * 4 + 3]);
             }
+          }
+        } else if (raw) {
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(t_acc + chunk * 32, r);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int piece = 0; piece < 8; ++piece) {
+            const uint32_t pos = static_cast<uint32_t>(piece) ^ sw;
+            st_shared_v4(buf + stage_row + pos * 16, r[piece * 4], r[piece * 4 + 1], r[piece * 4 + 2],
+                         r[piece * 4 + 3]);
           }
         } else {
 #pragma unroll
@@ -630,7 +650,7 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
 }
 
 using MlpKernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
-                             const CUtensorMap, const CUtensorMap, const MlpParams);
+                             const CUtensorMap, const CUtensorMap, const CUtensorMap, const MlpParams);
 
 MlpKernelFn pick_mlp_kernel(int tile_k, int dtype) {
   if (tile_k == 64) return dtype == TNX_BF16 ? swiglu_mlp_kernel<64, true> : swiglu_mlp_kernel<64, false>;
@@ -807,9 +827,12 @@ int tnx_swiglu_mlp(const tnx_mlp_problem* problem, const tnx_config* config, con
       return TNX_ERR_INVALID;
     }
     if (ex.y_multicast == nullptr || ex.signal_multicast == nullptr || ex.signal_local == nullptr ||
-        (reinterpret_cast<uintptr_t>(ex.y_multicast) & 15u) ||
+        ex.partial_local == nullptr || ex.partial_multicast == nullptr ||
+        ((reinterpret_cast<uintptr_t>(ex.y_multicast) | reinterpret_cast<uintptr_t>(ex.partial_local) |
+          reinterpret_cast<uintptr_t>(ex.partial_multicast)) & 15u) ||
         (reinterpret_cast<uintptr_t>(ex.signal_multicast) & 3u)) {
-      set_error("exchange: y_multicast (16-byte aligned), signal_multicast and signal_local must be set");
+      set_error("exchange: y_multicast, partial_local, partial_multicast (16-byte aligned), signal_multicast "
+                "and signal_local must be set");
       return TNX_ERR_INVALID;
     }
   }
@@ -844,13 +867,16 @@ int tnx_swiglu_mlp(const tnx_mlp_problem* problem, const tnx_config* config, con
   void* h = static_cast<char*>(workspace) + plan.counter_bytes;
   const int64_t h_rows = ring * plan.band * 2 * kRows;
   const int tk = plan.cfg.tile_k;
-  CUtensorMap tx, tw12, thst, thld, tw3, ty;
+  CUtensorMap tx, tw12, thst, thld, tw3, ty, tpart;
   rc = make_tmap_2d(&tx, x, p.dtype, p.d_model, p.m, p.stride_xm, kAtomElems, kRows, true);
   if (rc == TNX_OK) rc = make_tmap_2d(&tw12, w12, p.dtype, 2LL * p.d_ff, p.d_model, p.stride_w12k, kAtomElems, tk, true);
   if (rc == TNX_OK) rc = make_tmap_2d(&thst, h, p.dtype, p.d_ff, h_rows, p.d_ff, kAtomElems, kRows, false);
   if (rc == TNX_OK) rc = make_tmap_2d(&thld, h, p.dtype, p.d_ff, h_rows, p.d_ff, kAtomElems, kRows, true);
   if (rc == TNX_OK) rc = make_tmap_2d(&tw3, w3, p.dtype, p.n_out, p.d_ff, p.stride_w3k, kAtomElems, tk, true);
   if (rc == TNX_OK) rc = make_tmap_2d(&ty, y, p.dtype, p.n_out, p.m, p.stride_ym, kAtomElems, kRows, false);
+  tpart = ty;  // (a valid map; only read when ranks exchange)
+  if (rc == TNX_OK && comm_ctas > 0)
+    rc = make_tmap_2d(&tpart, exchange->partial_local, TNX_F32, p.n_out, p.m, p.n_out, 32, kRows, false);
   if (rc != TNX_OK) return rc;
 
   MlpParams kp = {};
@@ -882,6 +908,7 @@ int tnx_swiglu_mlp(const tnx_mlp_problem* problem, const tnx_config* config, con
     kp.comm_ctas = comm_ctas;
     kp.y_mc = exchange->y_multicast;
     kp.ldy = p.stride_ym;
+    kp.part_mc = static_cast<const float*>(exchange->partial_multicast);
     kp.sig_mc = exchange->signal_multicast;
     kp.sig_local = exchange->signal_local;
     kp.sig_tiles = exchange->signal_tiles;
@@ -922,7 +949,7 @@ int tnx_swiglu_mlp(const tnx_mlp_problem* problem, const tnx_config* config, con
     set_error("the GPU cannot hold %d exchanging CTAs next to a computing cluster", comm_ctas);
     return TNX_ERR_CUDA;
   }
-  e = cudaLaunchKernelEx(&lc, fn, tx, tw12, thst, thld, tw3, ty, kp);
+  e = cudaLaunchKernelEx(&lc, fn, tx, tw12, thst, thld, tw3, ty, tpart, kp);
   if (e != cudaSuccess) {
     set_error("kernel launch failed: %s", cudaGetErrorString(e));
     (void)cudaGetLastError();

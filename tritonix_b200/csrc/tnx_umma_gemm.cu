@@ -1036,11 +1036,13 @@ int make_tmap(CUtensorMap* out, const void* ptr, int dtype, int64_t cols, int64_
     return TNX_ERR_CUDA;
   }
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch_elems) * 2};
+  // (16-bit operands and outputs everywhere, except fp32 partial outputs of the MLP exchange)
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(pitch_elems) * (dtype == TNX_F32 ? 4 : 2)};
   const cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(box_rows)};
   const cuuint32_t estr[2] = {1, 1};
-  const CUtensorMapDataType dt =
-      dtype == TNX_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUtensorMapDataType dt = dtype == TNX_F32    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : dtype == TNX_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                     : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   CUresult r = encode(out, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr,
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                       is_operand ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_NONE,

@@ -198,7 +198,8 @@ class FusedTensorParallelSwiGLU:
     output buffer — so the exchange is spread over the whole step instead of following it.  No
     collective library call is made in ``forward``.
 
-    The output buffer and the exchange counters live in symmetric memory
+    The output buffer, the fp32 partial outputs (summed across the ranks before the one rounding
+    to the output type) and the exchange counters live in symmetric memory
     (``torch.distributed._symmetric_memory``: the same allocation on every rank, bound to one
     multicast object).  ``forward`` returns a view of that buffer: it holds the full result on
     every rank and is overwritten by the next call.  Needs NVSwitch multicast support; when it
@@ -231,8 +232,9 @@ class FusedTensorParallelSwiGLU:
         tiles = -(-self.max_tokens // 256)
         self._tiles = tiles
         self._y_bytes = tiles * 256 * self.d_out * dtype.itemsize
+        self._part_bytes = tiles * 256 * self.d_out * 4   # fp32 partial outputs of this rank
         sig_bytes = (tiles + 1) * 4
-        total = self._y_bytes + -(-sig_bytes // 256) * 256
+        total = self._y_bytes + self._part_bytes + -(-sig_bytes // 256) * 256
         try:  # older releases need the group enabled explicitly; newer ones deprecate the call
             symm.enable_symm_mem_for_group(self.group.group_name)
         except Exception:
@@ -251,7 +253,7 @@ class FusedTensorParallelSwiGLU:
         """Zeroes the exchange counters on every rank and restarts the call count (collective;
         needed after a call that raised ``DeviceStatusError``)."""
         torch.cuda.synchronize(self._buf.device)
-        self._buf[self._y_bytes:].zero_()
+        self._buf[self._y_bytes + self._part_bytes:].zero_()
         torch.cuda.synchronize(self._buf.device)
         self._handle.barrier()
         torch.cuda.synchronize(self._buf.device)
@@ -265,8 +267,9 @@ class FusedTensorParallelSwiGLU:
         y = self._buf[:m * self.d_out * x.element_size()].view(x.dtype).view(m, self.d_out)
         self._epoch += 1
         local = self._buf.data_ptr()
+        part, sig = self._y_bytes, self._y_bytes + self._part_bytes
         exchange = cabi.MlpExchange(self.world, self.rank, self.comm_ctas, self._epoch, self._tiles, 0,
-                                    self._mc, self._mc + self._y_bytes, local + self._y_bytes)
+                                    self._mc, local + part, self._mc + part, self._mc + sig, local + sig)
         cabi.launch_mlp(x, self.w12, self.w_down, y, self.cfg, cabi.EPI_GLU_SILU, exchange=exchange)
         return y
 
