@@ -311,7 +311,7 @@ def _mlp_weight_blocks(dev, lo, hi):
     return wg, wu, wd
 
 
-def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1, mode="auto", comm_ctas=4, band=8):
+def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1, mode="auto", comm_ctas=4, band=8, tokens=0):
     """SwiGLU MLP, tensor parallel: hidden units split over the ranks (column-parallel gate/up,
     row-parallel down projection), partial outputs summed across the ranks.  Global weights come
     from fixed seeds and are sliced, so every world size computes the same function.
@@ -323,7 +323,7 @@ def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1, mode="auto", comm_ctas=4,
                                            shard_bounds)
     comm_sms = (32 if world >= 8 else 0) if comm_sms < 0 else comm_sms
     w = WORKLOADS["mlp"]
-    m, d, ff, dt = w["m"], w["d"], w["ff"], torch.bfloat16
+    m, d, ff, dt = (tokens or w["m"]), w["d"], w["ff"], torch.bfloat16
     lo, hi = shard_bounds(ff, rank, world, 128)
     fr = hi - lo
     wg, wu, wd = _mlp_weight_blocks(dev, lo, hi)  # slice-then-interleave
@@ -493,7 +493,7 @@ def measure(workload, args, rank, local_rank, world, dev, D, peaks):
     if workload == "mlp":
         chunks = [float(v) for v in args.chunk_weights.split(",")] if args.chunk_weights else args.chunks
         step, e2e_step, work = setup_mlp(rank, world, dev, chunks, args.comm_sms, args.mlp_mode,
-                                         args.comm_ctas, args.mlp_band)
+                                         args.comm_ctas, args.mlp_band, args.mlp_tokens)
     elif workload == "conv":
         step, e2e_step, work = setup_conv(rank, world, dev, json.loads(args.cfg) if args.cfg else None)
     else:
@@ -564,6 +564,7 @@ def measure(workload, args, rank, local_rank, world, dev, D, peaks):
                    "kernel_config_source": CONFIG_SOURCE,
                    **({"implementation": work["mode"], "exchange": work["exchange"]}
                       if workload == "mlp" else {}),
+                   **({"tokens": args.mlp_tokens} if workload == "mlp" and args.mlp_tokens else {}),
                    **({"allreduce_chunks": work["chunks"], "comm_sms": work["comm_sms"]}
                       if workload == "mlp" and world > 1 and work["mode"] == "two_launch" else {}),
                    "parallelism": parallelism,
@@ -834,6 +835,9 @@ def main():
                     help="mlp one_launch on >1 GPU: CTAs that only exchange partial outputs")
     ap.add_argument("--mlp-band", type=int, default=8,
                     help="mlp one_launch: 256-row tiles per band")
+    ap.add_argument("--mlp-tokens", type=int, default=0,
+                    help="mlp: token count, if not the 32768 of the benchmark configuration (a smaller "
+                         "case for a profiler capture; the line then names it in config.tokens)")
     ap.add_argument("--launch", choices=["auto", "eager", "graph"], default="auto",
                     help="how the timed steps are issued: one by one, or as one CUDA graph of "
                          "`steps` launches (auto: graph for the launch-latency-bound splitk workload)")
