@@ -166,7 +166,8 @@ def test_tuner_on_real_kernels_prunes_out_of_resources():
             continue
         for kind2, c2 in events[i + 1:]:
             assert not (c2["block_n"] >= c["block_n"] and c2["num_stages"] >= c["num_stages"]
-                        and c2["block_m"] <= c["block_m"] and c2["block_k"] >= c["block_k"])
+                        and c2["block_m"] <= c["block_m"] and c2["block_k"] >= c["block_k"]
+                        and c2["acc_stages"] >= c["acc_stages"])
     out = mm._launch_matmul(a, b, best)
     assert_close(out.cpu(), O.matmul_oracle(a.cpu(), b.cpu()), bf16)
 
