@@ -311,7 +311,7 @@ def _mlp_weight_blocks(dev, lo, hi):
     return wg, wu, wd
 
 
-def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1, mode="auto", comm_ctas=4, band=8, tokens=0):
+def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1, mode="auto", comm_ctas=8, band=8, tokens=0):
     """SwiGLU MLP, tensor parallel: hidden units split over the ranks (column-parallel gate/up,
     row-parallel down projection), partial outputs summed across the ranks.  Global weights come
     from fixed seeds and are sliced, so every world size computes the same function.
@@ -831,7 +831,7 @@ def main():
                     help="mlp: which implementation `value` times (auto: two_launch on one GPU, one_launch "
                          "on several when the NVLink multicast mapping is available); the other one is "
                          "timed too, from the same rest, and reported under `variants`")
-    ap.add_argument("--comm-ctas", type=int, default=4,
+    ap.add_argument("--comm-ctas", type=int, default=8,
                     help="mlp one_launch on >1 GPU: CTAs that only exchange partial outputs")
     ap.add_argument("--mlp-band", type=int, default=8,
                     help="mlp one_launch: 256-row tiles per band")

@@ -240,7 +240,7 @@ typedef struct tnx_mlp_resources {
  *     restart at 1;
  *   - every rank makes the same sequence of calls with the same m, n_out, comm_ctas and
  *     signal_tiles (m may change from call to call).
- * comm_ctas CTAs (even; 0 = 4) take no tiles and only exchange; the persistent grid shrinks
+ * comm_ctas CTAs (even; 0 = 8) take no tiles and only exchange; the persistent grid shrinks
  * accordingly.
  */
 typedef struct tnx_mlp_exchange {

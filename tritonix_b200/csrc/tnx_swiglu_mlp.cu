@@ -341,31 +341,37 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
         const int row_lo = t * 2 * kRows + p.rank * rows_per_rank;
         const int rows = min(rows_per_rank, p.m - row_lo);
         const int total = rows > 0 ? rows * vec_per_row : 0;
-        constexpr int kInFlight = 4;  // output vectors per thread and round = 8 sums in flight
-        for (int base = threadIdx.x; base < total; base += blockDim.x * kInFlight) {
-          float4 lo[kInFlight], hi[kInFlight];
-          size_t off[kInFlight];
+        // A sum through the switch takes about ten microseconds to come back, so what an
+        // exchanging CTA moves per second is set by how much it keeps in flight: every thread
+        // has sixteen 16-byte sums outstanding before it converts and stores the first.
+        constexpr int kVec = 8;  // output vectors (eight values each) per thread and round
+        for (int base = threadIdx.x; base < total; base += blockDim.x * kVec) {
+          float4 lo[kVec], hi[kVec];
 #pragma unroll
-          for (int i = 0; i < kInFlight; ++i) {
+          for (int i = 0; i < kVec; ++i) {
             const int idx = base + i * static_cast<int>(blockDim.x);
             const int safe = idx < total ? idx : base;
             const int r = safe / vec_per_row;
-            const size_t col = static_cast<size_t>(safe - r * vec_per_row) * 8;
-            off[i] = (static_cast<size_t>(row_lo + r) * p.ldy + col) * 2;
-            const float* src = p.part_mc + static_cast<size_t>(row_lo + r) * p.n_out + col;
+            const float* src = p.part_mc + static_cast<size_t>(row_lo + r) * p.n_out +
+                               static_cast<size_t>(safe - r * vec_per_row) * 8;
             lo[i] = multimem_sum(src);
             hi[i] = multimem_sum(src + 4);
           }
 #pragma unroll
-          for (int i = 0; i < kInFlight; ++i)
-            if (base + i * static_cast<int>(blockDim.x) < total) {
+          for (int i = 0; i < kVec; ++i) {
+            const int idx = base + i * static_cast<int>(blockDim.x);
+            if (idx < total) {
+              const int r = idx / vec_per_row;
+              const size_t off = (static_cast<size_t>(row_lo + r) * p.ldy +
+                                  static_cast<size_t>(idx - r * vec_per_row) * 8) * 2;
               uint4 v;  // the one rounding of the cross-rank fp32 sum
               v.x = pack2<BF16>(lo[i].x, lo[i].y);
               v.y = pack2<BF16>(lo[i].z, lo[i].w);
               v.z = pack2<BF16>(hi[i].x, hi[i].y);
               v.w = pack2<BF16>(hi[i].z, hi[i].w);
-              multimem_store(y_mc + off[i], v);
+              multimem_store(y_mc + off, v);
             }
+          }
         }
       }
       __syncthreads();  // ctrl->flag is rewritten for the next row tile
@@ -817,7 +823,7 @@ int tnx_swiglu_mlp(const tnx_mlp_problem* problem, const tnx_config* config, con
   // (world == 1 with comm_ctas > 0 is the degenerate exchange: same protocol, one participant)
   if (exchange != nullptr && (exchange->world > 1 || exchange->comm_ctas > 0)) {
     const tnx_mlp_exchange& ex = *exchange;
-    comm_ctas = ex.comm_ctas > 0 ? ex.comm_ctas : 4;
+    comm_ctas = ex.comm_ctas > 0 ? ex.comm_ctas : 8;
     if (ex.world < 1 || ex.world > 2 * kRows || (2 * kRows) % ex.world != 0 || ex.rank < 0 || ex.rank >= ex.world ||
         (comm_ctas % 2) != 0 || comm_ctas > 64 || ex.epoch == 0 ||
         ex.signal_tiles < (problem != nullptr ? (problem->m + 2 * kRows - 1) / (2 * kRows) : 0)) {

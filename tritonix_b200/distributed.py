@@ -210,7 +210,7 @@ class FusedTensorParallelSwiGLU:
     """
 
     def __init__(self, w12_shard: torch.Tensor, w_down_shard: torch.Tensor, max_tokens: int,
-                 group: Optional[dist.ProcessGroup] = None, comm_ctas: int = 4,
+                 group: Optional[dist.ProcessGroup] = None, comm_ctas: int = 8,
                  cfg: Optional[dict] = None):
         import torch.distributed._symmetric_memory as symm
 
