@@ -311,7 +311,7 @@ def _mlp_weight_blocks(dev, lo, hi):
     return wg, wu, wd
 
 
-def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1, mode="auto", comm_ctas=8, band=8, tokens=0):
+def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1, mode="auto", tile_split=4, band=8, tokens=0):
     """SwiGLU MLP, tensor parallel: hidden units split over the ranks (column-parallel gate/up,
     row-parallel down projection), partial outputs summed across the ranks.  Global weights come
     from fixed seeds and are sliced, so every world size computes the same function.
@@ -339,7 +339,7 @@ def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1, mode="auto", comm_ctas=8,
     fused_note = None
     if world > 1:
         try:
-            fused = FusedTensorParallelSwiGLU(w12, wd, max_tokens=m, comm_ctas=comm_ctas, cfg=fused_cfg)
+            fused = FusedTensorParallelSwiGLU(w12, wd, max_tokens=m, tile_split=tile_split, cfg=fused_cfg)
         except Exception as exc:  # no multicast mapping on this system: the NCCL path remains
             fused_note = f"{type(exc).__name__}: {exc}"[:200]
 
@@ -395,8 +395,9 @@ def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1, mode="auto", comm_ctas=8,
     if mode == "one_launch":
         cfg = {"one_launch": dict(fused_cfg, tile_m=256, tile_n=256, cta_group=2)}
         launches = 1
-        exchange = ("inside the kernel: multimem.ld_reduce / multimem.st per 256-row tile, %d exchanging CTAs"
-                    % comm_ctas) if world > 1 else "none (one GPU)"
+        exchange = ("inside the kernel: fp32 partial outputs summed with multimem.ld_reduce / multimem.st per "
+                    "256-row tile by ten spare warps of every CTA, %d crews per tile" % tile_split) \
+            if world > 1 else "none (one GPU)"
     else:
         cfg = {"gate_up": GLU_CFG, "down": GEMM_CFG}
         launches = 2 * nchunks
@@ -493,7 +494,7 @@ def measure(workload, args, rank, local_rank, world, dev, D, peaks):
     if workload == "mlp":
         chunks = [float(v) for v in args.chunk_weights.split(",")] if args.chunk_weights else args.chunks
         step, e2e_step, work = setup_mlp(rank, world, dev, chunks, args.comm_sms, args.mlp_mode,
-                                         args.comm_ctas, args.mlp_band, args.mlp_tokens)
+                                         args.tile_split, args.mlp_band, args.mlp_tokens)
     elif workload == "conv":
         step, e2e_step, work = setup_conv(rank, world, dev, json.loads(args.cfg) if args.cfg else None)
     else:
@@ -831,8 +832,8 @@ def main():
                     help="mlp: which implementation `value` times (auto: two_launch on one GPU, one_launch "
                          "on several when the NVLink multicast mapping is available); the other one is "
                          "timed too, from the same rest, and reported under `variants`")
-    ap.add_argument("--comm-ctas", type=int, default=8,
-                    help="mlp one_launch on >1 GPU: CTAs that only exchange partial outputs")
+    ap.add_argument("--tile-split", type=int, default=4,
+                    help="mlp one_launch on >1 GPU: CTAs whose spare warps share one row tile's exchange")
     ap.add_argument("--mlp-band", type=int, default=8,
                     help="mlp one_launch: 256-row tiles per band")
     ap.add_argument("--mlp-tokens", type=int, default=0,

@@ -238,14 +238,16 @@ typedef struct tnx_mlp_resources {
  *     rank (counters are never reset; call number e waits for e * world arrivals).  After a
  *     call that reported TNX_ERR_DEVICE the counters are undefined: zero them on every rank and
  *     restart at 1;
- *   - every rank makes the same sequence of calls with the same m, n_out, comm_ctas and
- *     signal_tiles (m may change from call to call).
- * comm_ctas CTAs (even; 0 = 8) take no tiles and only exchange; the persistent grid shrinks
- * accordingly.
+ *   - every rank makes the same sequence of calls with the same m, n_out, tile_split and
+ *     signal_tiles (m may change from call to call), on the same GPU model (the closing barrier
+ *     counts the CTAs of every rank's grid).
+ * A tensor-parallel launch has 512 threads per CTA: ten warps of every CTA form a crew that
+ * exchanges while the other six compute.  tile_split (1, 2, 4 ...; 0 = 4; world * tile_split must
+ * divide 256) is the number of crews that share one row tile's exchange.
  */
 typedef struct tnx_mlp_exchange {
   int32_t world, rank;
-  int32_t comm_ctas;
+  int32_t tile_split;
   uint32_t epoch;
   int32_t signal_tiles;
   int32_t reserved0;
@@ -280,8 +282,7 @@ int tnx_swiglu_mlp_unit_order(const tnx_mlp_problem* problem, const tnx_config* 
  * Its content before and after the call is meaningless.  Calls sharing a workspace must be
  * ordered on one stream.  The kernel's CTAs wait for one another through the counters (bounded
  * waits that report through `status_word`), so the launch is sized to what the GPU can hold
- * at once.  With `exchange` the grid query of tnx_swiglu_mlp_query does not include the
- * exchanging CTAs.
+ * at once.
  */
 int tnx_swiglu_mlp(const tnx_mlp_problem* problem, const tnx_config* config, const void* x,
                    const void* w12, const void* w3, void* y, void* workspace,

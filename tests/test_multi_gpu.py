@@ -91,7 +91,7 @@ def _fused_worker(rank, world, port, out_dir):
         wd = (torch.randn(ff, d, generator=g) * 0.05).to(bf16)
         w12, wdr = shard_mlp_weights(wg, wu, wd, rank, world)
         try:
-            mlp = FusedTensorParallelSwiGLU(w12.to(dev), wdr.to(dev), max_tokens=m, comm_ctas=4,
+            mlp = FusedTensorParallelSwiGLU(w12.to(dev), wdr.to(dev), max_tokens=m, tile_split=2,
                                             cfg={"group_m": 2})
         except RuntimeError as exc:
             result["skip"] = str(exc)
@@ -127,7 +127,7 @@ def _run_fused(world, tmp_path):
 
 
 def test_in_kernel_exchange_with_one_participant(tmp_path):
-    """World size 1: the exchanging CTAs run the whole protocol (row-tile counters, multicast
+    """World size 1: the exchange crews run the whole protocol (row-tile counters, multicast
     signals, multimem sum and store, closing barrier, epochs) with a single rank."""
     _run_fused(1, tmp_path)
 

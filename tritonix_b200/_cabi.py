@@ -94,7 +94,7 @@ class MlpResources(ctypes.Structure):
 
 
 class MlpExchange(ctypes.Structure):
-    _fields_ = [("world", ctypes.c_int32), ("rank", ctypes.c_int32), ("comm_ctas", ctypes.c_int32),
+    _fields_ = [("world", ctypes.c_int32), ("rank", ctypes.c_int32), ("tile_split", ctypes.c_int32),
                 ("epoch", ctypes.c_uint32), ("signal_tiles", ctypes.c_int32),
                 ("reserved0", ctypes.c_int32), ("y_multicast", ctypes.c_void_p),
                 ("partial_local", ctypes.c_void_p), ("partial_multicast", ctypes.c_void_p),

@@ -27,21 +27,28 @@
 //  * Deterministic: no atomics on data, fixed summation order per tile.
 //  * Tensor parallel (optional): when the hidden dimension is split over `world` GPUs, every rank
 //    computes a partial Y and the partials must be summed.  The sum runs INSIDE this kernel, row
-//    tile by row tile, while later tiles are still being computed: the last few CTAs of the grid
-//    take no tiles; they watch a third counter (y_done: output tiles of a row tile stored), tell
-//    the other ranks through a multicast counter (multimem.red), wait until every rank has the
-//    row tile, and then sum their 1/world share of its rows across all ranks with
-//    multimem.ld_reduce and write the result to all ranks with multimem.st.  The partial outputs
-//    are kept in fp32 (a buffer of their own) and rounded to the output type only after the
-//    cross-rank sum, so the result carries ONE rounding, as on a single GPU.  The partial
-//    buffer, Y and the counters live in symmetric memory mapped into one multicast object; no
-//    TMA operation touches another GPU's memory.  The computing CTAs never wait for the
-//    exchanging ones.  Cross-rank counters are never reset: call number `epoch` waits for
-//    epoch * world arrivals.
+//    tile by row tile, while later tiles are still being computed.  A tensor-parallel launch has
+//    512 threads per CTA: warps 0-5 work as above, warps 6-15 of EVERY CTA form its exchange
+//    crew.  The crews share out the row tiles (each tile's share of rows is cut in `tile_split`
+//    pieces so that a burst of finished tiles spreads over many SMs).  For its piece a crew
+//    waits for a third counter (y_done: every output tile of the row tile stored), tells the
+//    other ranks through a multicast counter (multimem.red), waits until every rank has the row
+//    tile, then sums 256 / (world * tile_split) rows of it across all ranks with
+//    multimem.ld_reduce (the NVSwitch adds) and writes the result to all ranks with multimem.st.
+//    A multimem access costs an SM a few cycles whatever the number of threads behind it (about
+//    half a million 16-byte accesses per millisecond and SM were measured), so the exchange is
+//    spread over all SMs instead of being given a few of them.  The partial outputs are kept in
+//    fp32 (a buffer of their own) and rounded to the output type only after the cross-rank sum,
+//    so the result carries ONE rounding, as on a single GPU.  The partial buffer, Y and the
+//    counters live in symmetric memory mapped into one multicast object; no TMA operation
+//    touches another GPU's memory; the computing warps never wait for a crew.  Cross-rank
+//    counters are never reset: call number `epoch` waits for epoch * world arrivals.
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+
+#include <stdlib.h>
 
 #include <mutex>
 #include <utility>
@@ -58,7 +65,8 @@ constexpr int kRows = 128;       // rows per CTA (TMEM lanes); a pair owns 256
 constexpr int kTileN = 256;      // accumulator columns per unit
 constexpr int kLoadN = 128;      // B columns each CTA of the pair loads
 constexpr int kThreads = 192;         // producer warp, MMA warp, four epilogue warps
-constexpr int kExchangeThreads = 512; // block size of a tensor-parallel launch: more loads in flight per exchanging CTA
+constexpr int kExchangeThreads = 512; // block size of a tensor-parallel launch: warps 6..15 are the exchange crew
+constexpr int kCrewBarrier = 2;       // named barrier of the crew
 constexpr int kEpiThreads = 128;
 constexpr int kEpiBarrier = 1;
 constexpr int kAtomBytes = 128;
@@ -90,7 +98,8 @@ struct MlpParams {
   unsigned long long timeout_ns;
   // tensor-parallel exchange (world == 1: none of this is used)
   int world, rank;
-  int comm_ctas;           // CTAs at the end of the grid that only exchange (even: whole clusters)
+  int exchange;            // 1: tensor-parallel launch (fp32 partial outputs, crews sum them across ranks)
+  int tile_split;          // pieces a row tile's share of rows is cut into (one crew each)
   int* y_done;             // [tiles_m] CTAs that finished STORING a D unit of the row tile
   void* y_mc;              // multicast address of Y (the same buffer on every rank)
   long long ldy;           // row pitch of Y in elements
@@ -216,18 +225,20 @@ __device__ __forceinline__ bool wait_counter_sys(const unsigned* counter, unsign
 __device__ __forceinline__ void multimem_signal(unsigned* mc_counter) {
   asm volatile("multimem.red.release.sys.global.add.u32 [%0], 1;" ::"l"(mc_counter) : "memory");
 }
-// Four fp32 values summed over all GPUs of the multicast object (the switch adds them).
+// Four fp32 values summed over all GPUs of the multicast object (the switch adds them).  The
+// data accesses are weak: the counters' release/acquire pairs order them across the ranks
+// (relaxed.sys accesses measured the same).
 __device__ __forceinline__ float4 multimem_sum(const float* mc_addr) {
   float4 v;
-  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+  asm volatile("multimem.ld_reduce.weak.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
                : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
                : "l"(mc_addr)
                : "memory");
   return v;
 }
 __device__ __forceinline__ void multimem_store(void* mc_addr, const uint4& v) {
-  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr),
-               "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+  asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "r"(v.x),
+               "r"(v.y), "r"(v.z), "r"(v.w)
                : "memory");
 }
 
@@ -279,9 +290,7 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
   const uint32_t cta_rank = ptx::cluster_ctarank();
   const bool leader = cta_rank == 0;
   const int cluster_id = blockIdx.x >> 1;
-  // the last comm_ctas CTAs (whole clusters) exchange instead of computing
-  const int num_clusters = (static_cast<int>(gridDim.x) - p.comm_ctas) >> 1;
-  const bool exchanging = static_cast<int>(blockIdx.x) >= static_cast<int>(gridDim.x) - p.comm_ctas;
+  const int num_clusters = gridDim.x >> 1;
   volatile int* abort_flag = &ctrl->abort;
 
   if (threadIdx.x == 0) {
@@ -291,7 +300,7 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
     ptx::prefetch_tensormap(&tmap_h_ld);
     ptx::prefetch_tensormap(&tmap_w3);
     ptx::prefetch_tensormap(&tmap_y);
-    if (p.comm_ctas > 0) ptx::prefetch_tensormap(&tmap_part);
+    if (p.exchange) ptx::prefetch_tensormap(&tmap_part);
     for (int s = 0; s < p.stages; ++s) {
       ptx::mbar_init(ptx::smem_u32(&ctrl->full[s]), 1);
       ptx::mbar_init(ptx::smem_u32(&ctrl->empty[s]), 1);
@@ -316,40 +325,43 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = ctrl->tmem_base;
 
-  if (exchanging) {
-    // ===== cross-rank sum of Y, row tile by row tile (every thread of the CTA) =====
-    const int c = static_cast<int>(blockIdx.x) - (static_cast<int>(gridDim.x) - p.comm_ctas);
-    const int rows_per_rank = (2 * kRows) / p.world;
+  if (warp >= 6) {
+    // ===== exchange crew (tensor-parallel launches only): cross-rank sum of Y, piece by piece =====
+    const int crew_tid = threadIdx.x - kThreads;
+    const int crew_n = blockDim.x - kThreads;
+    const int rows_per_piece = (2 * kRows) / (p.world * p.tile_split);
     const int vec_per_row = p.n_out >> 3;  // 16-byte vectors (eight values) per output row
     char* y_mc = static_cast<char*>(p.y_mc);
+    const int pieces = p.tiles_m * p.tile_split;
     bool ok = true;
-    for (int t = c; t < p.tiles_m && ok; t += p.comm_ctas) {
-      if (threadIdx.x == 0) {
-        // this rank's partial rows are complete (every output tile of the row tile is stored) ...
-        bool got = wait_counter(p.y_done + t, 2 * p.n_d, abort_flag, p.status, p.timeout_ns);
-        if (got) {
-          multimem_signal(p.sig_mc + 1 + t);  // ... tell every rank ...
-          // ... and wait until every rank has said the same in this call
+    for (int j = blockIdx.x; j < pieces && ok; j += gridDim.x) {
+      const int t = j / p.tile_split, q = j - t * p.tile_split;
+      if (crew_tid == 0) {
+        bool got = true;
+        if (q == 0) {
+          // this rank's partial rows are complete (every output tile of the row tile is stored):
+          // tell every rank
+          got = wait_counter(p.y_done + t, 2 * p.n_d, abort_flag, p.status, p.timeout_ns);
+          if (got) multimem_signal(p.sig_mc + 1 + t);
+        }
+        // every rank has said so in this call
+        if (got)
           got = wait_counter_sys(p.sig_local + 1 + t, p.epoch * static_cast<unsigned>(p.world), abort_flag,
                                  p.status, p.timeout_ns);
-        }
         ctrl->flag = got ? 1 : 0;
       }
-      __syncthreads();
+      ptx::named_barrier_sync(kCrewBarrier, crew_n);
       ok = ctrl->flag != 0;
       if (ok) {
-        const int row_lo = t * 2 * kRows + p.rank * rows_per_rank;
-        const int rows = min(rows_per_rank, p.m - row_lo);
+        const int row_lo = t * 2 * kRows + (p.rank * p.tile_split + q) * rows_per_piece;
+        const int rows = min(rows_per_piece, p.m - row_lo);
         const int total = rows > 0 ? rows * vec_per_row : 0;
-        // A sum through the switch takes about ten microseconds to come back, so what an
-        // exchanging CTA moves per second is set by how much it keeps in flight: every thread
-        // has sixteen 16-byte sums outstanding before it converts and stores the first.
         constexpr int kVec = 8;  // output vectors (eight values each) per thread and round
-        for (int base = threadIdx.x; base < total; base += blockDim.x * kVec) {
+        for (int base = crew_tid; base < total; base += crew_n * kVec) {
           float4 lo[kVec], hi[kVec];
 #pragma unroll
           for (int i = 0; i < kVec; ++i) {
-            const int idx = base + i * static_cast<int>(blockDim.x);
+            const int idx = base + i * crew_n;
             const int safe = idx < total ? idx : base;
             const int r = safe / vec_per_row;
             const float* src = p.part_mc + static_cast<size_t>(row_lo + r) * p.n_out +
@@ -359,7 +371,7 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
           }
 #pragma unroll
           for (int i = 0; i < kVec; ++i) {
-            const int idx = base + i * static_cast<int>(blockDim.x);
+            const int idx = base + i * crew_n;
             if (idx < total) {
               const int r = idx / vec_per_row;
               const size_t off = (static_cast<size_t>(row_lo + r) * p.ldy +
@@ -374,22 +386,21 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
           }
         }
       }
-      __syncthreads();  // ctrl->flag is rewritten for the next row tile
+      ptx::named_barrier_sync(kCrewBarrier, crew_n);  // ctrl->flag is rewritten for the next piece
     }
     // Counters of row tiles this call does not have (it has fewer rows than the array was sized
     // for) advance all the same, so that "epoch * world" stays the target of every counter.
-    if (threadIdx.x == 0 && ok)
-      for (int t = p.tiles_m + c; t < p.sig_tiles; t += p.comm_ctas) multimem_signal(p.sig_mc + 1 + t);
-    // Every rank leaves only when all ranks have written all their shares: Y is complete
+    if (crew_tid == 0 && ok)
+      for (int t = p.tiles_m + blockIdx.x; t < p.sig_tiles; t += gridDim.x) multimem_signal(p.sig_mc + 1 + t);
+    // Every rank leaves only when all crews of all ranks have written their pieces: Y is complete
     // everywhere, and nobody still reads this rank's partial rows.
     __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x == 0) {
+    ptx::named_barrier_sync(kCrewBarrier, crew_n);
+    if (crew_tid == 0) {
       if (ok) {
         multimem_signal(p.sig_mc);
-        ok = wait_counter_sys(p.sig_local,
-                              p.epoch * static_cast<unsigned>(p.world) * static_cast<unsigned>(p.comm_ctas),
-                              abort_flag, p.status, p.timeout_ns);
+        ok = wait_counter_sys(p.sig_local, p.epoch * static_cast<unsigned>(p.world) * gridDim.x, abort_flag,
+                              p.status, p.timeout_ns);
       }
       if (!ok && p.status != nullptr) atomicCAS(p.status, 0, kAbortExchange);
     }
@@ -504,7 +515,7 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
       }
       if (!ok && p.status != nullptr) atomicCAS(p.status, 0, kAbortMma);
     }
-  } else if (warp < 6) {
+  } else {
     // ===== epilogue =====
     const int quarter = warp & 3;
     const int row_in_tile = quarter * 32 + lane;
@@ -520,7 +531,7 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
       const Unit un = decode_unit(p, u);
       const int row0 = ((un.down ? un.t : ring_tile(p, un.t)) * 2 + static_cast<int>(cta_rank)) * kRows;
       // (when ranks exchange, a D unit stores its fp32 accumulator as it is: 32 columns per chunk)
-      const bool raw = un.down && p.comm_ctas > 0;
+      const bool raw = un.down && p.exchange != 0;
       const CUtensorMap* map_c = raw ? &tmap_part : (un.down ? &tmap_y : &tmap_h_st);
       const int acc_per_chunk = raw ? 32 : (un.down ? 64 : 128);  // accumulator columns per 128-byte output row
       const int out_per_chunk = raw ? 32 : kAtomElems;            // output elements per 128-byte row
@@ -623,7 +634,7 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
         acc = 0;
         acc_phase ^= 1u;
       }
-      if ((!un.down || p.comm_ctas > 0) && epi_tid == 0) {
+      if ((!un.down || p.exchange != 0) && epi_tid == 0) {
         // Publish this CTA's part of H (or, when ranks exchange, of Y): the stores must have
         // landed (not merely have been read out of shared memory) before the counter moves.
         ptx::tma_store_wait_all<0>();
@@ -673,8 +684,7 @@ struct MlpPlan {
   int64_t counter_bytes, band_bytes;
 };
 
-int plan_mlp(const tnx_mlp_problem* p, const tnx_config* config, MlpPlan* plan, tnx_mlp_resources* out,
-             int comm_ctas = 0) {
+int plan_mlp(const tnx_mlp_problem* p, const tnx_config* config, MlpPlan* plan, tnx_mlp_resources* out) {
   if (p == nullptr || out == nullptr) {
     set_error("problem or out is NULL");
     return TNX_ERR_INVALID;
@@ -744,10 +754,10 @@ int plan_mlp(const tnx_mlp_problem* p, const tnx_config* config, MlpPlan* plan, 
   out->band_rows = plan->band * 2 * kRows;
   out->num_bands = plan->num_bands;
   const long long units = static_cast<long long>(plan->tiles_m) * (plan->n_g + plan->n_d);
-  int clusters = (sm_count() - comm_ctas) / 2;  // exchanging CTAs take SMs of their own
-  if (cfg.max_ctas > 0 && (cfg.max_ctas - comm_ctas) / 2 < clusters) clusters = (cfg.max_ctas - comm_ctas) / 2;
+  int clusters = sm_count() / 2;
+  if (cfg.max_ctas > 0 && cfg.max_ctas / 2 < clusters) clusters = cfg.max_ctas / 2;
   if (clusters < 1) clusters = 1;
-  out->grid = static_cast<int32_t>((units < clusters ? units : clusters) * 2 + comm_ctas);
+  out->grid = static_cast<int32_t>((units < clusters ? units : clusters) * 2);
   out->min_workspace_bytes = plan->counter_bytes + plan->ring_bands_min * plan->band_bytes;
   // Two bands measured best: a slot's previous readers are already a whole band of work ahead
   // of its next writers, and the smaller the ring the more of it stays in L2.
@@ -819,17 +829,18 @@ int tnx_swiglu_mlp(const tnx_mlp_problem* problem, const tnx_config* config, con
   using namespace tnx;
   MlpPlan plan;
   tnx_mlp_resources res;
-  int comm_ctas = 0;
-  // (world == 1 with comm_ctas > 0 is the degenerate exchange: same protocol, one participant)
-  if (exchange != nullptr && (exchange->world > 1 || exchange->comm_ctas > 0)) {
+  int tile_split = 0;  // > 0: tensor-parallel launch
+  // (world == 1 is the degenerate exchange: same protocol, one participant)
+  if (exchange != nullptr) {
     const tnx_mlp_exchange& ex = *exchange;
-    comm_ctas = ex.comm_ctas > 0 ? ex.comm_ctas : 8;
+    tile_split = ex.tile_split > 0 ? ex.tile_split : 4;
+    while (ex.world > 0 && tile_split > 1 && (2 * kRows) % (ex.world * tile_split) != 0) tile_split >>= 1;
     if (ex.world < 1 || ex.world > 2 * kRows || (2 * kRows) % ex.world != 0 || ex.rank < 0 || ex.rank >= ex.world ||
-        (comm_ctas % 2) != 0 || comm_ctas > 64 || ex.epoch == 0 ||
+        (2 * kRows) % (ex.world * tile_split) != 0 || ex.epoch == 0 ||
         ex.signal_tiles < (problem != nullptr ? (problem->m + 2 * kRows - 1) / (2 * kRows) : 0)) {
-      set_error("exchange: world must divide 256, 0 <= rank < world, comm_ctas even and <= 64, epoch >= 1, "
-                "signal_tiles >= row tiles (got world=%d rank=%d comm_ctas=%d epoch=%u signal_tiles=%d)",
-                ex.world, ex.rank, comm_ctas, ex.epoch, ex.signal_tiles);
+      set_error("exchange: world * tile_split must divide 256, 0 <= rank < world, epoch >= 1, signal_tiles >= "
+                "row tiles (got world=%d rank=%d tile_split=%d epoch=%u signal_tiles=%d)",
+                ex.world, ex.rank, ex.tile_split, ex.epoch, ex.signal_tiles);
       return TNX_ERR_INVALID;
     }
     if (ex.y_multicast == nullptr || ex.signal_multicast == nullptr || ex.signal_local == nullptr ||
@@ -842,7 +853,7 @@ int tnx_swiglu_mlp(const tnx_mlp_problem* problem, const tnx_config* config, con
       return TNX_ERR_INVALID;
     }
   }
-  int rc = plan_mlp(problem, config, &plan, &res, comm_ctas);
+  int rc = plan_mlp(problem, config, &plan, &res);
   if (rc != TNX_OK) return rc;
   if (x == nullptr || w12 == nullptr || w3 == nullptr || y == nullptr || workspace == nullptr) {
     set_error("NULL operand or workspace pointer");
@@ -881,7 +892,7 @@ int tnx_swiglu_mlp(const tnx_mlp_problem* problem, const tnx_config* config, con
   if (rc == TNX_OK) rc = make_tmap_2d(&tw3, w3, p.dtype, p.n_out, p.d_ff, p.stride_w3k, kAtomElems, tk, true);
   if (rc == TNX_OK) rc = make_tmap_2d(&ty, y, p.dtype, p.n_out, p.m, p.stride_ym, kAtomElems, kRows, false);
   tpart = ty;  // (a valid map; only read when ranks exchange)
-  if (rc == TNX_OK && comm_ctas > 0)
+  if (rc == TNX_OK && tile_split > 0)
     rc = make_tmap_2d(&tpart, exchange->partial_local, TNX_F32, p.n_out, p.m, p.n_out, 32, kRows, false);
   if (rc != TNX_OK) return rc;
 
@@ -908,10 +919,11 @@ int tnx_swiglu_mlp(const tnx_mlp_problem* problem, const tnx_config* config, con
   kp.timeout_ns = bounded_wait_limit_ns();
   kp.world = 1;
   kp.y_done = counters + 2 * plan.tiles_m;
-  if (comm_ctas > 0) {
+  if (tile_split > 0) {
+    kp.exchange = 1;
+    kp.tile_split = tile_split;
     kp.world = exchange->world;
     kp.rank = exchange->rank;
-    kp.comm_ctas = comm_ctas;
     kp.y_mc = exchange->y_multicast;
     kp.ldy = p.stride_ym;
     kp.part_mc = static_cast<const float*>(exchange->partial_multicast);
@@ -931,7 +943,7 @@ int tnx_swiglu_mlp(const tnx_mlp_problem* problem, const tnx_config* config, con
   }
   cudaLaunchConfig_t lc = {};
   lc.gridDim = dim3(res.grid, 1, 1);
-  lc.blockDim = dim3(comm_ctas > 0 ? kExchangeThreads : kThreads, 1, 1);
+  lc.blockDim = dim3(tile_split > 0 ? kExchangeThreads : kThreads, 1, 1);
   lc.dynamicSmemBytes = res.smem_bytes;
   lc.stream = s;
   cudaLaunchAttribute attr[1];
@@ -949,12 +961,7 @@ int tnx_swiglu_mlp(const tnx_mlp_problem* problem, const tnx_config* config, con
     (void)cudaGetLastError();
     return TNX_ERR_CUDA;
   }
-  // (the exchanging CTAs are the last of the grid, whatever its size; at least one cluster computes)
   if (static_cast<int>(lc.gridDim.x) > fit * 2) lc.gridDim.x = static_cast<unsigned>(fit * 2);
-  if (static_cast<int>(lc.gridDim.x) < comm_ctas + 2) {
-    set_error("the GPU cannot hold %d exchanging CTAs next to a computing cluster", comm_ctas);
-    return TNX_ERR_CUDA;
-  }
   e = cudaLaunchKernelEx(&lc, fn, tx, tw12, thst, thld, tw3, ty, tpart, kp);
   if (e != cudaSuccess) {
     set_error("kernel launch failed: %s", cudaGetErrorString(e));

@@ -193,10 +193,11 @@ class TensorParallelSwiGLU:
 class FusedTensorParallelSwiGLU:
     """The tensor-parallel SwiGLU MLP as ONE kernel per rank and step: the one-launch MLP kernel
     (``tnx_swiglu_mlp``) computes this rank's hidden units and its partial output row tile by row
-    tile, and a few of its CTAs sum the partial outputs across the ranks as the row tiles
-    complete — ``multimem.ld_reduce`` / ``multimem.st`` through an NVLink multicast mapping of the
-    output buffer — so the exchange is spread over the whole step instead of following it.  No
-    collective library call is made in ``forward``.
+    tile, and ten spare warps of every CTA sum the partial outputs across the ranks as the row
+    tiles complete — ``multimem.ld_reduce`` / ``multimem.st`` through an NVLink multicast mapping
+    — so the exchange is spread over the whole step and over all SMs instead of following the
+    step.  ``tile_split`` crews share one row tile.  No collective library call is made in
+    ``forward``.
 
     The output buffer, the fp32 partial outputs (summed across the ranks before the one rounding
     to the output type) and the exchange counters live in symmetric memory
@@ -210,7 +211,7 @@ class FusedTensorParallelSwiGLU:
     """
 
     def __init__(self, w12_shard: torch.Tensor, w_down_shard: torch.Tensor, max_tokens: int,
-                 group: Optional[dist.ProcessGroup] = None, comm_ctas: int = 8,
+                 group: Optional[dist.ProcessGroup] = None, tile_split: int = 4,
                  cfg: Optional[dict] = None):
         import torch.distributed._symmetric_memory as symm
 
@@ -224,7 +225,7 @@ class FusedTensorParallelSwiGLU:
         if 256 % self.world:
             raise ValueError("the in-kernel exchange splits 256-row tiles over the ranks: "
                              f"world size {self.world} does not divide 256")
-        self.comm_ctas = int(comm_ctas)
+        self.tile_split = int(tile_split)
         self.cfg = dict(cfg or {})
         self.d_out = w_down_shard.shape[1]
         self.max_tokens = int(max_tokens)
@@ -268,7 +269,7 @@ class FusedTensorParallelSwiGLU:
         self._epoch += 1
         local = self._buf.data_ptr()
         part, sig = self._y_bytes, self._y_bytes + self._part_bytes
-        exchange = cabi.MlpExchange(self.world, self.rank, self.comm_ctas, self._epoch, self._tiles, 0,
+        exchange = cabi.MlpExchange(self.world, self.rank, self.tile_split, self._epoch, self._tiles, 0,
                                     self._mc, local + part, self._mc + part, self._mc + sig, local + sig)
         cabi.launch_mlp(x, self.w12, self.w_down, y, self.cfg, cabi.EPI_GLU_SILU, exchange=exchange)
         return y
