@@ -311,7 +311,7 @@ def _mlp_weight_blocks(dev, lo, hi):
     return wg, wu, wd
 
 
-def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1, mode="auto", tile_split=4, band=8, tokens=0):
+def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1, mode="auto", tile_split=16, band=8, tokens=0):
     """SwiGLU MLP, tensor parallel: hidden units split over the ranks (column-parallel gate/up,
     row-parallel down projection), partial outputs summed across the ranks.  Global weights come
     from fixed seeds and are sliced, so every world size computes the same function.
@@ -396,7 +396,7 @@ def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1, mode="auto", tile_split=4
         cfg = {"one_launch": dict(fused_cfg, tile_m=256, tile_n=256, cta_group=2)}
         launches = 1
         exchange = ("inside the kernel: fp32 partial outputs summed with multimem.ld_reduce / multimem.st per "
-                    "256-row tile by ten spare warps of every CTA, %d crews per tile" % tile_split) \
+                    "256-row tile by two extra warps of every CTA, %d crews per tile" % tile_split) \
             if world > 1 else "none (one GPU)"
     else:
         cfg = {"gate_up": GLU_CFG, "down": GEMM_CFG}
@@ -832,7 +832,7 @@ def main():
                     help="mlp: which implementation `value` times (auto: two_launch on one GPU, one_launch "
                          "on several when the NVLink multicast mapping is available); the other one is "
                          "timed too, from the same rest, and reported under `variants`")
-    ap.add_argument("--tile-split", type=int, default=4,
+    ap.add_argument("--tile-split", type=int, default=16,
                     help="mlp one_launch on >1 GPU: CTAs whose spare warps share one row tile's exchange")
     ap.add_argument("--mlp-band", type=int, default=8,
                     help="mlp one_launch: 256-row tiles per band")

@@ -241,9 +241,9 @@ typedef struct tnx_mlp_resources {
  *   - every rank makes the same sequence of calls with the same m, n_out, tile_split and
  *     signal_tiles (m may change from call to call), on the same GPU model (the closing barrier
  *     counts the CTAs of every rank's grid).
- * A tensor-parallel launch has 512 threads per CTA: ten warps of every CTA form a crew that
- * exchanges while the other six compute.  tile_split (1, 2, 4 ...; 0 = 4; world * tile_split must
- * divide 256) is the number of crews that share one row tile's exchange.
+ * A tensor-parallel launch has 256 threads per CTA: two warps of every CTA form a crew that
+ * exchanges while the other six compute.  tile_split (1, 2, 4 ...; 0 = 16, halved until
+ * world * tile_split divides 256) is the number of crews that share one row tile's exchange.
  */
 typedef struct tnx_mlp_exchange {
   int32_t world, rank;

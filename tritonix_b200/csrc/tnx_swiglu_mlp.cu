@@ -28,16 +28,19 @@
 //  * Tensor parallel (optional): when the hidden dimension is split over `world` GPUs, every rank
 //    computes a partial Y and the partials must be summed.  The sum runs INSIDE this kernel, row
 //    tile by row tile, while later tiles are still being computed.  A tensor-parallel launch has
-//    512 threads per CTA: warps 0-5 work as above, warps 6-15 of EVERY CTA form its exchange
+//    256 threads per CTA: warps 0-5 work as above, warps 6-7 of EVERY CTA form its exchange
 //    crew.  The crews share out the row tiles (each tile's share of rows is cut in `tile_split`
 //    pieces so that a burst of finished tiles spreads over many SMs).  For its piece a crew
 //    waits for a third counter (y_done: every output tile of the row tile stored), tells the
 //    other ranks through a multicast counter (multimem.red), waits until every rank has the row
 //    tile, then sums 256 / (world * tile_split) rows of it across all ranks with
 //    multimem.ld_reduce (the NVSwitch adds) and writes the result to all ranks with multimem.st.
-//    A multimem access costs an SM a few cycles whatever the number of threads behind it (about
-//    half a million 16-byte accesses per millisecond and SM were measured), so the exchange is
-//    spread over all SMs instead of being given a few of them.  The partial outputs are kept in
+//    A multimem access occupies an SM's load/store path for a few cycles whatever the number of
+//    threads behind it (about half a million 16-byte accesses per millisecond and SM were
+//    measured), and a crew that saturates that path starves the barrier polls and shared-memory
+//    stores of the computing warps next to it.  Hence small crews (two warps: their own latency
+//    throttles them to a fraction of that rate) on ALL SMs, and small pieces, instead of a few
+//    SMs that do nothing else.  The partial outputs are kept in
 //    fp32 (a buffer of their own) and rounded to the output type only after the cross-rank sum,
 //    so the result carries ONE rounding, as on a single GPU.  The partial buffer, Y and the
 //    counters live in symmetric memory mapped into one multicast object; no TMA operation
@@ -65,7 +68,7 @@ constexpr int kRows = 128;       // rows per CTA (TMEM lanes); a pair owns 256
 constexpr int kTileN = 256;      // accumulator columns per unit
 constexpr int kLoadN = 128;      // B columns each CTA of the pair loads
 constexpr int kThreads = 192;         // producer warp, MMA warp, four epilogue warps
-constexpr int kExchangeThreads = 512; // block size of a tensor-parallel launch: warps 6..15 are the exchange crew
+constexpr int kExchangeThreads = 256; // block size of a tensor-parallel launch: warps 6 and 7 are the exchange crew
 constexpr int kCrewBarrier = 2;       // named barrier of the crew
 constexpr int kEpiThreads = 128;
 constexpr int kEpiBarrier = 1;
@@ -833,7 +836,7 @@ int tnx_swiglu_mlp(const tnx_mlp_problem* problem, const tnx_config* config, con
   // (world == 1 is the degenerate exchange: same protocol, one participant)
   if (exchange != nullptr) {
     const tnx_mlp_exchange& ex = *exchange;
-    tile_split = ex.tile_split > 0 ? ex.tile_split : 4;
+    tile_split = ex.tile_split > 0 ? ex.tile_split : 16;
     while (ex.world > 0 && tile_split > 1 && (2 * kRows) % (ex.world * tile_split) != 0) tile_split >>= 1;
     if (ex.world < 1 || ex.world > 2 * kRows || (2 * kRows) % ex.world != 0 || ex.rank < 0 || ex.rank >= ex.world ||
         (2 * kRows) % (ex.world * tile_split) != 0 || ex.epoch == 0 ||
@@ -930,7 +933,6 @@ int tnx_swiglu_mlp(const tnx_mlp_problem* problem, const tnx_config* config, con
     kp.sig_mc = exchange->signal_multicast;
     kp.sig_local = exchange->signal_local;
     kp.sig_tiles = exchange->signal_tiles;
-    kp.epoch = exchange->epoch;
   }
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);

@@ -193,7 +193,7 @@ class TensorParallelSwiGLU:
 class FusedTensorParallelSwiGLU:
     """The tensor-parallel SwiGLU MLP as ONE kernel per rank and step: the one-launch MLP kernel
     (``tnx_swiglu_mlp``) computes this rank's hidden units and its partial output row tile by row
-    tile, and ten spare warps of every CTA sum the partial outputs across the ranks as the row
+    tile, and two extra warps of every CTA sum the partial outputs across the ranks as the row
     tiles complete — ``multimem.ld_reduce`` / ``multimem.st`` through an NVLink multicast mapping
     — so the exchange is spread over the whole step and over all SMs instead of following the
     step.  ``tile_split`` crews share one row tile.  No collective library call is made in
@@ -211,7 +211,7 @@ class FusedTensorParallelSwiGLU:
     """
 
     def __init__(self, w12_shard: torch.Tensor, w_down_shard: torch.Tensor, max_tokens: int,
-                 group: Optional[dist.ProcessGroup] = None, tile_split: int = 4,
+                 group: Optional[dist.ProcessGroup] = None, tile_split: int = 16,
                  cfg: Optional[dict] = None):
         import torch.distributed._symmetric_memory as symm
 
