@@ -96,21 +96,30 @@ def _fused_worker(rank, world, port, out_dir):
         except RuntimeError as exc:
             result["skip"] = str(exc)
         else:
-            ref = O.swiglu_mlp_oracle(x, torch.stack((wg, wu), 2).reshape(d, 2 * ff), wd)
-            xd = x.to(dev)
-            outs = []
-            for _ in range(3):                 # the counters are never reset: epochs 1, 2, 3
-                y = mlp(xd)
+            import time
+            w12_global = torch.stack((wg, wu), 2).reshape(d, 2 * ff)
+            # Different tokens in every call, so that a sum that read a peer's previous (or not yet
+            # written) partial output cannot pass; and one rank arrives late to its first two
+            # calls, so that the others really have to wait for it inside the kernel.
+            inputs = [x, (-0.5 * x.flip(0)).contiguous(), x.roll(7, 0).contiguous()]
+            errs, outs = [], []
+            for call, xc in enumerate(inputs):      # the counters are never reset: epochs 1, 2, 3
+                if rank == world - 1 and call < 2:
+                    time.sleep(0.3)
+                y = mlp(xc.to(dev))
                 tnx.check_status(dev)
                 outs.append(y.clone())
-            result["err"] = max(O.rel_err(o.cpu(), ref) for o in outs)
-            result["repeatable"] = all(torch.equal(outs[0], o) for o in outs[1:])
-            gathered = [torch.empty_like(outs[0]) for _ in range(world)]
-            dist.all_gather(gathered, outs[0])
-            result["same"] = all(torch.equal(gathered[0], t) for t in gathered)
-            short = mlp(xd[:700])              # fewer tokens than the instance was sized for
+                errs.append(O.rel_err(outs[-1].cpu(), O.swiglu_mlp_oracle(xc, w12_global, wd)))
+            result["err"] = max(errs)
+            again = mlp(inputs[0].to(dev))
             tnx.check_status(dev)
-            result["err_short"] = O.rel_err(short.cpu(), ref[:700])
+            result["repeatable"] = torch.equal(again, outs[0])
+            gathered = [torch.empty_like(outs[1]) for _ in range(world)]
+            dist.all_gather(gathered, outs[1])
+            result["same"] = all(torch.equal(gathered[0], t) for t in gathered)
+            short = mlp(x[:700].to(dev))           # fewer tokens than the instance was sized for
+            tnx.check_status(dev)
+            result["err_short"] = O.rel_err(short.cpu(), O.swiglu_mlp_oracle(x[:700], w12_global, wd))
         torch.save(result, os.path.join(out_dir, f"f{rank}.pt"))
     finally:
         dist.destroy_process_group()

@@ -51,8 +51,6 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
-#include <stdlib.h>
-
 #include <mutex>
 #include <utility>
 #include <vector>
@@ -107,6 +105,7 @@ struct MlpParams {
   void* y_mc;              // multicast address of Y (the same buffer on every rank)
   long long ldy;           // row pitch of Y in elements
   const float* part_mc;    // multicast address of the fp32 partial outputs ([rows, n_out], pitch n_out)
+  float* part_local;       // this rank's mapping of the same buffer
   unsigned* sig_mc;        // [1 + sig_tiles] arrival counters: multicast address ...
   const unsigned* sig_local;  // ... and this rank's copy.  [0]: closing barrier; [1 + t]: row tile t
   int sig_tiles;           // row-tile counters in the array (>= tiles_m)
@@ -223,24 +222,32 @@ __device__ __forceinline__ bool wait_counter_sys(const unsigned* counter, unsign
     }
   }
 }
+// The multicast address and a GPU's own (unicast) address of the same bytes are virtual aliases:
+// accesses made through one are ordered with accesses made through the other only across this
+// fence (the partial outputs are written through the unicast alias and read through the
+// multicast one; Y and the counters the other way round).
+__device__ __forceinline__ void fence_proxy_alias() {
+  asm volatile("fence.proxy.alias;" ::: "memory");
+}
 // Adds 1 to the counter's copy on every GPU of the multicast object; earlier writes of this
 // thread (and those it has observed) are visible to whoever acquires the new value.
 __device__ __forceinline__ void multimem_signal(unsigned* mc_counter) {
   asm volatile("multimem.red.release.sys.global.add.u32 [%0], 1;" ::"l"(mc_counter) : "memory");
 }
 // Four fp32 values summed over all GPUs of the multicast object (the switch adds them).  The
-// data accesses are weak: the counters' release/acquire pairs order them across the ranks
-// (relaxed.sys accesses measured the same).
+// data accesses are relaxed at system scope, so that the fences and the counters'
+// release/acquire pairs order them across the ranks: with .weak accesses (same speed) a rank was
+// seen to leave the closing barrier before all of a peer's multimem.st had landed in its memory.
 __device__ __forceinline__ float4 multimem_sum(const float* mc_addr) {
   float4 v;
-  asm volatile("multimem.ld_reduce.weak.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
                : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
                : "l"(mc_addr)
                : "memory");
   return v;
 }
 __device__ __forceinline__ void multimem_store(void* mc_addr, const uint4& v) {
-  asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "r"(v.x),
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "r"(v.x),
                "r"(v.y), "r"(v.z), "r"(v.w)
                : "memory");
 }
@@ -274,7 +281,7 @@ __global__ void __launch_bounds__(kExchangeThreads, 1)
 swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w12,
                   const __grid_constant__ CUtensorMap tmap_h_st, const __grid_constant__ CUtensorMap tmap_h_ld,
                   const __grid_constant__ CUtensorMap tmap_w3, const __grid_constant__ CUtensorMap tmap_y,
-                  const __grid_constant__ CUtensorMap tmap_part, const MlpParams p) {
+                  const MlpParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
   const uint32_t base_addr = (raw_addr + 1023u) & ~1023u;
@@ -303,7 +310,6 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
     ptx::prefetch_tensormap(&tmap_h_ld);
     ptx::prefetch_tensormap(&tmap_w3);
     ptx::prefetch_tensormap(&tmap_y);
-    if (p.exchange) ptx::prefetch_tensormap(&tmap_part);
     for (int s = 0; s < p.stages; ++s) {
       ptx::mbar_init(ptx::smem_u32(&ctrl->full[s]), 1);
       ptx::mbar_init(ptx::smem_u32(&ctrl->empty[s]), 1);
@@ -345,6 +351,7 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
           // this rank's partial rows are complete (every output tile of the row tile is stored):
           // tell every rank
           got = wait_counter(p.y_done + t, 2 * p.n_d, abort_flag, p.status, p.timeout_ns);
+          fence_proxy_alias();
           if (got) multimem_signal(p.sig_mc + 1 + t);
         }
         // every rank has said so in this call
@@ -355,6 +362,7 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
       }
       ptx::named_barrier_sync(kCrewBarrier, crew_n);
       ok = ctrl->flag != 0;
+      fence_proxy_alias();  // the sums below go through the multicast alias
       if (ok) {
         const int row_lo = t * 2 * kRows + (p.rank * p.tile_split + q) * rows_per_piece;
         const int rows = min(rows_per_piece, p.m - row_lo);
@@ -397,6 +405,7 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
       for (int t = p.tiles_m + blockIdx.x; t < p.sig_tiles; t += gridDim.x) multimem_signal(p.sig_mc + 1 + t);
     // Every rank leaves only when all crews of all ranks have written their pieces: Y is complete
     // everywhere, and nobody still reads this rank's partial rows.
+    fence_proxy_alias();
     __threadfence_system();
     ptx::named_barrier_sync(kCrewBarrier, crew_n);
     if (crew_tid == 0) {
@@ -404,6 +413,7 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
         multimem_signal(p.sig_mc);
         ok = wait_counter_sys(p.sig_local, p.epoch * static_cast<unsigned>(p.world) * gridDim.x, abort_flag,
                               p.status, p.timeout_ns);
+        fence_proxy_alias();  // Y was written through the multicast alias; it is read through the unicast one
       }
       if (!ok && p.status != nullptr) atomicCAS(p.status, 0, kAbortExchange);
     }
@@ -533,11 +543,10 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
     for (int u = cluster_id; u < p.total_units && ok; u += num_clusters) {
       const Unit un = decode_unit(p, u);
       const int row0 = ((un.down ? un.t : ring_tile(p, un.t)) * 2 + static_cast<int>(cta_rank)) * kRows;
-      // (when ranks exchange, a D unit stores its fp32 accumulator as it is: 32 columns per chunk)
+      // (when ranks exchange, a D unit stores its fp32 accumulator as it is, with plain stores)
       const bool raw = un.down && p.exchange != 0;
-      const CUtensorMap* map_c = raw ? &tmap_part : (un.down ? &tmap_y : &tmap_h_st);
-      const int acc_per_chunk = raw ? 32 : (un.down ? 64 : 128);  // accumulator columns per 128-byte output row
-      const int out_per_chunk = raw ? 32 : kAtomElems;            // output elements per 128-byte row
+      const CUtensorMap* map_c = un.down ? &tmap_y : &tmap_h_st;
+      const int acc_per_chunk = un.down ? 64 : 128;  // accumulator columns per 128-byte output row
       const int out_col0 = un.j * (un.down ? kTileN : kTileN / 2);
       const int out_cols = un.down ? p.n_out : p.d_ff;
 
@@ -560,9 +569,30 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
       }
       ptx::tc_fence_after_sync();
       const uint32_t t_acc = tmem_base + lane_sel + acc * kTileN;
-      const int chunks = kTileN / acc_per_chunk;
+      if (raw) {
+        // This rank's fp32 partial rows, straight from registers (each thread a row: 128 contiguous
+        // bytes per step).  Plain stores, so that the fence below orders them for the other GPUs.
+        const int row = row0 + row_in_tile;
+        float* dst = p.part_local + static_cast<size_t>(row) * p.n_out + out_col0;
+        for (int chunk = 0; chunk < kTileN / 32; ++chunk) {
+          const int col = chunk * 32;
+          if (out_col0 + col >= p.n_out) break;
+          uint32_t r[32];
+          ptx::tmem_ld_32x32(t_acc + col, r);
+          ptx::tmem_ld_wait();
+          if (row < p.m) {
+#pragma unroll
+            for (int piece = 0; piece < 8; ++piece)
+              if (out_col0 + col + piece * 4 < p.n_out)
+                *reinterpret_cast<float4*>(dst + col + piece * 4) =
+                    make_float4(__uint_as_float(r[piece * 4]), __uint_as_float(r[piece * 4 + 1]),
+                                __uint_as_float(r[piece * 4 + 2]), __uint_as_float(r[piece * 4 + 3]));
+          }
+        }
+      }
+      const int chunks = raw ? 0 : kTileN / acc_per_chunk;
       for (int chunk = 0; chunk < chunks; ++chunk) {
-        const int out_col = out_col0 + chunk * out_per_chunk;
+        const int out_col = out_col0 + chunk * kAtomElems;
         if (out_col >= out_cols) break;
         const uint32_t buf = smem_out + (stores & 1u) * kStagingBytes;
         if (epi_tid == 0) ptx::tma_store_wait_read<1>();
@@ -586,16 +616,6 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
               st_shared_v4(buf + stage_row + pos * 16, o[piece * 4], o[piece * 4 + 1], o[piece * 4 + 2],
                            o[piece * 4 + 3]);
             }
-          }
-        } else if (raw) {
-          uint32_t r[32];
-          ptx::tmem_ld_32x32(t_acc + chunk * 32, r);
-          ptx::tmem_ld_wait();
-#pragma unroll
-          for (int piece = 0; piece < 8; ++piece) {
-            const uint32_t pos = static_cast<uint32_t>(piece) ^ sw;
-            st_shared_v4(buf + stage_row + pos * 16, r[piece * 4], r[piece * 4 + 1], r[piece * 4 + 2],
-                         r[piece * 4 + 3]);
           }
         } else {
 #pragma unroll
@@ -637,13 +657,20 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
         acc = 0;
         acc_phase ^= 1u;
       }
-      if ((!un.down || p.exchange != 0) && epi_tid == 0) {
-        // Publish this CTA's part of H (or, when ranks exchange, of Y): the stores must have
-        // landed (not merely have been read out of shared memory) before the counter moves.
+      if (raw) {
+        // Publish this CTA's partial rows of Y: every thread orders its stores for the whole
+        // system (other GPUs read them through the multicast mapping), then one counts the CTA in.
+        fence_proxy_alias();
+        __threadfence_system();
+        ptx::named_barrier_sync(kEpiBarrier, kEpiThreads);
+        if (epi_tid == 0) atomicAdd(p.y_done + un.t, 1);
+      } else if (!un.down && epi_tid == 0) {
+        // Publish this CTA's part of H: the stores must have landed (not merely have been read
+        // out of shared memory) before the counter moves.
         ptx::tma_store_wait_all<0>();
         fence_proxy_async_global();
         __threadfence();
-        atomicAdd((un.down ? p.y_done : p.g_done) + un.t, 1);
+        atomicAdd(p.g_done + un.t, 1);
       }
     }
     if (epi_tid == 0) ptx::tma_store_wait_all<0>();
@@ -670,7 +697,7 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
 }
 
 using MlpKernelFn = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
-                             const CUtensorMap, const CUtensorMap, const CUtensorMap, const MlpParams);
+                             const CUtensorMap, const CUtensorMap, const MlpParams);
 
 MlpKernelFn pick_mlp_kernel(int tile_k, int dtype) {
   if (tile_k == 64) return dtype == TNX_BF16 ? swiglu_mlp_kernel<64, true> : swiglu_mlp_kernel<64, false>;
@@ -887,16 +914,13 @@ int tnx_swiglu_mlp(const tnx_mlp_problem* problem, const tnx_config* config, con
   void* h = static_cast<char*>(workspace) + plan.counter_bytes;
   const int64_t h_rows = ring * plan.band * 2 * kRows;
   const int tk = plan.cfg.tile_k;
-  CUtensorMap tx, tw12, thst, thld, tw3, ty, tpart;
+  CUtensorMap tx, tw12, thst, thld, tw3, ty;
   rc = make_tmap_2d(&tx, x, p.dtype, p.d_model, p.m, p.stride_xm, kAtomElems, kRows, true);
   if (rc == TNX_OK) rc = make_tmap_2d(&tw12, w12, p.dtype, 2LL * p.d_ff, p.d_model, p.stride_w12k, kAtomElems, tk, true);
   if (rc == TNX_OK) rc = make_tmap_2d(&thst, h, p.dtype, p.d_ff, h_rows, p.d_ff, kAtomElems, kRows, false);
   if (rc == TNX_OK) rc = make_tmap_2d(&thld, h, p.dtype, p.d_ff, h_rows, p.d_ff, kAtomElems, kRows, true);
   if (rc == TNX_OK) rc = make_tmap_2d(&tw3, w3, p.dtype, p.n_out, p.d_ff, p.stride_w3k, kAtomElems, tk, true);
   if (rc == TNX_OK) rc = make_tmap_2d(&ty, y, p.dtype, p.n_out, p.m, p.stride_ym, kAtomElems, kRows, false);
-  tpart = ty;  // (a valid map; only read when ranks exchange)
-  if (rc == TNX_OK && tile_split > 0)
-    rc = make_tmap_2d(&tpart, exchange->partial_local, TNX_F32, p.n_out, p.m, p.n_out, 32, kRows, false);
   if (rc != TNX_OK) return rc;
 
   MlpParams kp = {};
@@ -930,9 +954,11 @@ int tnx_swiglu_mlp(const tnx_mlp_problem* problem, const tnx_config* config, con
     kp.y_mc = exchange->y_multicast;
     kp.ldy = p.stride_ym;
     kp.part_mc = static_cast<const float*>(exchange->partial_multicast);
+    kp.part_local = exchange->partial_local;
     kp.sig_mc = exchange->signal_multicast;
     kp.sig_local = exchange->signal_local;
     kp.sig_tiles = exchange->signal_tiles;
+    kp.epoch = exchange->epoch;
   }
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -964,7 +990,7 @@ int tnx_swiglu_mlp(const tnx_mlp_problem* problem, const tnx_config* config, con
     return TNX_ERR_CUDA;
   }
   if (static_cast<int>(lc.gridDim.x) > fit * 2) lc.gridDim.x = static_cast<unsigned>(fit * 2);
-  e = cudaLaunchKernelEx(&lc, fn, tx, tw12, thst, thld, tw3, ty, tpart, kp);
+  e = cudaLaunchKernelEx(&lc, fn, tx, tw12, thst, thld, tw3, ty, kp);
   if (e != cudaSuccess) {
     set_error("kernel launch failed: %s", cudaGetErrorString(e));
     (void)cudaGetLastError();
