@@ -311,7 +311,8 @@ def _mlp_weight_blocks(dev, lo, hi):
     return wg, wu, wd
 
 
-def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1, mode="auto", tile_split=16, band=8, tokens=0):
+def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1, mode="auto", tile_split=16, band=8, tokens=0,
+              fp32_partials=False):
     """SwiGLU MLP, tensor parallel: hidden units split over the ranks (column-parallel gate/up,
     row-parallel down projection), partial outputs summed across the ranks.  Global weights come
     from fixed seeds and are sliced, so every world size computes the same function.
@@ -339,7 +340,8 @@ def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1, mode="auto", tile_split=1
     fused_note = None
     if world > 1:
         try:
-            fused = FusedTensorParallelSwiGLU(w12, wd, max_tokens=m, tile_split=tile_split, cfg=fused_cfg)
+            fused = FusedTensorParallelSwiGLU(w12, wd, max_tokens=m, tile_split=tile_split, cfg=fused_cfg,
+                                              fp32_partials=fp32_partials)
         except Exception as exc:  # no multicast mapping on this system: the NCCL path remains
             fused_note = f"{type(exc).__name__}: {exc}"[:200]
 
@@ -395,8 +397,9 @@ def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1, mode="auto", tile_split=1
     if mode == "one_launch":
         cfg = {"one_launch": dict(fused_cfg, tile_m=256, tile_n=256, cta_group=2)}
         launches = 1
-        exchange = ("inside the kernel: fp32 partial outputs summed with multimem.ld_reduce / multimem.st per "
-                    "256-row tile by two extra warps of every CTA, %d crews per tile" % tile_split) \
+        exchange = ("inside the kernel: %s partial outputs summed with multimem.ld_reduce / multimem.st per "
+                    "256-row tile by two extra warps of every CTA, %d crews per tile"
+                    % ("fp32" if fp32_partials else "bf16", tile_split)) \
             if world > 1 else "none (one GPU)"
     else:
         cfg = {"gate_up": GLU_CFG, "down": GEMM_CFG}
@@ -494,7 +497,7 @@ def measure(workload, args, rank, local_rank, world, dev, D, peaks):
     if workload == "mlp":
         chunks = [float(v) for v in args.chunk_weights.split(",")] if args.chunk_weights else args.chunks
         step, e2e_step, work = setup_mlp(rank, world, dev, chunks, args.comm_sms, args.mlp_mode,
-                                         args.tile_split, args.mlp_band, args.mlp_tokens)
+                                         args.tile_split, args.mlp_band, args.mlp_tokens, args.fp32_partials)
     elif workload == "conv":
         step, e2e_step, work = setup_conv(rank, world, dev, json.loads(args.cfg) if args.cfg else None)
     else:
@@ -832,6 +835,8 @@ def main():
                     help="mlp: which implementation `value` times (auto: two_launch on one GPU, one_launch "
                          "on several when the NVLink multicast mapping is available); the other one is "
                          "timed too, from the same rest, and reported under `variants`")
+    ap.add_argument("--fp32-partials", action="store_true",
+                    help="mlp one_launch on >1 GPU: exchange fp32 partial outputs (one rounding) instead of bf16")
     ap.add_argument("--tile-split", type=int, default=16,
                     help="mlp one_launch on >1 GPU: CTAs whose spare warps share one row tile's exchange")
     ap.add_argument("--mlp-band", type=int, default=8,

@@ -230,7 +230,10 @@ typedef struct tnx_mlp_resources {
  *     rank allocated symmetrically and bound to ONE multicast object; y_multicast is the
  *     multicast address of the same bytes;
  *   - partial_local / partial_multicast: likewise for a buffer of m x n_out fp32 values (rows
- *     contiguous, pitch n_out) that receives this rank's partial outputs;
+ *     contiguous, pitch n_out) that receives this rank's partial outputs.  Both may be NULL:
+ *     the partial outputs are then rounded to the output type, stored in Y and summed in place
+ *     (fp32 accumulation in the switch, a second rounding) — half the NVLink traffic, for an
+ *     error of about two roundings instead of one;
  *   - signal_local / signal_multicast: likewise for an array of 1 + signal_tiles uint32
  *     counters (signal_tiles >= (m + 255) / 256 for the largest m ever passed with these
  *     buffers), zero before the first call and never written by the caller afterwards;
@@ -239,8 +242,7 @@ typedef struct tnx_mlp_resources {
  *     call that reported TNX_ERR_DEVICE the counters are undefined: zero them on every rank and
  *     restart at 1;
  *   - every rank makes the same sequence of calls with the same m, n_out, tile_split and
- *     signal_tiles (m may change from call to call), on the same GPU model (the closing barrier
- *     counts the CTAs of every rank's grid).
+ *     signal_tiles (m may change from call to call).
  * A tensor-parallel launch has 256 threads per CTA: two warps of every CTA form a crew that
  * exchanges while the other six compute.  tile_split (1, 2, 4 ...; 0 = 16, halved until
  * world * tile_split divides 256) is the number of crews that share one row tile's exchange.

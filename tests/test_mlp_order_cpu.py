@@ -46,7 +46,7 @@ def test_resource_query():
     assert (r.tiles_m, r.band_rows, r.num_bands, r.tmem_columns) == (128, 1024, 32, 512)
     assert r.smem_bytes == 3 * (128 + 128) * 128 * 2 + 2 * 16384 + 512 + 1024
     band = 1024 * 14336 * 2
-    assert r.min_workspace_bytes == 1536 + 2 * band and r.workspace_bytes == r.min_workspace_bytes
+    assert r.min_workspace_bytes == 1792 + 2 * band and r.workspace_bytes == r.min_workspace_bytes
     small = query(300, 512, 1024, 512)
     assert small.num_bands == 1 and small.min_workspace_bytes == small.workspace_bytes
     with pytest.raises(OutOfResources, match="shared memory"):

@@ -40,9 +40,11 @@
 //    measured), and a crew that saturates that path starves the barrier polls and shared-memory
 //    stores of the computing warps next to it.  Hence small crews (two warps: their own latency
 //    throttles them to a fraction of that rate) on ALL SMs, and small pieces, instead of a few
-//    SMs that do nothing else.  The partial outputs are kept in
-//    fp32 (a buffer of their own) and rounded to the output type only after the cross-rank sum,
-//    so the result carries ONE rounding, as on a single GPU.  The partial buffer, Y and the
+//    SMs that do nothing else.  The partial outputs are either kept in fp32 (a buffer of their
+//    own) and rounded to the output type only after the cross-rank sum, so that the result
+//    carries ONE rounding as on a single GPU, or (no such buffer given) rounded to the output
+//    type, stored in Y and summed in place with fp32 accumulation in the switch: half the
+//    NVLink traffic and half the multimem requests for a second rounding.  The partial buffer, Y and the
 //    counters live in symmetric memory mapped into one multicast object; no TMA operation
 //    touches another GPU's memory; the computing warps never wait for a crew.  Cross-rank
 //    counters are never reset: call number `epoch` waits for epoch * world arrivals.
@@ -102,6 +104,7 @@ struct MlpParams {
   int exchange;            // 1: tensor-parallel launch (fp32 partial outputs, crews sum them across ranks)
   int tile_split;          // pieces a row tile's share of rows is cut into (one crew each)
   int* y_done;             // [tiles_m] CTAs that finished STORING a D unit of the row tile
+  int* crews_done;         // [1] exchange crews of this GPU that have written all their pieces
   void* y_mc;              // multicast address of Y (the same buffer on every rank)
   long long ldy;           // row pitch of Y in elements
   const float* part_mc;    // multicast address of the fp32 partial outputs ([rows, n_out], pitch n_out)
@@ -246,6 +249,22 @@ __device__ __forceinline__ float4 multimem_sum(const float* mc_addr) {
                : "memory");
   return v;
 }
+// Eight 16-bit values summed over all GPUs, accumulated in fp32 by the switch, rounded once.
+template <bool BF16>
+__device__ __forceinline__ uint4 multimem_sum16(const void* mc_addr) {
+  uint4 v;
+  if (BF16)
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(mc_addr)
+                 : "memory");
+  else
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(mc_addr)
+                 : "memory");
+  return v;
+}
 __device__ __forceinline__ void multimem_store(void* mc_addr, const uint4& v) {
   asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc_addr), "r"(v.x),
                "r"(v.y), "r"(v.z), "r"(v.w)
@@ -368,6 +387,24 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
         const int rows = min(rows_per_piece, p.m - row_lo);
         const int total = rows > 0 ? rows * vec_per_row : 0;
         constexpr int kVec = 8;  // output vectors (eight values each) per thread and round
+        if (p.part_mc == nullptr) {
+          // partial outputs in the output type, summed in place in Y
+          for (int base = crew_tid; base < total; base += crew_n * kVec) {
+            uint4 v[kVec];
+            size_t off[kVec];
+#pragma unroll
+            for (int i = 0; i < kVec; ++i) {
+              const int idx = base + i * crew_n;
+              const int safe = idx < total ? idx : base;
+              const int r = safe / vec_per_row;
+              off[i] = (static_cast<size_t>(row_lo + r) * p.ldy + static_cast<size_t>(safe - r * vec_per_row) * 8) * 2;
+              v[i] = multimem_sum16<BF16>(y_mc + off[i]);
+            }
+#pragma unroll
+            for (int i = 0; i < kVec; ++i)
+              if (base + i * crew_n < total) multimem_store(y_mc + off[i], v[i]);
+          }
+        } else
         for (int base = crew_tid; base < total; base += crew_n * kVec) {
           float4 lo[kVec], hi[kVec];
 #pragma unroll
@@ -410,8 +447,13 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
     ptx::named_barrier_sync(kCrewBarrier, crew_n);
     if (crew_tid == 0) {
       if (ok) {
-        multimem_signal(p.sig_mc);
-        ok = wait_counter_sys(p.sig_local, p.epoch * static_cast<unsigned>(p.world) * gridDim.x, abort_flag,
+        // The last crew of this GPU to get here tells every rank once (so the target does not
+        // depend on how many CTAs a call launched).
+        if (atomicAdd(p.crews_done, 1) == static_cast<int>(gridDim.x) - 1) {
+          __threadfence_system();
+          multimem_signal(p.sig_mc);
+        }
+        ok = wait_counter_sys(p.sig_local, p.epoch * static_cast<unsigned>(p.world), abort_flag,
                               p.status, p.timeout_ns);
         fence_proxy_alias();  // Y was written through the multicast alias; it is read through the unicast one
       }
@@ -544,7 +586,7 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
       const Unit un = decode_unit(p, u);
       const int row0 = ((un.down ? un.t : ring_tile(p, un.t)) * 2 + static_cast<int>(cta_rank)) * kRows;
       // (when ranks exchange, a D unit stores its fp32 accumulator as it is, with plain stores)
-      const bool raw = un.down && p.exchange != 0;
+      const bool raw = un.down && p.exchange != 0 && p.part_local != nullptr;
       const CUtensorMap* map_c = un.down ? &tmap_y : &tmap_h_st;
       const int acc_per_chunk = un.down ? 64 : 128;  // accumulator columns per 128-byte output row
       const int out_col0 = un.j * (un.down ? kTileN : kTileN / 2);
@@ -664,13 +706,19 @@ swiglu_mlp_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_const
         __threadfence_system();
         ptx::named_barrier_sync(kEpiBarrier, kEpiThreads);
         if (epi_tid == 0) atomicAdd(p.y_done + un.t, 1);
-      } else if (!un.down && epi_tid == 0) {
-        // Publish this CTA's part of H: the stores must have landed (not merely have been read
-        // out of shared memory) before the counter moves.
+      } else if ((!un.down || p.exchange != 0) && epi_tid == 0) {
+        // Publish this CTA's part of H (or, when ranks exchange 16-bit partial outputs in place,
+        // of Y): the TMA stores must have landed (not merely have been read out of shared memory)
+        // before the counter moves; Y is read by other GPUs, hence the system-wide fence.
         ptx::tma_store_wait_all<0>();
         fence_proxy_async_global();
-        __threadfence();
-        atomicAdd(p.g_done + un.t, 1);
+        if (un.down) {
+          fence_proxy_alias();
+          __threadfence_system();
+        } else {
+          __threadfence();
+        }
+        atomicAdd((un.down ? p.y_done : p.g_done) + un.t, 1);
       }
     }
     if (epi_tid == 0) ptx::tma_store_wait_all<0>();
@@ -775,7 +823,7 @@ int plan_mlp(const tnx_mlp_problem* p, const tnx_config* config, MlpPlan* plan, 
   plan->num_bands = cdiv(plan->tiles_m, plan->band);
   plan->last_rows = plan->tiles_m - (plan->num_bands - 1) * plan->band;
   plan->ring_bands_min = plan->num_bands < 2 ? plan->num_bands : 2;
-  plan->counter_bytes = align256(3LL * plan->tiles_m * 4);
+  plan->counter_bytes = align256((3LL * plan->tiles_m + 1) * 4);
   plan->band_bytes = static_cast<int64_t>(plan->band) * 2 * kRows * p->d_ff * 2;
 
   out->smem_bytes = static_cast<int32_t>(smem > 0x7fffffff ? 0x7fffffff : smem);
@@ -874,12 +922,12 @@ int tnx_swiglu_mlp(const tnx_mlp_problem* problem, const tnx_config* config, con
       return TNX_ERR_INVALID;
     }
     if (ex.y_multicast == nullptr || ex.signal_multicast == nullptr || ex.signal_local == nullptr ||
-        ex.partial_local == nullptr || ex.partial_multicast == nullptr ||
+        (ex.partial_local == nullptr) != (ex.partial_multicast == nullptr) ||
         ((reinterpret_cast<uintptr_t>(ex.y_multicast) | reinterpret_cast<uintptr_t>(ex.partial_local) |
           reinterpret_cast<uintptr_t>(ex.partial_multicast)) & 15u) ||
         (reinterpret_cast<uintptr_t>(ex.signal_multicast) & 3u)) {
-      set_error("exchange: y_multicast, partial_local, partial_multicast (16-byte aligned), signal_multicast "
-                "and signal_local must be set");
+      set_error("exchange: y_multicast (16-byte aligned), signal_multicast and signal_local must be set; "
+                "partial_local and partial_multicast (16-byte aligned) both or neither");
       return TNX_ERR_INVALID;
     }
   }
@@ -946,6 +994,7 @@ int tnx_swiglu_mlp(const tnx_mlp_problem* problem, const tnx_config* config, con
   kp.timeout_ns = bounded_wait_limit_ns();
   kp.world = 1;
   kp.y_done = counters + 2 * plan.tiles_m;
+  kp.crews_done = counters + 3 * plan.tiles_m;
   if (tile_split > 0) {
     kp.exchange = 1;
     kp.tile_split = tile_split;
