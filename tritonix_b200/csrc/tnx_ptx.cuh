@@ -353,6 +353,14 @@ __device__ __forceinline__ float4 ld_shared_cluster_v4(uint32_t cluster_addr) {
                : "memory");
   return v;
 }
+// 16-byte store into the shared memory of any CTA of the cluster (addresses from mapa()); its
+// bytes count towards the transaction count of that CTA's mbarrier when they have landed.
+__device__ __forceinline__ void st_async_v4(uint32_t cluster_addr, uint32_t a, uint32_t b, uint32_t c,
+                                            uint32_t d, uint32_t cluster_bar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
+               ::"r"(cluster_addr), "r"(a), "r"(b), "r"(c), "r"(d), "r"(cluster_bar)
+               : "memory");
+}
 __device__ __forceinline__ void fence_acq_rel_cluster() {
   asm volatile("fence.acq_rel.cluster;" ::: "memory");
 }

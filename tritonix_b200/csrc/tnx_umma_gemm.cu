@@ -22,6 +22,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <stdlib.h>
 #include <string.h>
 
 #include <algorithm>
@@ -121,8 +122,8 @@ struct Ctrl {
   uint64_t empty[kMaxStages];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
-  uint64_t xchg_full;   // cluster split-K: every slice's partial is in its shared memory
-  uint64_t xchg_free;   // cluster split-K: every slice has finished reading the partials
+  uint64_t xchg_full;   // cluster split-K: every slice's share of this CTA's rows has landed here
+  uint64_t xchg_free;   // cluster split-K: every slice has summed what was pushed to it
   uint32_t tmem_base;
   int abort;
   int is_last;
@@ -178,6 +179,14 @@ __device__ __forceinline__ float unpack1(uint16_t bits) {
   return __half2float(__ushort_as_half(bits));
 }
 
+__device__ __forceinline__ float4 ld_shared_v4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(addr)
+               : "memory");
+  return v;
+}
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c,
                                              uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c),
@@ -274,7 +283,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       ptx::mbar_init(ptx::smem_u32(&ctrl->tmem_full[a]), 1);
       ptx::mbar_init(ptx::smem_u32(&ctrl->tmem_empty[a]), 4 * CTA_GROUP);  // one arrive per epilogue warp
     }
-    ptx::mbar_init(ptx::smem_u32(&ctrl->xchg_full), xchg ? cluster_size : 1);
+    ptx::mbar_init(ptx::smem_u32(&ctrl->xchg_full), 1);  // completes by the bytes pushed into this CTA
     ptx::mbar_init(ptx::smem_u32(&ctrl->xchg_free), xchg ? cluster_size : 1);
     ctrl->abort = 0;
     ctrl->is_last = 0;
@@ -294,6 +303,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = ctrl->tmem_base;
   if (threadIdx.x == 0) TNX_TRACE(0);
+  // Launched with programmatic stream serialization, everything above (no global memory touched
+  // yet: the tensor maps are kernel parameters) ran while the previous kernel of the stream was
+  // still finishing; from here on its writes are needed, or ours might overtake its reads.  The
+  // kernel after this one may start its own set-up as soon as SMs fall free.  Without the launch
+  // attribute both instructions do nothing.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   // ------------------------------------------------------------------ roles
   if (warp == 0) {
@@ -651,19 +667,31 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             break;
           }
         }
-        const uint32_t my_row = smem_out + static_cast<uint32_t>(row_in_tile) * (TILE_N * 4);
+        // Rows of the tile are dealt out to the slices in blocks of R: slice d sums (and stores)
+        // rows [d*R, (d+1)*R).  Every slice PUSHES its partial rows into their owner's shared
+        // memory (slot [source slice][row in block][TILE_N floats], 16-byte chunks XOR-swizzled
+        // by row) with st.async, whose bytes complete the owner's mbarrier: no round trip, and
+        // the owner then sums from its own shared memory.
+        const int R = (p.a_rows + static_cast<int>(S) - 1) / static_cast<int>(S);
+        const int my_rows = max(0, min(R, p.a_rows - static_cast<int>(cluster_rank) * R));
+        if (epi_tid == 0)
+          ptx::mbar_arrive_expect_tx(full_bar, static_cast<uint32_t>(my_rows) * S * (TILE_N * 4));
         if (quarter * 32 < p.a_rows) {  // warp-uniform: this warp's lanes hold loaded rows
+          const uint32_t owner = static_cast<uint32_t>(row_in_tile / R);
+          const uint32_t row_local = static_cast<uint32_t>(row_in_tile) - owner * R;
+          const uint32_t dst_row = ptx::mapa(
+              smem_out + (cluster_rank * static_cast<uint32_t>(R) + row_local) * (TILE_N * 4), owner);
+          const uint32_t dst_bar = ptx::mapa(full_bar, owner);
           for (int c = 0; c < TILE_N / 32; ++c) {
-            if (acc_col0 + c * 32 >= p.n) break;
             uint32_t r[32];
             ptx::tmem_ld_32x32(t_acc + c * 32, r);  // whole warp, converged
             ptx::tmem_ld_wait();
             if (row_in_tile < p.a_rows) {
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
-                const uint32_t chunk =
-                    (static_cast<uint32_t>(c * 8 + j) ^ static_cast<uint32_t>(row_in_tile)) & kChunkMask;
-                st_shared_v4(my_row + chunk * 16, r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                const uint32_t chunk = (static_cast<uint32_t>(c * 8 + j) ^ row_local) & kChunkMask;
+                ptx::st_async_v4(dst_row + chunk * 16, r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3],
+                                 dst_bar);
               }
             }
             __syncwarp();
@@ -676,32 +704,26 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           acc = 0;
           acc_phase ^= 1u;
         }
-        ptx::fence_acq_rel_cluster();
-        ptx::named_barrier_sync(kEpiBarrier, kEpiThreads);
-        if (epi_tid == 0)
-          for (uint32_t r = 0; r < S; ++r) ptx::mbar_arrive_cluster(ptx::mapa(full_bar, r));
         const bool got_full = ptx::mbar_wait<true>(full_bar, xchg_round & 1u, abort_flag, p.timeout_ns);
         if (!ptx::named_barrier_all(kEpiBarrier, kEpiThreads, got_full)) {
           ok = false;
           break;
         }
         if (epi_tid == 0 && u == cluster_id) TNX_TRACE(5);
-        const int rows_valid = min(p.a_rows, p.m - row0);
+        const int first_row = static_cast<int>(cluster_rank) * R;
+        const int rows_valid = max(0, min(my_rows, p.m - row0 - first_row));
         const int cols_valid = min(TILE_N, p.n - acc_col0);
         const int vec_per_row = (cols_valid + 3) >> 2;
         const int total_vec = rows_valid * vec_per_row;
-        const int share = (total_vec + static_cast<int>(S) - 1) / static_cast<int>(S);
-        const int lo_vec = static_cast<int>(cluster_rank) * share;
-        const int hi_vec = min(total_vec, lo_vec + share);
         constexpr int kInFlight = 4;
-        for (int base = lo_vec + epi_tid; base < hi_vec; base += kEpiThreads * kInFlight) {
+        for (int base = epi_tid; base < total_vec; base += kEpiThreads * kInFlight) {
           float4 sum[kInFlight];
           int rr[kInFlight], cc[kInFlight];
           uint32_t off[kInFlight];
 #pragma unroll
           for (int u2 = 0; u2 < kInFlight; ++u2) {
             const int idx = base + u2 * kEpiThreads;
-            const int safe = idx < hi_vec ? idx : base;
+            const int safe = idx < total_vec ? idx : base;
             rr[u2] = safe / vec_per_row;
             const int c4 = safe - rr[u2] * vec_per_row;
             cc[u2] = c4 << 2;
@@ -709,31 +731,23 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                       (((static_cast<uint32_t>(c4) ^ static_cast<uint32_t>(rr[u2])) & kChunkMask) << 4);
             sum[u2] = make_float4(0.f, 0.f, 0.f, 0.f);
           }
-          for (uint32_t s0 = 0; s0 < S; s0 += 4) {
-            float4 v[4][kInFlight];
+          for (uint32_t src = 0; src < S; ++src) {  // slice order: bit-reproducible
 #pragma unroll
-            for (int ds = 0; ds < 4; ++ds)
-#pragma unroll
-              for (int u2 = 0; u2 < kInFlight; ++u2)
-                v[ds][u2] = s0 + ds < S ? ptx::ld_shared_cluster_v4(ptx::mapa(off[u2], s0 + ds))
-                                        : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-            for (int ds = 0; ds < 4; ++ds)
-#pragma unroll
-              for (int u2 = 0; u2 < kInFlight; ++u2) {
-                sum[u2].x += v[ds][u2].x;
-                sum[u2].y += v[ds][u2].y;
-                sum[u2].z += v[ds][u2].z;
-                sum[u2].w += v[ds][u2].w;
-              }
+            for (int u2 = 0; u2 < kInFlight; ++u2) {
+              const float4 v = ld_shared_v4(off[u2] + src * static_cast<uint32_t>(R) * (TILE_N * 4));
+              sum[u2].x += v.x;
+              sum[u2].y += v.y;
+              sum[u2].z += v.z;
+              sum[u2].w += v.w;
+            }
           }
 #pragma unroll
           for (int u2 = 0; u2 < kInFlight; ++u2) {
-            if (base + u2 * kEpiThreads >= hi_vec) continue;
-            store_fixup<GLU, BF16>(p, row0 + rr[u2], acc_col0 + cc[u2], cols_valid - cc[u2], sum[u2]);
+            if (base + u2 * kEpiThreads >= total_vec) continue;
+            store_fixup<GLU, BF16>(p, row0 + first_row + rr[u2], acc_col0 + cc[u2], cols_valid - cc[u2], sum[u2]);
           }
         }
-        // Tell every slice that this one no longer reads their shared memory.
+        // Tell every slice that this one has read what they pushed: they may push the next tile.
         ptx::named_barrier_sync(kEpiBarrier, kEpiThreads);
         if (epi_tid == 0)
           for (uint32_t r = 0; r < S; ++r) ptx::mbar_arrive_cluster(ptx::mapa(free_bar, r));
@@ -1114,6 +1128,16 @@ cudaError_t allow_full_smem(KernelFn fn) {
   return e;
 }
 
+// Whether launches ask for programmatic stream serialization (the kernel's set-up overlaps the
+// tail of the kernel before it).  On unless TRITONIX_B200_OVERLAP_SETUP=0.
+bool overlap_setup() {
+  static const bool on = [] {
+    const char* v = getenv("TRITONIX_B200_OVERLAP_SETUP");
+    return !(v != nullptr && v[0] == '0');
+  }();
+  return on;
+}
+
 // cudaOccupancyMaxActiveClusters, remembered per (kernel, device, shared memory, cluster size).
 cudaError_t max_active_clusters(KernelFn fn, const cudaLaunchConfig_t& lc, int* out) {
   struct Entry {
@@ -1191,11 +1215,13 @@ unsigned long long bounded_wait_limit_ns() { return wait_limit_ns(); }
 // Split-K slices can exchange partials through distributed shared memory when they fit one
 // portable cluster (2, 4 or 8 CTAs, one SM each) and a slice's fp32 partial fits the epilogue
 // staging area.  Then no workspace is needed at all.
+// Rows of staging a CTA needs for the exchange: a block of ceil(rows / split) rows from each slice.
+static int exchange_rows(int rows, int split) { return (rows + split - 1) / split * split; }
 static bool use_cluster_split(const tnx_problem& p, const tnx_config& cfg, int split) {
   if (cfg.cta_group != 1 || (split != 2 && split != 4 && split != 8)) return false;
   if (getenv("TNX_NO_CLUSTER_SPLITK") != nullptr) return false;  // read every time: tests flip it
   const int rows = a_box_rows(p, cfg);
-  const long long partial = static_cast<long long>(rows) * cfg.tile_n * 4;
+  const long long partial = static_cast<long long>(exchange_rows(rows, split)) * cfg.tile_n * 4;
   // Fits the regular staging area, or (skinny M only) a staging area grown to 64 KiB.
   return partial <= 2 * kStagingBytes || (rows <= 64 && partial <= 4 * kStagingBytes);
 }
@@ -1203,7 +1229,7 @@ static bool use_cluster_split(const tnx_problem& p, const tnx_config& cfg, int s
 // Bytes of shared memory set aside for the epilogue.
 static int staging_bytes_for(const tnx_problem& p, const tnx_config& cfg, int split) {
   if (split > 1 && use_cluster_split(p, cfg, split)) {
-    const int partial = a_box_rows(p, cfg) * cfg.tile_n * 4;
+    const int partial = exchange_rows(a_box_rows(p, cfg), split) * cfg.tile_n * 4;
     if (partial > 2 * kStagingBytes) return (partial + 1023) / 1024 * 1024;
   }
   return 2 * kStagingBytes;
@@ -1416,13 +1442,17 @@ int umma_launch(const tnx_problem& p, const tnx_config& cfg, const tnx_resources
   lc.blockDim = dim3(kThreads, 1, 1);
   lc.dynamicSmemBytes = res.smem_bytes;
   lc.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = xchg ? res.split_k : cfg.cta_group;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  // The kernel's set-up (barriers, TMEM, cluster rendezvous) may overlap the tail of the kernel
+  // before it in the stream; it waits for that kernel to complete before touching global memory.
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   lc.attrs = attr;
-  lc.numAttrs = 1;
+  lc.numAttrs = overlap_setup() ? 2 : 1;
   if (xchg) {
     // Clusters of split_k CTAs do not always tile the GPU evenly: ask how many fit at once.
     int fit = 0;
