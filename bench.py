@@ -354,6 +354,40 @@ def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1, mode="auto", tile_split=1
         else:
             state["y"] = tnx.swiglu_mlp(x, w12, wd, fused=True, fused_cfg=fused_cfg)
 
+    chosen_by = None
+    if world > 1 and fused is not None and mode == "auto":
+        # Before the in-kernel exchange is given the headline: one trial step whose result must
+        # agree with the NCCL implementation's on every rank, then a short calibration of both.
+        import torch.distributed as dist
+        ok = torch.ones(1, device=dev)
+        failure = None
+        try:
+            y_one = fused(x).clone()
+            torch.cuda.synchronize(dev)
+            tnx.check_status(dev)
+        except Exception as exc:
+            failure = exc
+        y_two = mlp(x)  # (every rank, whatever happened above: it holds a collective)
+        torch.cuda.synchronize(dev)
+        if failure is None:
+            diff = (y_one.float() - y_two.float()).abs().max().item() / max(y_two.float().abs().max().item(), 1e-30)
+            if not diff <= 1.5e-2:
+                failure = RuntimeError("trial step differs from the NCCL implementation by %.3g" % diff)
+        if failure is not None:
+            ok.zero_()
+            fused_note = f"trial step failed on rank {rank}: {type(failure).__name__}: {failure}"[:240]
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if ok.item() == 0:
+            fused = None
+            fused_note = fused_note or "trial step failed on another rank"
+        else:
+            t_cal = {}
+            for name, fn in (("one_launch", lambda: fused(x)), ("two_launch", lambda: mlp(x))):
+                t = torch.tensor([time_steps(fn, 5, 2, dist.barrier)], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                t_cal[name] = t.item() / 5
+            mode = min(t_cal, key=t_cal.get)
+            chosen_by = "calibration of 5 steps each: " + ", ".join("%s %.3f ms" % kv for kv in sorted(t_cal.items()))
     one_launch_ok = world == 1 or fused is not None
     if mode == "auto":  # one GPU: two launches measure 5-9 % faster from the same rest
         mode = "one_launch" if (world > 1 and fused is not None) else "two_launch"
@@ -408,7 +442,8 @@ def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1, mode="auto", tile_split=1
                     % (nchunks, comm_sms)) if world > 1 else "none (one GPU)"
     work = dict(flops=flops, bytes=None, units=float(m), launches=launches, h2d=x_host.numel() * 2,
                 d2h=y_host.numel() * 2, copies=1, cfg=cfg, chunks=nchunks, comm_sms=comm_sms,
-                parity=parity, mode=mode, exchange=exchange, other=other, fused_note=fused_note)
+                parity=parity, mode=mode, exchange=exchange, other=other, fused_note=fused_note,
+                chosen_by=chosen_by)
     return step, e2e_step, work
 
 
@@ -568,6 +603,8 @@ def measure(workload, args, rank, local_rank, world, dev, D, peaks):
                    "kernel_config_source": CONFIG_SOURCE,
                    **({"implementation": work["mode"], "exchange": work["exchange"]}
                       if workload == "mlp" else {}),
+                   **({"implementation_chosen_by": work["chosen_by"]}
+                      if workload == "mlp" and work.get("chosen_by") else {}),
                    **({"tokens": args.mlp_tokens} if workload == "mlp" and args.mlp_tokens else {}),
                    **({"allreduce_chunks": work["chunks"], "comm_sms": work["comm_sms"]}
                       if workload == "mlp" and world > 1 and work["mode"] == "two_launch" else {}),
