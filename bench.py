@@ -76,6 +76,9 @@ CONFIG_SOURCE = "fixed in bench.py (the configurations that measured best on a B
 NCU_TRAFFIC_BYTES = {"gemm": 1_389_138_048, "gemm_strong": None, "splitk": 125_974_528,
                      "glu": 885_355_520, "mlp": None, "conv": 26_989_568}
 
+# swiglu_mlp_kernel at 8192 tokens (d_model 4096, d_ff 14336): dram read + written per launch
+MLP_ONE_LAUNCH_TRAFFIC_8192 = 2_526_534_000 + 299_845_376
+
 # The reference's Triton kernels are timed with configurations from its own search space
 # (tritonix/ops/matmul.py:33-38; the hand-picked list of tritonix/utils/triton.py:34-53 tops
 # out at 128 x 128 x 64 tiles); the best of these is reported.
@@ -588,7 +591,17 @@ def measure(workload, args, rank, local_rank, world, dev, D, peaks):
                 "frac_of_nominal_2250": achieved / 2250.0}
         if workload == "mlp":
             roof["note"] = ("whole step (fused gate/up GEMM + down GEMM"
-                            + (" + all-reduce" if world > 1 else "") + ") against the tensor peak")
+                            + (" + cross-rank sum" if world > 1 else "") + ") against the tensor peak")
+            if world == 1:
+                # captures exist for a quarter of the tokens (8192); traffic grows with the tokens
+                scale_m = work["units"] / 8192.0
+                if work["mode"] == "one_launch":
+                    roof["traffic"] = int(MLP_ONE_LAUNCH_TRAFFIC_8192 * scale_m)
+                    roof["traffic_note"] = "swiglu_mlp_kernel captured at 8192 tokens, scaled by the tokens"
+                else:
+                    roof["traffic"] = int(NCU_TRAFFIC_BYTES["glu"] * scale_m)
+                    roof["traffic_note"] = ("dominant kernel (fused gate/up GEMM) captured at 8192 tokens "
+                                            "(the glu workload), scaled by the tokens")
         if work.get("kernel_step") is not None:
             roof["kernel_ms"] = ms_kernel
             roof["note"] = ("dominant kernel timed alone on channels_last tensors, launches replayed "
