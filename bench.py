@@ -66,7 +66,10 @@ WORKLOADS = {
                  name="conv2d_fwd_bf16_nchw_64x256x28x28_w256x256x3x3_s1_p1_per_gpu_batch_sharded"),
 }
 
-GEMM_CFG = {"kernel": "tcgen05", "tile_n": 256, "tile_k": 128, "stages": 3, "cta_group": 2, "group_m": 16}
+# tile_n 512 = two 256-column tiles per CTA pair fed by one stream of A: fewer operand bytes per
+# flop, at the price of an epilogue that is only partly hidden; it pays for long K
+GEMM_CFG = {"kernel": "tcgen05", "tile_n": 512, "tile_k": 64, "stages": 4, "cta_group": 2, "group_m": 8}
+GEMM_CFG_SHORT_K = {"kernel": "tcgen05", "tile_n": 256, "tile_k": 128, "stages": 3, "cta_group": 2, "group_m": 16}
 SPLITK_CFG = {"kernel": "tcgen05", "tile_n": 128, "tile_k": 128, "stages": 4, "cta_group": 1, "split_k": 4}
 GLU_CFG = {"kernel": "tcgen05", "tile_n": 256, "tile_k": 128, "stages": 3, "cta_group": 2, "group_m": 16}
 CONFIG_SOURCE = "fixed in bench.py (the configurations that measured best on a B200)"
@@ -191,6 +194,16 @@ def randn(shape, dtype, device, seed, scale):
     return (torch.randn(shape, device=device, generator=g, dtype=torch.float32) * scale).to(dtype)
 
 
+def gemm_cfg_for_rows(m, n):
+    """Double tiles unless their last wave over the 74 CTA pairs is much emptier than that of
+    single tiles (4096 rows: 256 double tiles = 3.46 waves against 512 = 6.92)."""
+    def wave_fill(tiles):
+        return tiles / (-(-tiles // 74) * 74)
+    rows = -(-m // 256)
+    double, single = rows * -(-n // 512), rows * -(-n // 256)
+    return GEMM_CFG if wave_fill(double) >= wave_fill(single) - 0.05 else GEMM_CFG_SHORT_K
+
+
 def setup_contraction(workload, rank, world, dev):
     """gemm / gemm_strong / splitk / glu: one kernel launch per step."""
     from tritonix_b200 import _cabi
@@ -202,7 +215,8 @@ def setup_contraction(workload, rank, world, dev):
     glu = workload == "glu"
     epi = _cabi.EPI_GLU_SILU if glu else _cabi.EPI_NONE
     n_out = n // 2 if epi else n
-    cfg = {"gemm": GEMM_CFG, "gemm_strong": GEMM_CFG, "splitk": SPLITK_CFG, "glu": GLU_CFG}[workload]
+    cfg = {"gemm": GEMM_CFG, "gemm_strong": gemm_cfg_for_rows(m, n), "splitk": SPLITK_CFG,
+           "glu": GLU_CFG}[workload]
     algo_bytes = (m * k + k * n + m * n_out) * 2
     # operands smaller than L2 are rotated through enough copies to defeat it
     copies = 1 if algo_bytes > 2 * L2_BYTES else -(-3 * L2_BYTES // algo_bytes)
@@ -334,9 +348,10 @@ def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1, mode="auto", tile_split=1
     w12 = torch.stack((wg, wu), 2).reshape(d, 2 * fr).contiguous()
     del wg, wu
     x = randn((m, d), dt, dev, 5, 1.0)
+    down_cfg = GEMM_CFG if fr >= 6144 else GEMM_CFG_SHORT_K   # K of the down projection = this rank's hidden units
     mlp = TensorParallelSwiGLU(
         w12, wd, chunks=chunks if (isinstance(chunks, list) or chunks > 0) else (1 if world == 1 else 4),
-        comm_sms=comm_sms, gate_up_cfg=GLU_CFG, down_cfg=GEMM_CFG)
+        comm_sms=comm_sms, gate_up_cfg=GLU_CFG, down_cfg=down_cfg)
     state = {}
     fused_cfg = {"tile_k": 128, "stages": 3, "group_m": band}
     fused = None
@@ -407,7 +422,7 @@ def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1, mode="auto", tile_split=1
     y_host = torch.empty((m, d), dtype=dt).pin_memory()
     pipe = tnx.HostRowPipeline(dev, d, d, dt, rows_per_chunk=4096)
     chunk_mlp = TensorParallelSwiGLU(w12, wd, chunks=1, comm_sms=comm_sms, gate_up_cfg=GLU_CFG,
-                                     down_cfg=GEMM_CFG)
+                                     down_cfg=down_cfg)
 
     def e2e_step():
         # rows of x stream in, rows of y stream out, 4096 rows (one all-reduce) at a time
@@ -439,7 +454,7 @@ def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1, mode="auto", tile_split=1
                     % ("fp32" if fp32_partials else "bf16", tile_split)) \
             if world > 1 else "none (one GPU)"
     else:
-        cfg = {"gate_up": GLU_CFG, "down": GEMM_CFG}
+        cfg = {"gate_up": GLU_CFG, "down": down_cfg}
         launches = 2 * nchunks
         exchange = ("NCCL all-reduce per row chunk on a side stream (%d chunks, %d SMs left to it)"
                     % (nchunks, comm_sms)) if world > 1 else "none (one GPU)"

@@ -82,7 +82,9 @@ typedef struct tnx_problem {
  */
 typedef struct tnx_config {
   int32_t tile_m;     /* rows of C per CTA (128) or per CTA pair (256 when cta_group == 2)        */
-  int32_t tile_n;     /* columns of B per tile: 64, 128 or 256                                    */
+  int32_t tile_n;     /* columns of B per tile: 64, 128 or 256; 512 = a CTA pair computes two
+                         column-adjacent 256-column tiles from one stream of A (needs
+                         cta_group 2, split_k 1, acc_stages 2, a computed tile order, row-major B) */
   int32_t tile_k;     /* K elements per pipeline stage: 64 or 128                                 */
   int32_t stages;     /* depth of the TMA -> shared-memory ring, >= 2                             */
   int32_t acc_stages; /* TMEM accumulator buffers: 1 or 2 (2 overlaps epilogue and main loop)     */

@@ -134,7 +134,7 @@ def test_shipped_kernel_spaces_are_consistent():
         # the reference's memory axes plus the TMEM accumulator count
         assert set(names) == {"block_m", "block_n", "block_k", "num_stages", "acc_stages"}
         assert values[names.index("block_m")][0] == max(tk.space["block_m"].values())
-    assert len(t.matmul_kernel.configs()) == 2 * 3 * 2 * 3 * 4 * 7 * 2
+    assert len(t.matmul_kernel.configs()) == 2 * 4 * 2 * 3 * 4 * 7 * 2
 
 
 def test_seeds_steady_state_and_finalists():

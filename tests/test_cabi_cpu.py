@@ -69,6 +69,24 @@ def test_resource_query_budgets():
             q(4096, 4096, 4096, {"tile_n": 256, "cta_group": 1, "stages": 5, "tile_k": 64, axis: bigger})
 
 
+def test_double_tile_resources():
+    """tile_n = 512 = two 256-column tiles per CTA pair: both TMEM buffers are accumulators and a
+    ring slot holds the B columns of both tiles."""
+    r = q(8192, 8192, 8192, {"tile_n": 512, "cta_group": 2, "tile_k": 64, "stages": 4})
+    assert r.kernel == _cabi.KERNEL_TCGEN05 and r.tmem_columns == 512
+    assert r.smem_bytes == 4 * (128 + 256) * 64 * 2 + 2 * 16384 + 512 + 1024 <= 232448
+    assert (r.tiles_m, r.tiles_n, r.grid) == (32, 16, 148)
+    assert q(512, 768, 512, {"tile_n": 512, "cta_group": 2}).tiles_n == 2   # the last one is half empty
+    with pytest.raises(OutOfResources, match="shared memory"):
+        q(8192, 8192, 8192, {"tile_n": 512, "cta_group": 2, "tile_k": 64, "stages": 5})
+    for bad in ({"cta_group": 1}, {"cta_group": 2, "split_k": 2}, {"cta_group": 2, "acc_stages": 1},
+                {"cta_group": 2, "tile_order": "hilbert"}):
+        with pytest.raises(ValueError, match="tile_n=512"):
+            q(2048, 2048, 2048, {"tile_n": 512, **bad})
+    with pytest.raises(ValueError, match="tile_n=512"):   # B stored N x K
+        q(2048, 2048, 2048, {"tile_n": 512, "cta_group": 2}, strides=(2048, 1, 1, 2048, 2048, 1))
+
+
 def test_invalid_and_unbuilt_configs_are_value_errors():
     with pytest.raises(ValueError, match="not built"):
         q(512, 512, 512, {"tile_k": 32})

@@ -50,6 +50,33 @@ def test_tcgen05_against_oracle(m, n, k, dtype, cfg):
     assert_close(out, O.matmul_oracle(a, b), dtype)
 
 
+WIDE = {"tile_n": 512, "cta_group": 2, "tile_k": 64, "stages": 4}
+
+
+@pytest.mark.parametrize("m,n,k,dtype,cfg", [
+    (512, 1024, 512, bf16, WIDE),
+    (256, 512, 64, f16, WIDE),                                    # a single K block
+    (256, 512, 192, bf16, WIDE),                                  # fewer K blocks than ring slots
+    (1000, 1296, 1000, bf16, WIDE),                               # ragged; six 256-column tiles
+    (384, 768, 2048, f16, WIDE),                                  # the last double tile has no right half
+    (300, 264, 520, bf16, WIDE),                                  # one double tile, right half 8 columns
+    (2048, 2048, 2048, bf16, {**WIDE, "stages": 3, "group_m": 4}),
+    (1024, 1024, 4096, bf16, {**WIDE, "tile_order": "serpentine", "group_m": 2}),
+    (4096, 4096, 1024, bf16, {**WIDE, "max_ctas": 24}),           # many double tiles per CTA pair
+    (1024, 2048, 512, f16, {**WIDE, "tile_k": 128, "stages": 2}),
+])
+def test_double_tiles_against_oracle_and_single_tiles(m, n, k, dtype, cfg):
+    """tile_n = 512: a CTA pair computes two column-adjacent 256-column tiles from one stream of
+    A.  The K order of every output is that of the 256-column configuration, so the two must
+    agree bit for bit."""
+    a, b = seeded(m, k, n, dtype, seed=m + n + k)
+    out, res = run_gemm(a, b, {**T, **cfg})
+    assert res.kernel == _cabi.KERNEL_TCGEN05 and res.tmem_columns == 512
+    assert_close(out, O.matmul_oracle(a, b), dtype)
+    single, _ = run_gemm(a, b, {**T, "tile_n": 256, "cta_group": 2, "tile_k": cfg["tile_k"]})
+    assert torch.equal(out, single)
+
+
 @pytest.mark.parametrize("m,n,k,dtype", [(100, 70, 90, f16), (100, 70, 90, bf16), (96, 80, 72, f32),
                                          (33, 1, 17, f32), (5, 3, 0, f16), (257, 129, 65, f32)])
 def test_strided_kernel_against_oracle(m, n, k, dtype):

@@ -69,6 +69,8 @@ struct UmmaParams {
   int a_rows;           // rows of A that TMA brings in per stage (128, or fewer for a skinny M)
   int stages;
   int acc_stages;
+  int wide;             // 1: a CTA pair works on two column-adjacent 256-column tiles at once (one
+                        // A stage feeds both accumulators; tiles_n counts such double tiles)
   int group_m;
   int tile_order;
   int epilogue;
@@ -245,7 +247,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int a_stage_bytes = p.a_rows * TILE_K * 2;
   const int a_atom_bytes = p.a_rows * kAtomBytes;  // one 64-element K slab of the A stage
   const bool halo = CTA_GROUP == 1 && p.conv == 3;
-  const int b_stage_bytes = halo ? p.cv_taps * LOAD_N * kAtomBytes : LOAD_N * TILE_K * 2;
+  constexpr int kBHalfBytes = LOAD_N * TILE_K * 2;  // this CTA's B columns of one tile, one stage
+  const int b_stage_bytes = halo ? p.cv_taps * LOAD_N * kAtomBytes : (p.wide ? 2 : 1) * kBHalfBytes;
   const uint32_t smem_a = base_addr;
   const uint32_t smem_b = smem_a + p.stages * a_stage_bytes;
   // (halo convolution: the weights are loaded once per CTA and stay put: one B buffer, not a ring)
@@ -329,7 +332,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         tile_coords(p, t, tm, tn);
         const int bt_img = p.batched ? tm / p.bt_tiles_m : 0;  // which matrix of a batch
         const int row0 = ((tm - bt_img * p.bt_tiles_m) * CTA_GROUP + static_cast<int>(cta_rank)) * kRowsPerCta;
-        const int col0 = tn * TILE_N + static_cast<int>(cta_rank) * LOAD_N;
+        const int col0 = tn * TILE_N * (p.wide ? 2 : 1) + static_cast<int>(cta_rank) * LOAD_N;
         const int kb0 = slice * p.kb_per_slice;
         const int kb1 = min(kb0 + p.kb_per_slice, p.num_kb);
         // Convolution: image and first input column / row (before the tap's offset) of this
@@ -491,6 +494,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               for (int na = 0; na < LOAD_N / kAtomElems; ++na)
                 ptx::tma_load_2d_pair(b_dst + na * (TILE_K * kAtomBytes), &tmap_b,
                                       col0 + na * kAtomElems, k0, leader_bar);
+              if (p.wide) {  // the same columns of the right-hand tile, behind the left-hand ones
+#pragma unroll
+                for (int na = 0; na < LOAD_N / kAtomElems; ++na)
+                  ptx::tma_load_2d_pair(b_dst + kBHalfBytes + na * (TILE_K * kAtomBytes), &tmap_b,
+                                        col0 + TILE_N + na * kAtomElems, k0, leader_bar);
+              }
             }
           }
           if (u == cluster_id) TNX_TRACE(64 + (kb - kb0));
@@ -532,10 +541,91 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
+      // The MMAs of one K block of one tile: A and B from ring slot `slot`, B `b_byte_off` bytes
+      // into the slot's B area, accumulator at TMEM column `d`.
+      auto mma_block = [&](int slot, uint32_t d, uint32_t b_byte_off, uint32_t& accumulate) {
+        const uint32_t a16 = (smem_a + slot * a_stage_bytes) >> 4;
+        const uint32_t b16 = (smem_b + slot * b_stage_bytes + b_byte_off) >> 4;
+#pragma unroll
+        for (int k16 = 0; k16 < TILE_K / 16; ++k16) {
+          const uint32_t a_off = a16 + (k16 >> 2) * a_slab16 + (k16 & 3) * a_step16;
+          const uint32_t b_off = b16 + (k16 >> 2) * b_slab16 + (k16 & 3) * b_step16;
+          ptx::umma_f16<CTA_GROUP>(d, a_desc_hi | (a_off & 0x3fffu), b_desc_hi | (b_off & 0x3fffu), idesc,
+                                   accumulate);
+          accumulate = 1;
+        }
+      };
+      auto commit_to = [&](uint64_t* bar) {
+        if (CTA_GROUP == 1)
+          ptx::umma_commit(ptx::smem_u32(bar));
+        else
+          ptx::umma_commit_pair(ptx::smem_u32(bar), 0x3);
+      };
       for (int u = cluster_id; u < total_units && ok; u += num_clusters) {
         const int slice = xchg ? static_cast<int>(cluster_rank) : u % p.split_k;
         const int kb0 = slice * p.kb_per_slice;
         const int kb1 = min(kb0 + p.kb_per_slice, p.num_kb);
+        if (CTA_GROUP == 2 && p.wide) {
+          // ---- two column-adjacent tiles at once: left accumulator in TMEM buffer 0, right in
+          // buffer 1, every ring slot's A feeds both.  The epilogue drains the left buffer first,
+          // so the left tile's MMAs of the first K blocks (as many as the ring holds) are issued
+          // before the right buffer is waited for: the tensor pipe has work while it drains.
+          const int nkb = kb1 - kb0;
+          const int ahead = min(nkb, p.stages);
+          const uint32_t d_left = tmem_base, d_right = tmem_base + TILE_N;
+          if (!ptx::mbar_wait<true>(ptx::smem_u32(&ctrl->tmem_empty[0]), acc_phase ^ 1u, abort_flag,
+                                    p.timeout_ns)) {
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+          uint32_t acc_left = 0, acc_right = 0;
+          {
+            int st = stage;
+            uint32_t ph = phase;
+            for (int i = 0; i < ahead && ok; ++i) {
+              if (!ptx::mbar_wait(ptx::smem_u32(&ctrl->full[st]), ph, abort_flag, p.timeout_ns)) {
+                ok = false;
+                break;
+              }
+              ptx::tc_fence_after_sync();
+              mma_block(st, d_left, 0, acc_left);
+              if (++st == p.stages) {
+                st = 0;
+                ph ^= 1u;
+              }
+            }
+          }
+          if (!ok) break;
+          if (nkb == ahead) commit_to(&ctrl->tmem_full[0]);  // the left tile is complete
+          if (!ptx::mbar_wait<true>(ptx::smem_u32(&ctrl->tmem_empty[1]), acc_phase ^ 1u, abort_flag,
+                                    p.timeout_ns)) {
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after_sync();
+          for (int i = 0; i < nkb && ok; ++i) {
+            if (i >= ahead) {
+              if (!ptx::mbar_wait(ptx::smem_u32(&ctrl->full[stage]), phase, abort_flag, p.timeout_ns)) {
+                ok = false;
+                break;
+              }
+              ptx::tc_fence_after_sync();
+              mma_block(stage, d_left, 0, acc_left);
+              if (i == nkb - 1) commit_to(&ctrl->tmem_full[0]);
+            }
+            mma_block(stage, d_right, kBHalfBytes, acc_right);
+            commit_to(&ctrl->empty[stage]);  // frees the slot in both CTAs once both tiles have read it
+            if (++stage == p.stages) {
+              stage = 0;
+              phase ^= 1u;
+            }
+          }
+          if (!ok) break;
+          commit_to(&ctrl->tmem_full[1]);
+          acc_phase ^= 1u;
+          continue;
+        }
         const uint32_t te_bar = ptx::smem_u32(&ctrl->tmem_empty[acc]);
         if (!ptx::mbar_wait<CTA_GROUP == 2>(te_bar, acc_phase ^ 1u, abort_flag, p.timeout_ns)) {
           ok = false;
@@ -622,11 +712,15 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint32_t stores = 0;  // staging buffers used so far (selects the buffer)
     uint32_t xchg_round = 0;  // tiles this cluster has exchanged so far (barrier parity)
     bool ok = true;
-    for (int u = cluster_id; u < total_units && ok; u += num_clusters) {
+    // (a double tile is written out as its left tile, then its right tile: accumulator buffers 0, 1)
+    int half = 0;
+    for (int u = cluster_id; u < total_units && ok;
+         (p.wide && half == 0) ? (half = 1) : (half = 0, u += num_clusters)) {
       const int t = xchg ? u : u / p.split_k;
       const int slice = xchg ? static_cast<int>(cluster_rank) : u - t * p.split_k;
       int tm, tn;
       tile_coords(p, t, tm, tn);
+      if (p.wide) tn = tn * 2 + half;
       const int bt_img = p.batched ? tm / p.bt_tiles_m : 0;  // which matrix of a batch
       // 128-row tile index (inside its matrix for a batch)
       const int row_tile = (tm - bt_img * p.bt_tiles_m) * CTA_GROUP + static_cast<int>(cta_rank);
@@ -1128,6 +1222,8 @@ cudaError_t allow_full_smem(KernelFn fn) {
   return e;
 }
 
+constexpr int kWideHalf = 256;  // tile_n = 512 is two 256-column tiles per CTA pair
+
 // Whether launches ask for programmatic stream serialization (the kernel's set-up overlaps the
 // tail of the kernel before it).  On unless TRITONIX_B200_OVERLAP_SETUP=0.
 bool overlap_setup() {
@@ -1288,7 +1384,16 @@ int umma_query(const tnx_problem& p, tnx_config* cfg, tnx_resources* out) {
               cfg->split_k, cfg->group_m, cfg->tile_order);
     return TNX_ERR_INVALID;
   }
-  if (pick_kernel(cfg->tile_n, cfg->tile_k, cfg->cta_group, glu, p.dtype) == nullptr) {
+  // tile_n = 512: a CTA pair works on two column-adjacent 256-column tiles at once (both TMEM
+  // buffers are live accumulators, one A stage feeds both).
+  const bool wide = cfg->tile_n == 2 * kWideHalf;
+  if (wide && (cfg->cta_group != 2 || cfg->split_k != 1 || cfg->acc_stages != 2 ||
+               cfg->tile_order == TNX_ORDER_TABLE || p.stride_bn != 1)) {
+    set_error("tile_n=512 needs cta_group=2, split_k=1, acc_stages=2, a computed tile order and a row-major B");
+    return TNX_ERR_NOT_BUILT;
+  }
+  const int kernel_tile_n = wide ? kWideHalf : cfg->tile_n;
+  if (pick_kernel(kernel_tile_n, cfg->tile_k, cfg->cta_group, glu, p.dtype) == nullptr) {
     set_error("no kernel built for tile_n=%d cta_group=%d%s", cfg->tile_n, cfg->cta_group,
               glu ? " with a GLU epilogue" : "");
     return TNX_ERR_NOT_BUILT;
@@ -1306,7 +1411,7 @@ int umma_query(const tnx_problem& p, tnx_config* cfg, tnx_resources* out) {
   const int kb_per = cdiv(num_kb, split);
   split = cdiv(num_kb, kb_per);  // no empty slice
 
-  const int load_n = cfg->tile_n / cfg->cta_group;
+  const int load_n = cfg->tile_n / cfg->cta_group;  // (a double tile: the B columns of both tiles)
   const int stage_bytes = (a_box_rows(p, *cfg) + load_n) * cfg->tile_k * 2;
   const int fixed = staging_bytes_for(p, *cfg, split) + kCtrlBytes + kAlignSlack;
   if (cfg->stages == 0) {
@@ -1319,7 +1424,7 @@ int umma_query(const tnx_problem& p, tnx_config* cfg, tnx_resources* out) {
   }
   const long long smem = static_cast<long long>(cfg->stages) * stage_bytes + fixed;
   int tmem = 32;
-  while (tmem < cfg->acc_stages * cfg->tile_n) tmem <<= 1;
+  while (tmem < cfg->acc_stages * kernel_tile_n) tmem <<= 1;
 
   out->kernel = TNX_KERNEL_TCGEN05;
   out->smem_bytes = static_cast<int32_t>(smem > 0x7fffffff ? 0x7fffffff : smem);
@@ -1372,7 +1477,8 @@ int umma_launch(const tnx_problem& p, const tnx_config& cfg, const tnx_resources
     set_error("tcgen05 path needs 16-byte aligned A, B and C base addresses");
     return TNX_ERR_INVALID;
   }
-  KernelFn fn = pick_kernel(cfg.tile_n, cfg.tile_k, cfg.cta_group, glu, p.dtype);
+  const bool wide = cfg.tile_n == 2 * kWideHalf;
+  KernelFn fn = pick_kernel(wide ? kWideHalf : cfg.tile_n, cfg.tile_k, cfg.cta_group, glu, p.dtype);
   if (fn == nullptr) return TNX_ERR_NOT_BUILT;
 
   const int n_out = glu ? p.n / 2 : p.n;
@@ -1412,6 +1518,7 @@ int umma_launch(const tnx_problem& p, const tnx_config& cfg, const tnx_resources
   kp.a_mmajor = a_mmajor ? 1 : 0;
   kp.stages = cfg.stages;
   kp.acc_stages = cfg.acc_stages;
+  kp.wide = wide ? 1 : 0;
   kp.group_m = cfg.group_m;
   kp.tile_order = cfg.tile_order;
   kp.epilogue = p.epilogue;

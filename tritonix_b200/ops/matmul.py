@@ -35,7 +35,7 @@ matmul_kernel = tunable(
     keys=["m", "n", "k"],
     space={
         "block_m": PowerOfTwo(128, 256),
-        "block_n": PowerOfTwo(64, 256),
+        "block_n": PowerOfTwo(64, 512),   # 512: two 256-column tiles per CTA pair, sharing A
         "block_k": PowerOfTwo(64, 128),
         "group_m": Choice([4, 8, 16]),
         "split_k": Choice([1, 2, 4, 8]),
@@ -112,7 +112,15 @@ def default_config(m: int, n: int, k: int, split_k: int | None = None) -> dict:
     def ctas(bm, bn):
         return -(-m // bm) * -(-n // bn) * (bm // 128)
 
-    if m > 128 and n >= 256 and ctas(256, 256) >= 100:
+    def wave_fill(pairs):
+        return pairs / (-(-pairs // 74) * 74)
+
+    if (m > 128 and n >= 512 and k >= 6144 and ctas(256, 512) >= 100
+            and wave_fill(ctas(256, 512) // 2) >= wave_fill(ctas(256, 256) // 2) - 0.05):
+        # two waves or more of double tiles and a K loop long enough to pay for their epilogue
+        # (8192^3: +5 %, K = 14336: +10 %, K = 4096: -4 %): one stage of A feeds two accumulators
+        cfg = {"block_m": 256, "block_n": 512, "block_k": 64, "group_m": 8, "num_stages": 4}
+    elif m > 128 and n >= 256 and ctas(256, 256) >= 100:
         cfg = {"block_m": 256, "block_n": 256, "block_k": 128, "group_m": 16, "num_stages": 3}
     elif n > 64 and (m <= 128 or ctas(128, 128) >= 74):
         cfg = {"block_m": 128, "block_n": 128, "block_k": 128, "group_m": 8, "num_stages": 4}
@@ -162,6 +170,9 @@ def _plausible(m: int, n: int):
             return False
         if cfg["block_n"] > 64 and cfg["block_n"] >= 2 * max(n, 64):
             return False
+        if cfg["block_n"] == 512 and (cfg.get("block_m", 128) != 256 or cfg.get("split_k", 1) != 1
+                                      or cfg.get("acc_stages", 2) != 2):
+            return False  # a double tile needs a CTA pair, both accumulator buffers and all of K
         if cfg.get("acc_stages", 2) == 1:
             # a single accumulator only ties when no CTA ever gets a second tile
             tiles = -(-m // 128) * -(-n // cfg["block_n"]) * cfg.get("split_k", 1)
@@ -179,7 +190,8 @@ def seed_configs(m: int, n: int, k: int, split_k: int | None = None) -> list:
         return [dict(block_m=128, block_n=bn, block_k=128, group_m=8, split_k=int(split_k),
                      num_stages=st, acc_stages=2) for bn, st in ((128, 4), (64, 6), (256, 3))]
     seeds = []
-    for bm, bn, bk, g, st in ((256, 256, 128, 16, 3), (256, 256, 64, 16, 6), (256, 256, 128, 8, 3),
+    for bm, bn, bk, g, st in ((256, 512, 64, 8, 4), (256, 512, 64, 16, 4),
+                              (256, 256, 128, 16, 3), (256, 256, 64, 16, 6), (256, 256, 128, 8, 3),
                               (128, 256, 64, 8, 4), (128, 128, 128, 8, 4), (128, 64, 128, 8, 4)):
         seeds.append(dict(block_m=bm, block_n=bn, block_k=bk, group_m=g, split_k=1, num_stages=st,
                           acc_stages=2))
