@@ -949,21 +949,31 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
 
       // ---- write the tile: chunks of 128 bytes of output per row, through swizzled staging ----
-      for (int chunk = 0; chunk < TILE_N / ACC_PER_CHUNK; ++chunk) {
+      // The accumulator is read 32 columns at a time, one read ahead: while a piece is converted
+      // and staged (and while a chunk's store is handed to TMA and the next buffer is waited
+      // for) the next piece is already on its way out of TMEM.
+      constexpr int kSubs = ACC_PER_CHUNK / 32;  // even: the read-ahead buffers alternate cleanly
+      constexpr int kChunks = TILE_N / ACC_PER_CHUNK;
+      static_assert(kSubs % 2 == 0, "read-ahead needs an even number of pieces per chunk");
+      uint32_t racc[2][32];
+      if (out_col0 < p.n_out) ptx::tmem_ld_32x32(t_acc, racc[0]);
+      for (int chunk = 0; chunk < kChunks; ++chunk) {
         const int out_col = out_col0 + chunk * kAtomElems;
         if (out_col >= p.n_out) break;
+        const bool more_chunks = chunk + 1 < kChunks && out_col + kAtomElems < p.n_out;
         const uint32_t buf = smem_out + (stores & 1u) * kStagingBytes;
         // The TMA store issued two chunks ago must have finished reading this buffer.
         if (epi_tid == 0) ptx::tma_store_wait_read<1>();
         ptx::named_barrier_sync(kEpiBarrier, kEpiThreads);
 #pragma unroll
-        for (int sub = 0; sub < ACC_PER_CHUNK / 32; ++sub) {
+        for (int sub = 0; sub < kSubs; ++sub) {
           const int col = chunk * ACC_PER_CHUNK + sub * 32;
           float v[32];
           {
-            uint32_t r[32];
-            ptx::tmem_ld_32x32(t_acc + col, r);
-            ptx::tmem_ld_wait();
+            uint32_t (&r)[32] = racc[sub & 1];
+            ptx::tmem_ld_wait(r);
+            // (whole warp, converged: the conditions depend on the tile only)
+            if (sub + 1 < kSubs || more_chunks) ptx::tmem_ld_32x32(t_acc + col + 32, racc[(sub + 1) & 1]);
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
           }
