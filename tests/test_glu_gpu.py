@@ -39,6 +39,18 @@ def test_tcgen05_against_oracle(act, m, f, k, dtype, cfg):
     assert_close(out, O.glu_oracle(x, w12, act), dtype)
 
 
+@pytest.mark.parametrize("m,f,k,dtype", [(512, 512, 512, bf16), (1000, 328, 264, f16), (300, 136, 2048, bf16)])
+def test_double_tiles_with_glu_epilogue(m, f, k, dtype):
+    """tile_n = 512 (two 256-column tiles per CTA pair) under the GLU epilogue: bit-identical to
+    single tiles, including a last double tile whose right half is empty or ragged."""
+    x, w12 = seeded(m, k, 2 * f, dtype, seed=f + 1, b_scale=0.02 * (4096 / k) ** 0.5)
+    wide, res = run_gemm(x, w12, {**T, "tile_n": 512, "cta_group": 2, "tile_k": 64, "stages": 4}, EPI["silu"])
+    assert res.kernel == _cabi.KERNEL_TCGEN05 and wide.shape == (m, f)
+    assert_close(wide, O.glu_oracle(x, w12, "silu"), dtype)
+    single, _ = run_gemm(x, w12, {**T, "tile_n": 256, "cta_group": 2, "tile_k": 64}, EPI["silu"])
+    assert torch.equal(wide, single)
+
+
 @pytest.mark.parametrize("m,f,k,dtype", [(64, 36, 50, f16), (100, 35, 90, bf16), (64, 48, 40, f32)])
 def test_strided_kernel_glu(m, f, k, dtype):
     x, w12 = seeded(m, k, 2 * f, dtype, seed=1, b_scale=0.1)
