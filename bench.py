@@ -247,11 +247,26 @@ def setup_contraction(workload, rank, world, dev):
     sw._glu_cfg[(m, n, k)] = dict(GLU_CFG)
     pipe = tnx.HostRowPipeline(dev, k, n_out, dt, rows_per_chunk=rows) if glu else None
 
+    # B is the same on every rank: on several GPUs each rank uploads 1/N of its rows and the
+    # ranks all-gather the rest over NVLink, instead of N uploads of all of B through one host
+    share_b = world > 1 and workload in ("gemm", "gemm_strong") and k % world == 0
+    b_upload = None
+    if share_b:
+        import torch.distributed as dist
+        rows_b = k // world
+        b_slice_host = b_host[rank * rows_b:(rank + 1) * rows_b]
+
+        def b_upload(b_device):
+            mine = b_device[rank * rows_b:(rank + 1) * rows_b]
+            mine.copy_(b_slice_host, non_blocking=True)
+            dist.all_gather_into_tensor(b_device, mine)
+
     def e2e_step():
         # every step uploads A and B from pinned host memory and downloads the result; for the
         # large workloads the rows of A / C are pipelined against the kernel (public helpers)
         if workload in ("gemm", "gemm_strong"):
-            tnx.matmul_from_host(a_host, b_host, c_host, rows_per_chunk=rows, b_device=b_in)
+            tnx.matmul_from_host(a_host, b_host, c_host, rows_per_chunk=rows, b_device=b_in,
+                                 b_upload=b_upload)
         elif glu:
             pipe.run(lambda xd, od: tnx.swiglu(xd, b_in, out=od), a_host, c_host,
                      before=lambda: b_in.copy_(b_host, non_blocking=True))
@@ -261,9 +276,18 @@ def setup_contraction(workload, rank, world, dev):
             out = tnx.matmul_splitk(a_in, b_in, split_k=SPLITK_CFG["split_k"])
             c_host.copy_(out, non_blocking=True)
 
-    work = dict(flops=2.0 * m * n * k, bytes=float(algo_bytes), units=None, launches=1,
-                h2d=a_host.numel() * 2 + b_host.numel() * 2, d2h=c_host.numel() * 2, copies=copies,
-                cfg=cfg, operands=(a_dev, b_dev, c_dev), shape=(m, n, k))
+    def e2e_check():
+        """The end-to-end result (host buffer) against the device-resident one of the same
+        operands: same kernel, same K order, so sampled rows must agree bit for bit."""
+        if copies != 1 or workload not in ("gemm", "gemm_strong"):
+            return None
+        rows_s = sorted({0, m // 3, m - 1})
+        return bool(torch.equal(c_host[rows_s], c_dev[rows_s].cpu()))
+
+    work = dict(flops=2.0 * m * n * k, bytes=float(algo_bytes), units=None, launches=1, e2e_check=e2e_check,
+                h2d=a_host.numel() * 2 + b_host.numel() * 2 // (world if share_b else 1),
+                d2h=c_host.numel() * 2, copies=copies,
+                cfg=cfg, operands=(a_dev, b_dev, c_dev), shape=(m, n, k), share_b=share_b)
     return step, e2e_step, work
 
 
@@ -424,9 +448,45 @@ def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1, mode="auto", tile_split=1
     chunk_mlp = TensorParallelSwiGLU(w12, wd, chunks=1, comm_sms=comm_sms, gate_up_cfg=GLU_CFG,
                                      down_cfg=down_cfg)
 
+    e2e_rows = 4096
+    share_io = world > 1 and e2e_rows % world == 0 and m % e2e_rows == 0
+    if share_io:
+        # x and y are the same on every rank: each rank uploads 1/N of the rows of every chunk
+        # (the ranks all-gather the chunk over NVLink) and downloads 1/N of the chunk's result,
+        # instead of N copies of both crossing the one host's PCIe links
+        import torch.distributed as dist
+        per = e2e_rows // world
+        x_host = x.view(m // e2e_rows, world, per, d)[:, rank].reshape(-1, d).cpu().pin_memory()
+        y_host = torch.empty((m // world, d), dtype=dt).pin_memory()
+        pipe = tnx.HostRowPipeline(dev, d, d, dt, rows_per_chunk=per)
+        x_full = torch.empty((e2e_rows, d), device=dev, dtype=dt)
+        y_full = torch.empty((e2e_rows, d), device=dev, dtype=dt)
+
+        def chunk_fn(xd, yd):
+            dist.all_gather_into_tensor(x_full, xd)
+            chunk_mlp(x_full, out=y_full)
+            yd.copy_(y_full[rank * per:(rank + 1) * per])
+    else:
+        def chunk_fn(xd, yd):
+            chunk_mlp(xd, out=yd)
+
     def e2e_step():
         # rows of x stream in, rows of y stream out, 4096 rows (one all-reduce) at a time
-        pipe.run(lambda xd, yd: chunk_mlp(xd, out=yd), x_host, y_host)
+        pipe.run(chunk_fn, x_host, y_host)
+
+    def e2e_check():
+        """Sampled rows of the end-to-end result against the device-timed implementation's
+        (another chunking or another implementation of the same function: not bit-equal)."""
+        if "y" not in state:
+            return None
+        if share_io:
+            mine = [c * e2e_rows + rank * per + r for c in (0, m // e2e_rows - 1) for r in (0, per - 1)]
+            got = y_host.view(m // e2e_rows, per, d)[[0, 0, -1, -1], [0, per - 1, 0, per - 1]].float()
+        else:
+            mine = [0, m // 2, m - 1]
+            got = y_host[mine].float()
+        want = state["y"][mine].float().cpu()
+        return bool(((got - want).abs().max() / want.abs().max().clamp_min(1e-30)).item() <= 1.5e-2)
 
     def parity():
         """max|err|/max|ref| of sampled tokens of the last step's output against the CPU oracle
@@ -460,6 +520,7 @@ def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1, mode="auto", tile_split=1
                     % (nchunks, comm_sms)) if world > 1 else "none (one GPU)"
     work = dict(flops=flops, bytes=None, units=float(m), launches=launches, h2d=x_host.numel() * 2,
                 d2h=y_host.numel() * 2, copies=1, cfg=cfg, chunks=nchunks, comm_sms=comm_sms,
+                e2e_check=e2e_check, share_io=share_io,
                 parity=parity, mode=mode, exchange=exchange, other=other, fused_note=fused_note,
                 chosen_by=chosen_by)
     return step, e2e_step, work
@@ -574,6 +635,10 @@ def measure(workload, args, rank, local_rank, world, dev, D, peaks):
         ms_e2e = D.max(time_steps(e2e_step, e2e_steps, 3, D.barrier)) / e2e_steps
         tnx.check_status(dev)
 
+    e2e_ok = None
+    if ms_e2e is not None and work.get("e2e_check") is not None:
+        torch.cuda.synchronize(dev)
+        e2e_ok = work["e2e_check"]()
     strong = workload in ("mlp", "gemm_strong")
     # weak scaling: every rank does the whole per-GPU problem; gemm_strong: each rank 1/N of it
     scale = 1 if workload == "mlp" else world
@@ -641,7 +706,16 @@ def measure(workload, args, rank, local_rank, world, dev, D, peaks):
                    "l2": ("operands rotate through %d copies (> 3x L2)" % work["copies"]) if work["copies"] > 1
                    else "operands exceed the 126 MB L2"},
         "e2e": {"value": e2e_value, "unit": unit, "h2d_bytes_per_step": work["h2d"],
-                "d2h_bytes_per_step": work["d2h"], "ms_per_step": ms_e2e},
+                "d2h_bytes_per_step": work["d2h"], "ms_per_step": ms_e2e,
+                **({("agrees_with_device_result" if workload == "mlp" else "equals_device_result"): e2e_ok}
+                   if e2e_ok is not None else {}),
+                **({"note": "bytes per rank; B is identical on every rank: each uploads 1/%d of it "
+                            "and the ranks all-gather the rest over NVLink" % world}
+                   if work.get("share_b") else {}),
+                **({"note": "bytes per rank; x and y are identical on every rank: each uploads 1/%d of "
+                            "every 4096-row chunk (all-gathered over NVLink) and downloads 1/%d of its "
+                            "result" % (world, world)}
+                   if work.get("share_io") else {})},
         "gpu_launches": work["launches"] * args.steps,
         "clocks": clocks.summary(),
         "roofline": roof,

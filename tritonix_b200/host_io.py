@@ -73,12 +73,15 @@ _pipelines: dict = {}
 
 def matmul_from_host(a_host: torch.Tensor, b: torch.Tensor, out_host: torch.Tensor,
                      rows_per_chunk: int = 1024, b_device: Optional[torch.Tensor] = None,
-                     device: Optional[torch.device] = None) -> torch.Tensor:
+                     device: Optional[torch.device] = None,
+                     b_upload: Optional[Callable[[torch.Tensor], None]] = None) -> torch.Tensor:
     """``out_host[:] = a_host @ b`` with A and the result in pinned host memory.
 
     ``b`` may be a device tensor, or a host tensor that is uploaded (into ``b_device`` if given)
-    ahead of the first chunk.  Work is enqueued asynchronously; synchronise the current stream
-    before reading ``out_host``.
+    ahead of the first chunk.  ``b_upload(b_device)``, if given, replaces the plain upload of a
+    host ``b``: it runs on the upload stream and must leave all of B in ``b_device`` (e.g. ranks
+    that hold the same B each upload a slice and all-gather the rest over NVLink).  Work is
+    enqueued asynchronously; synchronise the current stream before reading ``out_host``.
     """
     from tritonix_b200.ops import cuda_matmul
     dev = torch.device(device) if device is not None else (
@@ -95,7 +98,10 @@ def matmul_from_host(a_host: torch.Tensor, b: torch.Tensor, out_host: torch.Tens
             b_device = torch.empty(b.shape, device=dev, dtype=b.dtype)
         b_src, b = b, b_device
         # uploaded on the same stream as A's chunks, so it is complete before the first kernel
-        before = lambda: b_device.copy_(b_src, non_blocking=True)  # noqa: E731
+        if b_upload is not None:
+            before = lambda: b_upload(b_device)  # noqa: E731
+        else:
+            before = lambda: b_device.copy_(b_src, non_blocking=True)  # noqa: E731
 
     def step(x_dev, out_dev):
         cuda_matmul(x_dev, b, out=out_dev)
