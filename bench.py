@@ -403,6 +403,8 @@ def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1, mode="auto", tile_split=1
         import torch.distributed as dist
         ok = torch.ones(1, device=dev)
         failure = None
+        torch.cuda.synchronize(dev)
+        dist.barrier()  # the ranks enter the first call together: its cross-rank waits are bounded
         try:
             y_one = fused(x).clone()
             torch.cuda.synchronize(dev)
