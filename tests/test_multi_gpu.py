@@ -120,6 +120,18 @@ def _fused_worker(rank, world, port, out_dir):
             short = mlp(x[:700].to(dev))           # fewer tokens than the instance was sized for
             tnx.check_status(dev)
             result["err_short"] = O.rel_err(short.cpu(), O.swiglu_mlp_oracle(x[:700], w12_global, wd))
+            # the other exchange mode (fp32 partial outputs, one rounding) and the other dtype
+            exact = FusedTensorParallelSwiGLU(w12.to(dev), wdr.to(dev), max_tokens=m, tile_split=2,
+                                              cfg={"group_m": 2}, fp32_partials=True)
+            y_exact = exact(x.to(dev))
+            tnx.check_status(dev)
+            result["err_fp32_partials"] = O.rel_err(y_exact.cpu(), O.swiglu_mlp_oracle(x, w12_global, wd))
+            half = FusedTensorParallelSwiGLU(w12.half().to(dev), wdr.half().to(dev), max_tokens=m,
+                                             tile_split=4)
+            y_half = half(x.half().to(dev))
+            tnx.check_status(dev)
+            result["err_fp16"] = O.rel_err(y_half.cpu(), O.swiglu_mlp_oracle(x.half(), w12_global.half(),
+                                                                            wd.half()))
         torch.save(result, os.path.join(out_dir, f"f{rank}.pt"))
     finally:
         dist.destroy_process_group()
@@ -133,6 +145,8 @@ def _run_fused(world, tmp_path):
         pytest.skip(results[0].get("skip", "no multicast support"))
     for res in results:
         assert res["err"] <= 8e-3 and res["err_short"] <= 8e-3 and res["repeatable"] and res["same"], res
+        # fp16: the tolerance of one rounding (2e-3) doubled for the in-place sum's second rounding
+        assert res["err_fp32_partials"] <= 8e-3 and res["err_fp16"] <= 4e-3, res
 
 
 def test_in_kernel_exchange_with_one_participant(tmp_path):
