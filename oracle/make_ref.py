@@ -1,6 +1,7 @@
 """Stages the reference's Python package for runs on a GPU box.  TEST INFRASTRUCTURE ONLY.
 
-    python oracle/make_ref.py [<reference source tree>]      (default: /root/reference)
+    python oracle/make_ref.py [<reference source tree>]
+    (default: $TRITONIX_REFERENCE_ROOT, else the directory `reference` beside this repository)
 
 The reference (ayghri/tritonix) is pure Python + Triton, so "building" it is copying the
 `tritonix` package's .py files, unmodified, into oracle/_ref/ — a directory that version
@@ -20,9 +21,17 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 DEST = os.path.join(HERE, "_ref")
 
 
-def stage(root: str = "/root/reference") -> str | None:
+def default_root() -> str:
+    """Where the reference's source tree is expected: the environment's answer, else a checkout
+    named `reference` in the directory that holds this repository."""
+    return os.environ.get("TRITONIX_REFERENCE_ROOT") or os.path.join(
+        os.path.dirname(os.path.dirname(HERE)), "reference")
+
+
+def stage(root: str | None = None) -> str | None:
     """Copies <root>/tritonix/**/*.py to oracle/_ref/tritonix.  Returns the destination, or None
     when there is no reference tree at ``root`` (then whatever was staged before stays)."""
+    root = root or default_root()
     src = os.path.join(root, "tritonix")
     if not os.path.isdir(src):
         return None
@@ -38,5 +47,5 @@ def stage(root: str = "/root/reference") -> str | None:
 
 
 if __name__ == "__main__":
-    out = stage(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    out = stage(sys.argv[1] if len(sys.argv) > 1 else None)
     print(out if out else "no reference tree found; nothing staged")
