@@ -352,7 +352,7 @@ def _mlp_weight_blocks(dev, lo, hi):
     return wg, wu, wd
 
 
-def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1, mode="auto", tile_split=16, band=8, tokens=0,
+def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1, mode="auto", tile_split=16, band=0, tokens=0,
               fp32_partials=False):
     """SwiGLU MLP, tensor parallel: hidden units split over the ranks (column-parallel gate/up,
     row-parallel down projection), partial outputs summed across the ranks.  Global weights come
@@ -377,6 +377,8 @@ def setup_mlp(rank, world, dev, chunks=0, comm_sms=-1, mode="auto", tile_split=1
         w12, wd, chunks=chunks if (isinstance(chunks, list) or chunks > 0) else (1 if world == 1 else 4),
         comm_sms=comm_sms, gate_up_cfg=GLU_CFG, down_cfg=down_cfg)
     state = {}
+    if band <= 0:  # bands of 8 row tiles; 4 where a rank's weights stay in L2 anyway (see the class)
+        band = 4 if 3 * d * fr * 2 <= 48 * 1024 * 1024 else 8
     fused_cfg = {"tile_k": 128, "stages": 3, "group_m": band}
     fused = None
     fused_note = None
@@ -980,8 +982,8 @@ def main():
                     help="mlp one_launch on >1 GPU: exchange fp32 partial outputs (one rounding) instead of bf16")
     ap.add_argument("--tile-split", type=int, default=16,
                     help="mlp one_launch on >1 GPU: CTAs whose spare warps share one row tile's exchange")
-    ap.add_argument("--mlp-band", type=int, default=8,
-                    help="mlp one_launch: 256-row tiles per band")
+    ap.add_argument("--mlp-band", type=int, default=0,
+                    help="mlp one_launch: 256-row tiles per band (0: 8, or 4 when a rank's weights are under 48 MB)")
     ap.add_argument("--mlp-tokens", type=int, default=0,
                     help="mlp: token count, if not the 32768 of the benchmark configuration (a smaller "
                          "case for a profiler capture; the line then names it in config.tokens)")
