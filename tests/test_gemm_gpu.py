@@ -140,6 +140,7 @@ def test_transposed_b_operand(m, n, k, dtype, cfg, epi):
     (2048, 1024, 1024, bf16, {"tile_n": 256, "cta_group": 2, "tile_k": 128, "stages": 3}, True),
     (64, 1024, 2048, f16, {"tile_n": 128, "split_k": 4}, False),
     (200, 256, 320, bf16, {"tile_n": 64, "split_k": 2}, True),
+    (1024, 1024, 768, bf16, {"tile_n": 512, "cta_group": 2, "tile_k": 64, "stages": 4}, False),  # double tiles
 ])
 def test_transposed_a_operand(m, n, k, dtype, cfg, b_transposed):
     """A given as the transpose of a (K, M) row-major tensor (as in a weight-gradient product
