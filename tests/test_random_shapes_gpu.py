@@ -52,3 +52,33 @@ def test_random_problem(seed):
     ref = O.glu_oracle(a, b, EPI[epi]) if epi else O.matmul_oracle(a, b)
     scale = 10 if dtype == torch.float32 else 1
     assert_close(out, ref, dtype, scale=scale)
+
+
+def draw_double_tile_case(rng: random.Random):
+    m = rng.choice([1, 100, 129, 256, 300, 512, 777, 1024, 1500])
+    n = rng.randrange(8, 2600, 8)
+    k = rng.randrange(8, 2100, 8)
+    epi = rng.choice([0, 0, _cabi.EPI_GLU_SILU, _cabi.EPI_GLU_LINEAR])
+    if epi:
+        n = max(16, n // 16 * 16)
+    tile_k = rng.choice([64, 64, 128])
+    cfg = {"tile_n": 512, "cta_group": 2, "tile_k": tile_k,
+           "stages": 2 if tile_k == 128 else rng.choice([2, 3, 4]),
+           "group_m": rng.choice([1, 3, 8]), "tile_order": rng.choice(["grouped", "serpentine"]),
+           "max_ctas": rng.choice([0, 0, 2, 6])}
+    return m, n, k, rng.choice([torch.float16, torch.bfloat16]), epi, cfg
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_random_problem_on_double_tiles(seed):
+    """tile_n = 512 (two 256-column tiles per CTA pair): against the oracle, and bit for bit
+    against the same problem on single tiles."""
+    rng = random.Random(5000 + seed)
+    m, n, k, dtype, epi, cfg = draw_double_tile_case(rng)
+    a, b = seeded(m, k, n, dtype, seed=seed, b_scale=(0.5 * k ** -0.5) if epi else None)
+    out, res = run_gemm(a, b, cfg, epi)
+    assert res.kernel == _cabi.KERNEL_TCGEN05
+    ref = O.glu_oracle(a, b, EPI[epi]) if epi else O.matmul_oracle(a, b)
+    assert_close(out, ref, dtype)
+    single, _ = run_gemm(a, b, {"tile_n": 256, "cta_group": 2, "tile_k": cfg["tile_k"]}, epi)
+    assert torch.equal(out, single)
