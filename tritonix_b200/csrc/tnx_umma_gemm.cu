@@ -776,10 +776,14 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const uint32_t dst_row = ptx::mapa(
               smem_out + (cluster_rank * static_cast<uint32_t>(R) + row_local) * (TILE_N * 4), owner);
           const uint32_t dst_bar = ptx::mapa(full_bar, owner);
+          // (32 columns at a time, one read ahead of the push: whole warp, converged)
+          uint32_t ra[2][32];
+          ptx::tmem_ld_32x32(t_acc, ra[0]);
+#pragma unroll
           for (int c = 0; c < TILE_N / 32; ++c) {
-            uint32_t r[32];
-            ptx::tmem_ld_32x32(t_acc + c * 32, r);  // whole warp, converged
-            ptx::tmem_ld_wait();
+            uint32_t (&r)[32] = ra[c & 1];
+            ptx::tmem_ld_wait(r);
+            if (c + 1 < TILE_N / 32) ptx::tmem_ld_32x32(t_acc + (c + 1) * 32, ra[(c + 1) & 1]);
             if (row_in_tile < p.a_rows) {
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
