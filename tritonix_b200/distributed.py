@@ -199,8 +199,8 @@ class FusedTensorParallelSwiGLU:
     step.  ``tile_split`` crews share one row tile.  No collective library call is made in
     ``forward``.
 
-    The output buffer, the fp32 partial outputs (summed across the ranks before the one rounding
-    to the output type) and the exchange counters live in symmetric memory
+    The output buffer, the exchange counters and (with ``fp32_partials``) the fp32 partial
+    outputs live in symmetric memory
     (``torch.distributed._symmetric_memory``: the same allocation on every rank, bound to one
     multicast object).  ``forward`` returns a view of that buffer: it holds the full result on
     every rank and is overwritten by the next call.  Needs NVSwitch multicast support; when it
@@ -284,6 +284,8 @@ class FusedTensorParallelSwiGLU:
             raise ValueError(f"{m} tokens exceed the {self.max_tokens} this instance was sized for")
         cabi = self._cabi
         y = self._buf[:m * self.d_out * x.element_size()].view(x.dtype).view(m, self.d_out)
+        if (self._epoch + 1) * self.world >= 2 ** 31:
+            self.reset()  # the counters count calls x ranks in 32 bits; every rank gets here at the same call
         self._epoch += 1
         local = self._buf.data_ptr()
         part, sig = self._y_bytes, self._y_bytes + self._part_bytes
