@@ -76,7 +76,7 @@ CONFIG_SOURCE = "fixed in bench.py (the configurations that measured best on a B
 
 # DRAM traffic of the dominant kernel per launch, from the ncu captures summarised under
 # profiles/ (None until a capture of that workload exists).
-NCU_TRAFFIC_BYTES = {"gemm": 1_045_709_568, "gemm_strong": None, "splitk": 125_974_528,
+NCU_TRAFFIC_BYTES = {"gemm": 1_045_709_568, "gemm_strong": None, "splitk": 124_318_464,
                      "glu": 885_355_520, "mlp": None, "conv": 26_989_568}
 
 # swiglu_mlp_kernel at 8192 tokens (d_model 4096, d_ff 14336): dram read + written per launch
