@@ -308,10 +308,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   if (threadIdx.x == 0) TNX_TRACE(0);
   // Launched with programmatic stream serialization, everything above (no global memory touched
   // yet: the tensor maps are kernel parameters) ran while the previous kernel of the stream was
-  // still finishing; from here on its writes are needed, or ours might overtake its reads.  The
-  // kernel after this one may start its own set-up as soon as SMs fall free.  Without the launch
-  // attribute both instructions do nothing.
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  // still finishing.  Its writes are needed, and ours must not overtake its reads, from the
+  // first access to global memory on: the producer waits for that kernel just before its first
+  // load (its first unit's coordinates are computed by then), every epilogue thread on entry;
+  // the MMA thread touches no global memory.  The kernel after this one may start its own
+  // set-up as soon as SMs fall free.  Without the launch attribute the instructions do nothing.
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   // ------------------------------------------------------------------ roles
@@ -325,6 +326,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                : static_cast<uint32_t>(a_stage_bytes + b_stage_bytes) * CTA_GROUP;
       bool weights_resident = false;  // halo convolution: this CTA's copy of the weights is in place
       bool ok = true;
+      bool dependency_met = false;
+      if (p.tile_order == TNX_ORDER_TABLE) {  // the tile table is read from global memory
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        dependency_met = true;
+      }
       for (int u = cluster_id; u < total_units && ok; u += num_clusters) {
         const int t = xchg ? u : u / p.split_k;
         const int slice = xchg ? static_cast<int>(cluster_rank) : u - t * p.split_k;
@@ -362,6 +368,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const int ho = rem / p.cv_wout;
           cv_y = ho * p.cv_sh - p.cv_ph;
           cv_x = (rem - ho * p.cv_wout) * p.cv_sw - p.cv_pw;
+        }
+        if (!dependency_met) {
+          asm volatile("griddepcontrol.wait;" ::: "memory");
+          dependency_met = true;
         }
         for (int kb = kb0; kb < kb1; ++kb) {
           const uint32_t empty_bar = ptx::smem_u32(&ctrl->empty[stage]);
@@ -701,6 +711,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
   } else {
     // ===== epilogue =====
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int quarter = warp & 3;                 // TMEM lanes this warp may touch
     const int row_in_tile = quarter * 32 + lane;  // row of the CTA's 128-row tile held by this thread
     const int epi_tid = threadIdx.x - 64;
