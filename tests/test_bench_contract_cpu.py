@@ -31,3 +31,14 @@ def test_reference_arm_other_ranks_stay_silent():
                           "--gpus", "2", "--steps", "1"], capture_output=True, text=True,
                          timeout=120, cwd=REPO, env=env)
     assert out.returncode == 0 and out.stdout.strip() == ""
+
+
+def test_tile_choice_for_row_shards():
+    """Strong scaling cuts the 8192 rows of the GEMM into N blocks: double tiles unless their last
+    wave over the 74 CTA pairs is much emptier than that of single tiles."""
+    sys.path.insert(0, REPO)
+    import bench
+    assert bench.gemm_cfg_for_rows(8192, 8192) is bench.GEMM_CFG and bench.GEMM_CFG["tile_n"] == 512
+    assert bench.gemm_cfg_for_rows(4096, 8192) is bench.GEMM_CFG_SHORT_K     # 3.46 waves against 6.92
+    assert bench.gemm_cfg_for_rows(2048, 8192) is bench.GEMM_CFG
+    assert bench.gemm_cfg_for_rows(1024, 8192) is bench.GEMM_CFG
