@@ -68,7 +68,8 @@ WORKLOADS = {
 
 # tile_n 512 = two 256-column tiles per CTA pair fed by one stream of A: fewer operand bytes per
 # flop, at the price of an epilogue that is only partly hidden; it pays for long K
-GEMM_CFG = {"kernel": "tcgen05", "tile_n": 512, "tile_k": 64, "stages": 4, "cta_group": 2, "group_m": 8}
+GEMM_CFG = {"kernel": "tcgen05", "tile_n": 512, "tile_k": 64, "stages": 4, "cta_group": 2, "group_m": 8,
+            "tile_order": "serpentine"}
 GEMM_CFG_SHORT_K = {"kernel": "tcgen05", "tile_n": 256, "tile_k": 128, "stages": 3, "cta_group": 2, "group_m": 16}
 SPLITK_CFG = {"kernel": "tcgen05", "tile_n": 128, "tile_k": 128, "stages": 4, "cta_group": 1, "split_k": 4}
 GLU_CFG = {"kernel": "tcgen05", "tile_n": 256, "tile_k": 128, "stages": 3, "cta_group": 2, "group_m": 16}
