@@ -118,6 +118,13 @@ class TunableKernel:
         timed: Dict[tuple, float] = {}   # coordinates -> ms, for the seeds and the final round
         settled = steady_state_ms <= 0
 
+        # Kernels timed at their sustained clock are timed the way they will run: launches back
+        # to back, no L2 flush in between (a flush after every launch lets the GPU cool, and
+        # then the configuration that is best per clock wins, not the one that is best under
+        # the power cap).
+        time_it = _burst_ms if steady_state_ms > 0 else (
+            lambda fn, warm, budget: do_bench(fn, warmup=warm, rep=budget))
+
         def measure(cfg, mem_idx):
             """ms of one configuration, or None (skipped) / "oom" (pruned)."""
             nonlocal best_ms, best_cfg, evaluated, settled
@@ -129,7 +136,7 @@ class TunableKernel:
                     launcher(cfg)  # raises here if the configuration cannot run at all
                     _busy_for(lambda: launcher(cfg), steady_state_ms)
                     settled = True
-                ms = do_bench(lambda: launcher(cfg), warmup=warmup, rep=rep)
+                ms = time_it(lambda: launcher(cfg), warmup, rep)
             except ValueError as exc:
                 if verbose:
                     print(f"  SKIP      {cfg}  ({exc})", flush=True)
@@ -149,6 +156,7 @@ class TunableKernel:
                 print(f"  {ms:8.3f}ms  {cfg}{' *' if improved else ''}", flush=True)
             return ms
 
+        seed_coords: List[tuple] = []
         for seed in seeds:
             if not budget_left():
                 break
@@ -159,7 +167,8 @@ class TunableKernel:
             mem_idx = tuple(mem_values[d].index(seed[n]) for d, n in enumerate(mem_names))
             if trie.is_pruned(mem_idx):
                 continue
-            measure({n: seed[n] for n in names}, mem_idx)
+            if isinstance(measure({n: seed[n] for n in names}, mem_idx), float):
+                seed_coords.append(tuple(position[n][seed[n]] for n in names))
 
         for mem_idx in trie.generate_all_unpruned_midpoint():
             if not budget_left():
@@ -181,14 +190,23 @@ class TunableKernel:
             # The sweep's best few, timed again in alternation: whatever the clocks do in the
             # meantime, they do it to all of them.
             ranked = sorted(timed, key=timed.get)[:finalists]
+            # The seeds were timed first, on a GPU in another state than the rest of the sweep
+            # met: the best three of them get their place in the final whatever they measured.
+            for coords in sorted(seed_coords, key=timed.get)[:3]:
+                if coords not in ranked:
+                    ranked.append(coords)
             cfg_of = lambda coords: {n: axis_values[n][i] for n, i in zip(names, coords)}  # noqa: E731
             rounds: Dict[tuple, List[float]] = {c: [] for c in ranked}
-            for _ in range(3):
+            passes = 3
+            # At the sustained clock a burst must outlast the power controller's memory of the
+            # configuration that ran before it (a frugal one leaves the next one room to boost:
+            # with 30 ms bursts the ranking followed the order of the candidates).
+            final_warm, final_rep = (60.0, 120.0) if steady_state_ms > 0 else (min(warmup, 5), min(rep, 30))
+            for _ in range(passes):
                 for coords in ranked:
                     cfg = cfg_of(coords)
-                    rounds[coords].append(do_bench(lambda: launcher(cfg), warmup=min(warmup, 5),
-                                                   rep=min(rep, 30)))
-            median = {c: sorted(v)[1] for c, v in rounds.items()}
+                    rounds[coords].append(time_it(lambda: launcher(cfg), final_warm, final_rep))
+            median = {c: sorted(v)[passes // 2] for c, v in rounds.items()}
             winner = min(ranked, key=median.get)
             best_cfg = cfg_of(winner)
             if verbose:
@@ -245,6 +263,29 @@ class TunableKernel:
                 print(f"  [{trial + 1}/{max_evals}] {ms:.3f}ms — {cfg}")
         best, _ = client.get_best_parameters()
         return {**fixed, **best}
+
+
+def _burst_ms(fn: Callable[[], Any], warmup: float, rep: float) -> float:
+    """Milliseconds per call of ``fn`` launched back to back for about ``rep`` ms (after about
+    ``warmup`` ms of the same), timed as one burst between two events."""
+    import torch
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    fn()  # (raises here if the configuration cannot run)
+    start.record()
+    for _ in range(3):
+        fn()
+    end.record()
+    torch.cuda.synchronize()
+    estimate = max(start.elapsed_time(end) / 3, 1e-6)
+    for _ in range(max(1, int(warmup / estimate))):
+        fn()
+    n = max(3, int(rep / estimate))
+    start.record()
+    for _ in range(n):
+        fn()
+    end.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(end) / n
 
 
 def _busy_for(fn: Callable[[], Any], milliseconds: float) -> None:

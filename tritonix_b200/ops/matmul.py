@@ -217,7 +217,9 @@ def _tuned(kernel, launcher, shape_key: tuple, a: torch.Tensor, filter_fn, seeds
         cfg = None  # written by a version with a different space
     if cfg is None:
         heavy = flops >= 1e11
-        cfg = kernel.tune(launcher, filter_fn=filter_fn, seeds=seeds, finalists=3,
+        # (kernels that long differ by a few per cent between their best configurations, less
+        # than the clock wanders during a sweep: five finalists, five alternating passes)
+        cfg = kernel.tune(launcher, filter_fn=filter_fn, seeds=seeds, finalists=5 if heavy else 3,
                           steady_state_ms=300.0 if heavy else 0.0)
         # tuning has synchronised anyway: make sure no probed configuration gave up a device wait
         _cabi.check_status(a.device)
